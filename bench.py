@@ -1,0 +1,353 @@
+#!/usr/bin/env python
+"""EMA chunked scan benchmark: forward + backward tokens/s on B200, with roofline and CPU baseline.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]            # this library
+    python bench.py --impl reference [--steps K] [--warmup W]      # the reference's CPU path
+
+One "step" is one forward (y, saved tile states) plus one backward (dx, da) over one batch of
+synthetic input with the shapes of the headline workload: x, dy bf16 [16, 8192, 2, 1024] ~ N(0,1),
+time-invariant decay a fp32 [2] = sigmoid(U(2,6)).  A token is one (b, t) position (all h*d
+channels), so a step processes b*L = 131072 tokens per GPU.  With N > 1 every rank runs its own
+batch shard of that size (rows are independent: no data-path collective; the per-head decay
+gradient is all-reduced, h floats) and the reported value is the whole-job aggregate.
+
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "triton-kernels_b200"))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(name="ema_fwd_bwd_b16_L8192_h2_d1024_bf16_perhead_decay_chunk256",
+                b=16, L=8192, h=2, d=1024, chunk=256)
+METRIC = "ema_fwd_bwd_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t_begin, t_end):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        inside = [r for (t, r) in self.rows if t_begin <= t <= t_end + 0.2] or [r for (_, r) in self.rows]
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in inside:
+            try:
+                sm.append(float(r[1]))
+                mx = float(r[2])
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def algorithmic_bytes(b, L, h, d, s=2):
+    n = b * L * h * d
+    fwd = n * 2 * s + 4 * h                   # x read, y written, a[h] read
+    bwd = n * 3 * s + 4 * h + 4 * h           # x, dy read, dx written, a read, da written
+    return fwd, bwd
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU reference arm
+# ---------------------------------------------------------------------------------------------
+def cpu_reference_sample(b, L, h, d, steps, warmup):
+    """Times the reference's CPU path (sequential PyTorch loop, autograd backward), restated in
+    oracle/ema_loop_port.py, on a bounded sample: `b` batch rows of the workload, `L` steps."""
+    import torch
+    from oracle import ema_loop_port as lp
+    g = torch.Generator().manual_seed(1236)
+    x = torch.randn((b, L, h, d), generator=g)
+    dy = torch.randn((b, L, h, d), generator=g)
+    a = torch.sigmoid(2 + 4 * torch.rand((h,), generator=g))
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        lp.north_star_fwd_bwd(x, a, dy)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    sec = sum(times) / len(times)
+    return b * L / sec, sec, torch.get_num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sb, sL = 1, 1024
+    val, sec, threads = cpu_reference_sample(sb, sL, WORKLOAD["h"], WORKLOAD["d"], args.steps, args.warmup)
+    sample = (f"{sb} of {WORKLOAD['b']} batch rows x first {sL} of {WORKLOAD['L']} steps x all "
+              f"{WORKLOAD['h']}x{WORKLOAD['d']} channels per step; the loop is sequential over rows and "
+              "steps, so tokens/s does not depend on the sample size")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], "sample": sample},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
+                         "host_cpus": os.cpu_count()},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the EMA library has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    import ema_b200
+    from ema_b200 import ops
+
+    W = WORKLOAD
+    b, L, h, d = W["b"], W["L"], W["h"], W["d"]
+    g = torch.Generator(device=dev).manual_seed(1236 + rank)
+    x = torch.randn((b, L, h, d), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    dy = torch.randn((b, L, h, d), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+    a = torch.sigmoid(2 + 4 * torch.rand((h,), generator=torch.Generator(device=dev).manual_seed(99), device=dev))
+    y = torch.empty_like(x)
+    dx = torch.empty_like(x)
+    da = torch.empty_like(a)
+    ts, nt = ops.n_tiles_of(x, a)
+    tile_states = torch.empty((b * h, nt, d), dtype=torch.float32, device=dev)
+    ws = None
+
+    def step():
+        nonlocal ws
+        ops.ema_fwd(x, a, out=y, tile_states=tile_states)
+        r = ops.ema_bwd(x, a, dy, tile_states, dx=dx, ddecay=da, workspace=ws)
+        ws = r["workspace"]
+        if world > 1:
+            dist.all_reduce(da)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+
+    K = args.steps
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(K)]
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t_begin = time.time()
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(K):
+        ev[i][0].record()
+        ops.ema_fwd(x, a, out=y, tile_states=tile_states)
+        ev[i][1].record()
+        ops.ema_bwd(x, a, dy, tile_states, dx=dx, ddecay=da, workspace=ws)
+        ev[i][2].record()
+        if world > 1:
+            dist.all_reduce(da)
+    stop.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t_end = time.time()
+    elapsed_ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
+
+    fwd_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    bwd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    ms_per_step = elapsed_ms / K
+    tokens = b * L * world
+    value = tokens / (ms_per_step * 1e-3)
+
+    # ---- end to end through the public API with host buffers (pinned), copies inside the timing
+    e2e = None
+    try:
+        hx, hdy = x.cpu().pin_memory(), dy.cpu().pin_memory()
+        ha = a.cpu().pin_memory()
+        hy, hdx = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
+        hda = torch.empty_like(ha).pin_memory()
+        xd, dyd, ad = torch.empty_like(x), torch.empty_like(dy), torch.empty_like(a)
+
+        def e2e_step():
+            xd.copy_(hx, non_blocking=True)
+            dyd.copy_(hdy, non_blocking=True)
+            ad.copy_(ha, non_blocking=True)
+            xr = xd.requires_grad_(True)
+            ar = ad.requires_grad_(True)
+            out = ema_b200.ema(xr, ar)
+            out.backward(dyd)
+            hy.copy_(out.detach(), non_blocking=True)
+            hdx.copy_(xr.grad, non_blocking=True)
+            hda.copy_(ar.grad, non_blocking=True)
+            xr.grad = None
+            ar.grad = None
+            xd.requires_grad_(False)
+            ad.requires_grad_(False)
+
+        e2e_steps = min(K, 5)
+        e2e_step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        s1.record()
+        torch.cuda.synchronize()
+        e2e_ms = s0.elapsed_time(s1) / e2e_steps
+        if world > 1:
+            t = torch.tensor([e2e_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        nbytes = x.numel() * 2
+        e2e = {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": 2 * nbytes + 4 * h, "d2h_bytes_per_step": 2 * nbytes + 4 * h,
+               "api": "ema_b200.ema(x, a) + backward, pinned host buffers for x, dy, a -> y, dx, da"}
+        del hx, hdy, hy, hdx, xd, dyd
+    except RuntimeError as exc:  # e.g. pinned allocation refused
+        e2e = {"value": None, "unit": UNIT, "error": str(exc)[:200]}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peaks()
+    fwd_b, bwd_b = algorithmic_bytes(b, L, h, d)
+    bwd_gbs = bwd_b / (bwd_ms * 1e-3) / 1e9
+    fwd_gbs = fwd_b / (fwd_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": "ema_bwd (reverse scan: reads x, dy, writes dx; plus its small da reduction)",
+                "achieved": bwd_gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                "frac": bwd_gbs / peak, "traffic": None,
+                "algorithmic_bytes_per_launch": bwd_b, "ms_per_launch": bwd_ms,
+                "fwd": {"achieved": fwd_gbs, "frac": fwd_gbs / peak, "algorithmic_bytes_per_launch": fwd_b,
+                        "ms_per_launch": fwd_ms},
+                "step": {"achieved": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9,
+                         "frac": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9 / peak}}
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        with open(traffic_file) as f:
+            roofline["traffic"] = json.load(f).get("ema_bwd_bytes_per_launch")
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        sb, sL = 1, 4096
+        val, sec, threads = cpu_reference_sample(sb, sL, h, d, steps=1, warmup=0)
+        cpu_baseline = {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
+                        "sample": f"{sb} of {b} batch rows x first {sL} of {L} steps, fwd + autograd bwd, "
+                                  f"{sec:.1f} s; sequential Python loop, tokens/s independent of sample size",
+                        "host_cpus": os.cpu_count()}
+        try:
+            from oracle import ema_oracle as eo
+            import numpy as np
+            xs = np.random.RandomState(0).standard_normal((2, L, h, d)).astype(np.float32)
+            an = a.cpu().numpy()
+            t0 = time.perf_counter()
+            eo.fwd(xs, an)
+            eo.bwd(xs, an, xs)
+            cpu_baseline["c_oracle_tokens_per_s"] = 2 * L / (time.perf_counter() - t0)
+            cpu_baseline["c_oracle_threads"] = min(eo.threads(), 2 * h)
+        except Exception as exc:  # the C oracle is optional context, never the measured product
+            cpu_baseline["c_oracle_error"] = str(exc)[:120]
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 in/out, f32 accumulate", "data": "synthetic",
+        "config": {"workload": W["name"], "b_per_gpu": b, "L": L, "h": h, "d": d, "chunk": W["chunk"],
+                   "tile_steps": ts, "sharding": "batch rows per rank, no data-path collective",
+                   "l2": "inputs (2 GiB per step) exceed the 126 MB L2; no flush needed"},
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+        "gpu_launches": 4 * K, "clocks": clocks,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps > 10:
+            args.steps = 10  # each step is a ~2 s CPU sample
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,170 @@
+/*
+ * ema_b200.h - C ABI of libema_b200.so: the EMA chunked scan (forward and backward) as
+ * hand-written CUDA for NVIDIA B200 (sm_100a).
+ *
+ * The library replaces the GPU side of the reference project's EMA path.  The reference has no
+ * FFI of its own: its boundary is a set of Python functions that launch Triton kernels.  Every
+ * entry point below names the reference function (file:line inside the reference project) whose
+ * device work it performs; the Python drop-ins with the reference's names and signatures call
+ * these through ctypes.
+ *
+ * Conventions for every call
+ *   - returns EMA_OK (0) or a negative EMA_ERR_* code; never throws, aborts or traps;
+ *   - every pointer is a DEVICE pointer owned by the caller; the library allocates nothing;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*) and the call returns
+ *     without synchronising; a bad argument is reported before anything is launched;
+ *   - x, y, dy, dx have element type `dtype` (EMA_F32 or EMA_BF16); decay, states, gradients
+ *     of the decay and all workspaces are fp32; accumulation is always fp32.
+ */
+#ifndef EMA_B200_H
+#define EMA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EMA_B200_VERSION 100
+
+enum {
+    EMA_OK = 0,
+    EMA_ERR_BADARG = -1,      /* null pointer, negative size, inconsistent shape             */
+    EMA_ERR_ALIGN = -2,       /* pointer or stride not aligned as the dtype requires          */
+    EMA_ERR_UNSUPPORTED = -3, /* valid request the library has no kernel for                  */
+    EMA_ERR_CUDA = -4,        /* a CUDA call failed; see ema_b200_last_cuda_error()           */
+    EMA_ERR_TIMEOUT = -5,     /* a bounded device-side wait ran out                           */
+    EMA_ERR_WORKSPACE = -6    /* workspace pointer null or smaller than _workspace_bytes says */
+};
+
+enum { EMA_F32 = 0, EMA_BF16 = 1 };
+
+/* decay_mode */
+enum {
+    EMA_DECAY_PER_STEP = 0, /* decay[b, L, h] with element strides a_sb, a_sl, a_sh            */
+    EMA_DECAY_PER_HEAD = 1  /* decay[h] with element stride a_sh (time-invariant)              */
+};
+
+/* convention */
+enum {
+    /* decay holds a in (0,1) and x is the raw input:  y_t = a_t y_{t-1} + (1 - a_t) x_t;
+     * the backward returns d/dx and d/da.                                                     */
+    EMA_CONV_NORTH_STAR = 0,
+    /* decay holds A = log a <= 0 and x is the pre-scaled input u = (1-a) x, the pair
+     * (A_ema, X_ema) of the reference's chunked kernels:  y_t = exp(A_t) y_{t-1} + u_t;
+     * the backward returns d/du and d/dA.                                                     */
+    EMA_CONV_PRESCALED_LOG = 1
+};
+
+/* One EMA problem on the strided 4-D view x[b, L, h, d] (d contiguous; rows of the scan are the
+ * (b, h) pairs).  The reference's folded layout X[B, L, T] is the case h = 1, b = B, d = T.
+ * All strides are in ELEMENTS of the tensor they describe. */
+typedef struct ema_b200_problem {
+    int64_t b, L, h, d;
+    int64_t x_sb, x_sl, x_sh; /* input x                                      */
+    int64_t y_sb, y_sl, y_sh; /* output: y in the forward, dx in the backward  */
+    int64_t g_sb, g_sl, g_sh; /* upstream gradient dy (backward only)          */
+    int64_t a_sb, a_sl, a_sh; /* decay, and its gradient in the backward       */
+    int32_t dtype;            /* EMA_F32 | EMA_BF16                            */
+    int32_t decay_mode;       /* EMA_DECAY_PER_STEP | EMA_DECAY_PER_HEAD       */
+    int32_t convention;       /* EMA_CONV_NORTH_STAR | EMA_CONV_PRESCALED_LOG  */
+    int32_t chunk;            /* API-level chunk size Q for chunk_states; 0 = none */
+} ema_b200_problem;
+
+/* ---- library info ------------------------------------------------------------------------ */
+
+int ema_b200_version(void);
+/* cudaError_t of the most recent failing CUDA call made by this library on this thread. */
+int ema_b200_last_cuda_error(void);
+const char *ema_b200_error_string(int code);
+
+/* Number of time steps one internal tile covers for this problem.  The forward writes one saved
+ * state per tile and the backward consumes them, so both report the same value for the same
+ * (dtype, d, strides).  n_tiles = ceil(L / tile_steps). */
+int ema_b200_tile_steps(const ema_b200_problem *p);
+
+/* Bytes of fp32 storage for the per-tile saved states the forward hands to the backward:
+ * [b*h, n_tiles, d]. */
+size_t ema_b200_tile_states_bytes(const ema_b200_problem *p);
+
+/* Bytes of scratch the backward needs (partial sums of the decay gradient, one slice per
+ * channel tile, reduced by a second kernel in a fixed order: no float atomics). */
+size_t ema_b200_bwd_workspace_bytes(const ema_b200_problem *p);
+
+/* ---- fused path -------------------------------------------------------------------------- */
+
+/* Forward scan: one read of x, one write of y (y may be null: only the states are produced).
+ * Replaces the four launches of _ema_matmul_scan_combined_fwd
+ * (kernels/ema_kernels/ema_combined_fwd.py:12-47) and the three of EMAChunkScanCombinedFn.forward
+ * (kernels/ema.py:283-364).
+ *   chunk_states  optional [b, h, ceil(L/chunk), d] fp32: state at the START of every API chunk
+ *                 (the `states` the reference returns, kernels/ema_kernels/ema_state_pass.py:100-120)
+ *   tile_states   optional [b*h, n_tiles, d] fp32 for ema_b200_bwd
+ *   init_state    optional [b, h, d] fp32 state before step 0 (zeros when null)
+ *   final_state   optional [b, h, d] fp32 state after step L-1
+ *   log_decay_sum optional [b, h] fp32: sum of log a over the steps that were processed
+ *   stop_below    0 to scan all L steps.  > 0: stop after the first tile at whose end the
+ *                 product of decays since step 0 is below this value - used to re-scan only the
+ *                 prefix an incoming carry can still influence (sequence-parallel fix-up). */
+int ema_b200_fwd(const ema_b200_problem *p, const void *x, const float *decay, void *y,
+                 float *chunk_states, float *tile_states, const float *init_state,
+                 float *final_state, float *log_decay_sum, float stop_below, void *stream);
+
+/* Backward scan: reads x, dy and the saved tile states once, writes dx and d(decay).
+ * Replaces the nine launches and the torch glue of _ema_chunk_scan_combined_bwd
+ * (kernels/ema_kernels_bwd/ema_combined_bwd.py:13-82).
+ *   ddecay        [b, L, h] (strides a_s*) or [h]; overwritten, not accumulated
+ *   dfinal_state  optional [b, h, d]: gradient flowing into the state after step L-1
+ *   dinit_state   optional [b, h, d]: receives the gradient of the state before step 0
+ *   stop_below    as in the forward, counted from step L-1 backwards (suffix re-scan)
+ *   workspace     ema_b200_bwd_workspace_bytes(p) bytes, 16-byte aligned */
+int ema_b200_bwd(const ema_b200_problem *p, const void *x, const float *decay, const void *dy,
+                 const float *tile_states, void *dx, float *ddecay, const float *dfinal_state,
+                 float *dinit_state, float stop_below, void *workspace, size_t workspace_bytes,
+                 void *stream);
+
+/* ---- stage kernels on the reference's folded layouts --------------------------------------
+ * X, dout, out, dx: [B, L, T] contiguous, element type `dtype`;  A: [B, L] fp32 with element
+ * strides (A_sb, A_sl);  cs: [B, C, Q] fp32 contiguous;  per-chunk states: [B, C, T] fp32
+ * contiguous;  C = ceil(L / Q). */
+
+/* ema_chunk_cumsum_fwd, kernels/ema_kernels/ema_cumsum.py:66 (kernel :32). */
+int ema_b200_chunk_cumsum(const float *A, int64_t A_sb, int64_t A_sl, float *cs, int64_t B,
+                          int64_t L, int Q, void *stream);
+/* _ema_chunk_state_fwd, kernels/ema_kernels/ema_state_fwd.py:130 (kernel :54). */
+int ema_b200_chunk_state(const void *X, const float *cs, float *S, int dtype, int64_t B, int64_t L,
+                         int64_t T, int Q, void *stream);
+/* _ema_state_passing_fwd, kernels/ema_kernels/ema_state_pass.py:125 (kernel :57).
+ * cs_last has element strides (cl_sb, cl_sc) so that the view cs[..., -1] can be passed as is. */
+int ema_b200_state_passing_fwd(const float *S, const float *cs_last, int64_t cl_sb, int64_t cl_sc,
+                               float *out, float *final_states, int64_t B, int64_t C, int64_t T,
+                               void *stream);
+/* _ema_scan_fwd, kernels/ema_kernels/ema_scan_fwd.py:161 (kernel :53). */
+int ema_b200_chunk_scan(const void *X, const float *cs, const float *h, void *out, int dtype,
+                        int64_t B, int64_t L, int64_t T, int Q, void *stream);
+/* _ema_chunk_scan_bwd_dstates, kernels/ema_kernels_bwd/ema_scan_bwd.py:132 (kernel :39). */
+int ema_b200_bwd_dstates(const float *cs, const void *dout, float *dh, int dtype, int64_t B,
+                         int64_t L, int64_t T, int Q, void *stream);
+/* _ema_state_passing_bwd, kernels/ema_kernels_bwd/ema_state_passing_bwd_dstates.py:103 (kernel :20). */
+int ema_b200_state_passing_bwd(const float *h, const float *cs_last, int64_t cl_sb, int64_t cl_sc,
+                               const float *dh, float *dS, float *ddA_last, int64_t B, int64_t C,
+                               int64_t T, void *stream);
+/* _chunk_scan_chunk_state_bwd_dx, kernels/ema_kernels_bwd/ema_chunk_scan_chunk_state_bwd_dx.py:208 (kernel :69). */
+int ema_b200_bwd_dx(const float *cs, const void *dout, const float *dS, void *dx, int dtype,
+                    int64_t B, int64_t L, int64_t T, int Q, void *stream);
+/* _ema_chunk_state_bwd_db, kernels/ema_kernels_bwd/ema_chunk_state_bwd_db.py:122 (kernel :28);
+ * raw != 0 skips the cumulative sum, like raw_scale_gradient=True. */
+int ema_b200_bwd_db(const void *X, const float *cs, const float *dS, float *ddA, int dtype, int raw,
+                    int64_t B, int64_t L, int64_t T, int Q, void *stream);
+/* _ema_chunk_scan_bwd_dC, kernels/ema_kernels_bwd/ema_chunk_scan_bwd_dc.py:115 (kernel :25). */
+int ema_b200_bwd_dc(const float *h, const float *cs, const void *dout, float *ddA, int dtype,
+                    int64_t B, int64_t L, int64_t T, int Q, void *stream);
+/* _ema_chunk_scan_bwd_ddAcs_stable, kernels/ema_kernels_bwd/ema_scan_da.py:113 (kernel :25). */
+int ema_b200_bwd_dacs(const void *X, const float *cs, const void *dout, float *ddA, int dtype,
+                      int64_t B, int64_t L, int64_t T, int Q, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EMA_B200_H */

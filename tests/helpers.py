@@ -1,0 +1,56 @@
+"""Shared helpers for the GPU parity tests: seeded inputs and the tolerances of the contract.
+
+Tolerances (stated once, used everywhere):
+  fp32 inputs : y and dx within 1e-4 max-abs of the sequential fp32 EMA; the decay gradient is a sum
+                over d (and over b, L for per-head decay) of products of size O(1), so it is compared
+                with 1e-4 + 2e-5 * max|ref|.
+  bf16 inputs : oracle run in fp32/fp64 on the bf16-rounded inputs; every output within
+                2e-2 * max|ref| (normalised max error), fp32 accumulation on the GPU side.
+"""
+import numpy as np
+import torch
+
+from oracle import ema_oracle as eo
+
+FP32_ATOL = 1e-4
+BF16_REL = 2e-2
+
+
+def make_inputs(seed, b, L, h, d, lo=2.0, hi=6.0, per_head=False, dtype=torch.float32, device="cuda"):
+    """x, dy ~ N(0,1); a = sigmoid(U(lo,hi)).  Returns torch tensors on `device` and the numpy fp32
+    copies of the (dtype-rounded) values the oracle must see."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = torch.randn((b, L, h, d), generator=g, dtype=torch.float32).to(dtype)
+    dy = torch.randn((b, L, h, d), generator=g, dtype=torch.float32).to(dtype)
+    shape = (h,) if per_head else (b, L, h)
+    a = torch.sigmoid(lo + (hi - lo) * torch.rand(shape, generator=g, dtype=torch.float32))
+    np_in = (x.float().numpy(), a.numpy(), dy.float().numpy())
+    return x.to(device), a.to(device), dy.to(device), np_in
+
+
+def assert_close_fp32(got, ref, what, scale_rel=0.0):
+    got = got.detach().float().cpu().numpy() if isinstance(got, torch.Tensor) else got
+    err = float(np.abs(got - ref).max()) if ref.size else 0.0
+    tol = FP32_ATOL + scale_rel * (float(np.abs(ref).max()) if ref.size else 0.0)
+    assert err <= tol, f"{what}: max abs err {err:.3e} > {tol:.3e}"
+
+
+def assert_close_bf16(got, ref, what, rel=BF16_REL):
+    got = got.detach().float().cpu().numpy() if isinstance(got, torch.Tensor) else got
+    scale = float(np.abs(ref).max()) if ref.size else 1.0
+    err = float(np.abs(got - ref).max()) if ref.size else 0.0
+    assert err <= rel * max(scale, 1e-6), f"{what}: normalised max err {err / max(scale, 1e-6):.3e} > {rel}"
+
+
+def check_outputs(dtype, got, ref, what, grad_of_decay=False):
+    if dtype == torch.float32:
+        assert_close_fp32(got, ref, what, scale_rel=2e-5 if grad_of_decay else 0.0)
+    else:
+        assert_close_bf16(got, ref, what)
+
+
+def oracle_fwd_bwd(np_in, convention=eo.NORTH_STAR, acc64=True):
+    x, a, dy = np_in
+    y = eo.fwd(x, a, convention=convention, acc64=acc64)
+    dx, da = eo.bwd(x, a, dy, convention=convention, acc64=acc64)
+    return y, dx, da

@@ -1,0 +1,178 @@
+// C-ABI entry points of the fused path: argument checks, kernel selection, launches.
+#include "ema_common.cuh"
+
+#include <cstring>
+
+namespace ema {
+
+static thread_local int g_last_cuda_error = 0;
+void set_last_cuda_error(cudaError_t e) { g_last_cuda_error = static_cast<int>(e); }
+
+namespace {
+
+inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+int check_problem(const ema_b200_problem *p) {
+    if (!p) return EMA_ERR_BADARG;
+    if (p->b < 0 || p->L < 0 || p->h < 0 || p->d < 0) return EMA_ERR_BADARG;
+    if (p->dtype != EMA_F32 && p->dtype != EMA_BF16) return EMA_ERR_UNSUPPORTED;
+    if (p->decay_mode != EMA_DECAY_PER_STEP && p->decay_mode != EMA_DECAY_PER_HEAD) return EMA_ERR_BADARG;
+    if (p->convention != EMA_CONV_NORTH_STAR && p->convention != EMA_CONV_PRESCALED_LOG) return EMA_ERR_BADARG;
+    if (p->chunk < 0) return EMA_ERR_BADARG;
+    if (p->L >= (1ll << 31) - 4096) return EMA_ERR_UNSUPPORTED;
+    if (p->b * p->h > (1ll << 24) || p->d > (1ll << 24)) return EMA_ERR_UNSUPPORTED;
+    return EMA_OK;
+}
+
+// widest vector the FMA kernels may use on every big tensor of this call
+int pick_vec(const ema_b200_problem *p, const void *x, const void *out, const void *dy) {
+    const size_t es = p->dtype == EMA_F32 ? 4 : 2;
+    bool ok = p->d % 4 == 0;
+    auto strides_ok = [](int64_t a, int64_t b, int64_t c) { return a % 4 == 0 && b % 4 == 0 && c % 4 == 0; };
+    ok = ok && strides_ok(p->x_sb, p->x_sl, p->x_sh) && strides_ok(p->y_sb, p->y_sl, p->y_sh);
+    ok = ok && aligned(x, 4 * es) && aligned(out, 4 * es);
+    if (dy) ok = ok && strides_ok(p->g_sb, p->g_sl, p->g_sh) && aligned(dy, 4 * es);
+    return ok ? 4 : 1;
+}
+
+void fill_params(FusedParams &fp, const ema_b200_problem *p, int vec) {
+    std::memset(&fp, 0, sizeof(fp));
+    fp.b = p->b; fp.L = p->L; fp.h = p->h; fp.d = p->d;
+    fp.x_sb = p->x_sb; fp.x_sl = p->x_sl; fp.x_sh = p->x_sh;
+    fp.o_sb = p->y_sb; fp.o_sl = p->y_sl; fp.o_sh = p->y_sh;
+    fp.g_sb = p->g_sb; fp.g_sl = p->g_sl; fp.g_sh = p->g_sh;
+    fp.a_sb = p->a_sb; fp.a_sl = p->a_sl; fp.a_sh = p->a_sh;
+    fp.decay_mode = p->decay_mode;
+    fp.convention = p->convention;
+    fp.chunk = p->chunk;
+    fp.n_tiles = static_cast<int>((p->L + kFmaTile - 1) / kFmaTile);
+    const int dt = kFmaCT * vec;
+    fp.n_dtiles = static_cast<int>((p->d + dt - 1) / dt);
+    fp.n_chunks = p->chunk > 0 ? (p->L + p->chunk - 1) / p->chunk : 0;
+}
+
+}  // namespace
+}  // namespace ema
+
+using namespace ema;
+
+extern "C" int ema_b200_version(void) { return EMA_B200_VERSION; }
+
+extern "C" int ema_b200_last_cuda_error(void) { return g_last_cuda_error; }
+
+extern "C" const char *ema_b200_error_string(int code) {
+    switch (code) {
+        case EMA_OK: return "ok";
+        case EMA_ERR_BADARG: return "bad argument (null pointer, negative size or inconsistent shape)";
+        case EMA_ERR_ALIGN: return "pointer or stride not aligned for the element type";
+        case EMA_ERR_UNSUPPORTED: return "request not supported by this library";
+        case EMA_ERR_CUDA: return "a CUDA call failed (see ema_b200_last_cuda_error)";
+        case EMA_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+        case EMA_ERR_WORKSPACE: return "workspace missing or too small";
+        default: return "unknown error code";
+    }
+}
+
+extern "C" int ema_b200_tile_steps(const ema_b200_problem *p) {
+    if (check_problem(p) != EMA_OK) return 0;
+    return kFmaTile;
+}
+
+extern "C" size_t ema_b200_tile_states_bytes(const ema_b200_problem *p) {
+    if (check_problem(p) != EMA_OK) return 0;
+    const int64_t n_tiles = (p->L + kFmaTile - 1) / kFmaTile;
+    return static_cast<size_t>(p->b * p->h * n_tiles * p->d) * sizeof(float);
+}
+
+extern "C" size_t ema_b200_bwd_workspace_bytes(const ema_b200_problem *p) {
+    if (check_problem(p) != EMA_OK) return 0;
+    // sized for the narrowest channel tile (vec = 1) so that it never depends on pointer alignment
+    const int64_t n_tiles = (p->L + kFmaTile - 1) / kFmaTile;
+    const int64_t n_dtiles = (p->d + kFmaCT - 1) / kFmaCT;
+    const int64_t rows = p->b * p->h;
+    const int64_t per_step = rows * n_dtiles * n_tiles * kFmaTile;
+    const int64_t per_head = kHeadPartialOffset(rows) + rows * n_dtiles * n_tiles * (kFmaThreads / 32);
+    const int64_t n = p->decay_mode == EMA_DECAY_PER_STEP ? per_step : per_head;
+    return static_cast<size_t>(n > 0 ? n : 1) * sizeof(float);
+}
+
+extern "C" int ema_b200_fwd(const ema_b200_problem *p, const void *x, const float *decay, void *y,
+                            float *chunk_states, float *tile_states, const float *init_state,
+                            float *final_state, float *log_decay_sum, float stop_below, void *stream) {
+    int rc = check_problem(p);
+    if (rc) return rc;
+    if (!x || !decay) return EMA_ERR_BADARG;
+    if (!y && !chunk_states && !tile_states && !final_state) return EMA_ERR_BADARG;
+    if (chunk_states && p->chunk <= 0) return EMA_ERR_BADARG;
+    if (!(stop_below >= 0.f)) return EMA_ERR_BADARG;
+    const size_t es = p->dtype == EMA_F32 ? 4 : 2;
+    if (!aligned(x, es) || !aligned(y, es) || !aligned(decay, 4)) return EMA_ERR_ALIGN;
+    auto st = static_cast<cudaStream_t>(stream);
+    const int64_t rows = p->b * p->h;
+    if (rows == 0 || p->d == 0) return EMA_OK;
+    if (p->L == 0) {
+        // nothing to scan: the state passes through
+        cudaError_t e = cudaSuccess;
+        if (final_state) {
+            e = init_state ? cudaMemcpyAsync(final_state, init_state, rows * p->d * 4, cudaMemcpyDeviceToDevice, st)
+                           : cudaMemsetAsync(final_state, 0, rows * p->d * 4, st);
+        }
+        if (e == cudaSuccess && log_decay_sum) e = cudaMemsetAsync(log_decay_sum, 0, rows * 4, st);
+        if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
+        return EMA_OK;
+    }
+    const int vec = pick_vec(p, x, y ? y : x, nullptr);
+    FusedParams fp;
+    fill_params(fp, p, vec);
+    fp.x = x; fp.decay = decay; fp.out = y;
+    fp.chunk_states = chunk_states; fp.tile_states = tile_states;
+    fp.init_state = init_state; fp.final_state = final_state;
+    fp.log_decay_sum = log_decay_sum;
+    fp.stop_below = stop_below;
+    if (rows * fp.n_dtiles >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;
+    return launch_fused_fwd_fma(fp, p->dtype, vec, st);
+}
+
+extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const float *decay, const void *dy,
+                            const float *tile_states, void *dx, float *ddecay, const float *dfinal_state,
+                            float *dinit_state, float stop_below, void *workspace, size_t workspace_bytes,
+                            void *stream) {
+    int rc = check_problem(p);
+    if (rc) return rc;
+    if (!x || !decay || !dy || !dx || !ddecay || !tile_states) return EMA_ERR_BADARG;
+    if (!(stop_below >= 0.f)) return EMA_ERR_BADARG;
+    const size_t es = p->dtype == EMA_F32 ? 4 : 2;
+    if (!aligned(x, es) || !aligned(dy, es) || !aligned(dx, es) || !aligned(decay, 4) || !aligned(ddecay, 4))
+        return EMA_ERR_ALIGN;
+    if (!workspace || workspace_bytes < ema_b200_bwd_workspace_bytes(p)) return EMA_ERR_WORKSPACE;
+    if (!aligned(workspace, 16)) return EMA_ERR_ALIGN;
+    auto st = static_cast<cudaStream_t>(stream);
+    const int64_t rows = p->b * p->h;
+    if (rows == 0) return EMA_OK;
+    if (p->L == 0 || p->d == 0) {
+        cudaError_t e = cudaSuccess;
+        if (p->decay_mode == EMA_DECAY_PER_HEAD) {
+            // ddecay[h] may be strided: clear element by element through a 2-D memset
+            e = cudaMemset2DAsync(ddecay, static_cast<size_t>(p->a_sh > 0 ? p->a_sh : 1) * 4, 0, 4,
+                                  static_cast<size_t>(p->h), st);
+        }
+        if (e == cudaSuccess && dinit_state && p->d > 0) {
+            e = dfinal_state ? cudaMemcpyAsync(dinit_state, dfinal_state, rows * p->d * 4, cudaMemcpyDeviceToDevice, st)
+                             : cudaMemsetAsync(dinit_state, 0, rows * p->d * 4, st);
+        }
+        if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
+        return EMA_OK;
+    }
+    const int vec = pick_vec(p, x, dx, dy);
+    FusedParams fp;
+    fill_params(fp, p, vec);
+    fp.x = x; fp.decay = decay; fp.dy = dy; fp.out = dx;
+    fp.tile_states = const_cast<float *>(tile_states);
+    fp.dfinal_state = dfinal_state; fp.dinit_state = dinit_state;
+    fp.da_partial = static_cast<float *>(workspace);
+    fp.stop_below = stop_below;
+    if (rows * fp.n_dtiles >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;
+    rc = launch_fused_bwd_fma(fp, p->dtype, vec, st);
+    if (rc) return rc;
+    return launch_da_reduce(fp, ddecay, kFmaTile, st);
+}

@@ -1,0 +1,162 @@
+// Shared device/host helpers for the EMA kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ema_b200.h"
+
+namespace ema {
+
+// Everything a fused launch needs.  Strides are in elements, as in ema_b200_problem.
+struct FusedParams {
+    const void *x;
+    const float *decay;
+    const void *dy;
+    void *out;  // y (forward) or dx (backward)
+    float *chunk_states;
+    float *tile_states;
+    const float *init_state;
+    float *final_state;
+    float *log_decay_sum;
+    const float *dfinal_state;
+    float *dinit_state;
+    float *da_partial;
+    int64_t b, L, h, d;
+    int64_t x_sb, x_sl, x_sh;
+    int64_t o_sb, o_sl, o_sh;
+    int64_t g_sb, g_sl, g_sh;
+    int64_t a_sb, a_sl, a_sh;
+    int decay_mode, convention, chunk;
+    int n_tiles, n_dtiles;
+    int64_t n_chunks;
+    float stop_below;
+};
+
+// ---- raw vector types: VEC elements of T moved by one load/store instruction ----------------
+template <int BYTES> struct RawT;
+template <> struct RawT<16> { using type = uint4; };
+template <> struct RawT<8> { using type = uint2; };
+template <> struct RawT<4> { using type = uint32_t; };
+template <> struct RawT<2> { using type = unsigned short; };
+
+template <typename T, int VEC> using raw_t = typename RawT<sizeof(T) * VEC>::type;
+
+template <typename T, int VEC>
+__device__ __forceinline__ raw_t<T, VEC> raw_zero() {
+    raw_t<T, VEC> r;
+    if constexpr (sizeof(T) * VEC == 16) r = make_uint4(0u, 0u, 0u, 0u);
+    else if constexpr (sizeof(T) * VEC == 8) r = make_uint2(0u, 0u);
+    else r = 0;
+    return r;
+}
+
+// streaming (evict-first) load/store: every big tensor is touched exactly once per pass
+template <typename T, int VEC>
+__device__ __forceinline__ raw_t<T, VEC> ld_stream(const T *p) {
+    return __ldcs(reinterpret_cast<const raw_t<T, VEC> *>(p));
+}
+template <typename T, int VEC>
+__device__ __forceinline__ void st_stream(T *p, const raw_t<T, VEC> &r) {
+    __stcs(reinterpret_cast<raw_t<T, VEC> *>(p), r);
+}
+
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ void unpack(const raw_t<T, VEC> &r, float (&f)[VEC]) {
+    if constexpr (sizeof(T) == 4) {
+        if constexpr (VEC == 4) {
+            f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y);
+            f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
+        } else {
+            static_assert(VEC == 1, "fp32 vectors are 1 or 4 wide");
+            f[0] = __uint_as_float(r);
+        }
+    } else {
+        if constexpr (VEC == 8) {
+            f[0] = bf16lo(r.x); f[1] = bf16hi(r.x); f[2] = bf16lo(r.y); f[3] = bf16hi(r.y);
+            f[4] = bf16lo(r.z); f[5] = bf16hi(r.z); f[6] = bf16lo(r.w); f[7] = bf16hi(r.w);
+        } else if constexpr (VEC == 4) {
+            f[0] = bf16lo(r.x); f[1] = bf16hi(r.x); f[2] = bf16lo(r.y); f[3] = bf16hi(r.y);
+        } else {
+            static_assert(VEC == 1, "bf16 vectors are 1, 4 or 8 wide");
+            f[0] = __uint_as_float(static_cast<uint32_t>(r) << 16);
+        }
+    }
+}
+
+template <typename T, int VEC>
+__device__ __forceinline__ raw_t<T, VEC> pack(const float (&f)[VEC]) {
+    raw_t<T, VEC> r;
+    if constexpr (sizeof(T) == 4) {
+        if constexpr (VEC == 4) {
+            r = make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]),
+                           __float_as_uint(f[3]));
+        } else {
+            r = __float_as_uint(f[0]);
+        }
+    } else {
+        if constexpr (VEC == 8) {
+            r = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                           pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+        } else if constexpr (VEC == 4) {
+            r = make_uint2(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]));
+        } else {
+            __nv_bfloat16 v = __float2bfloat16_rn(f[0]);
+            r = *reinterpret_cast<unsigned short *>(&v);
+        }
+    }
+    return r;
+}
+
+// scalar element access for the stage kernels
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) {
+    return __bfloat162float(v);
+}
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// decay value -> multiplicative decay a, for either convention; steps past L use a = 1
+__device__ __forceinline__ float decay_to_a(float v, int convention) {
+    return convention == EMA_CONV_PRESCALED_LOG ? __expf(v) : v;
+}
+
+// ---- host side ------------------------------------------------------------------------------
+void set_last_cuda_error(cudaError_t e);
+inline int check_launch() {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_last_cuda_error(e);
+        return EMA_ERR_CUDA;
+    }
+    return EMA_OK;
+}
+
+// geometry of the FMA kernels: 128 threads = NS sub-blocks x CT channel threads
+constexpr int kFmaThreads = 128;
+constexpr int kFmaCT = 16;
+constexpr int kFmaSB = 8;
+constexpr int kFmaNS = kFmaThreads / kFmaCT;
+constexpr int kFmaTile = kFmaNS * kFmaSB;  // 64 time steps per tile
+
+// per-head decay gradient workspace: [rows doubles of row sums][partials], the partials starting
+// at this float offset (kept 16-byte aligned)
+__host__ __device__ inline int64_t kHeadPartialOffset(int64_t rows) { return ((rows * 2 + 3) / 4) * 4; }
+
+int launch_fused_fwd_fma(const FusedParams &p, int dtype, int vec, cudaStream_t stream);
+int launch_fused_bwd_fma(const FusedParams &p, int dtype, int vec, cudaStream_t stream);
+int launch_da_reduce(const FusedParams &p, float *ddecay, int tile_steps, cudaStream_t stream);
+
+}  // namespace ema

@@ -1,0 +1,190 @@
+"""Host side of the fused EMA scan: tensor checks, output allocation, C-ABI calls, autograd.
+
+Layouts follow the reference project's heads-style convention (kernels/ema_combined.py:100:
+x[b, l, h, p] with one decay per (b, l, h) or per head): x[b, L, h, d], decay a[b, L, h] or a[h].
+The reference's folded layout X[B, L, T] with A[B, L] is the same thing with h = 1.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import (CONV_NORTH_STAR, CONV_PRESCALED_LOG, DECAY_PER_HEAD, DECAY_PER_STEP, Problem,
+                   check, dtype_code, lib, ptr, require_cuda, stream_ptr)
+
+
+def _problem(x, decay, out, dy=None, convention=CONV_NORTH_STAR, chunk=0):
+    b, L, h, d = x.shape
+    p = Problem()
+    p.b, p.L, p.h, p.d = b, L, h, d
+    p.x_sb, p.x_sl, p.x_sh = x.stride(0), x.stride(1), x.stride(2)
+    p.y_sb, p.y_sl, p.y_sh = out.stride(0), out.stride(1), out.stride(2)
+    if dy is not None:
+        p.g_sb, p.g_sl, p.g_sh = dy.stride(0), dy.stride(1), dy.stride(2)
+    if decay.dim() == 1:
+        p.decay_mode = DECAY_PER_HEAD
+        p.a_sh = decay.stride(0)
+    else:
+        p.decay_mode = DECAY_PER_STEP
+        p.a_sb, p.a_sl, p.a_sh = decay.stride(0), decay.stride(1), decay.stride(2)
+    p.dtype = dtype_code(x.dtype)
+    p.convention = convention
+    p.chunk = int(chunk)
+    return p
+
+
+def _check_inputs(x, decay):
+    if x.dim() != 4:
+        raise ValueError(f"x must be [b, L, h, d], got shape {tuple(x.shape)}")
+    b, L, h, d = x.shape
+    if decay.dim() == 1:
+        if decay.shape[0] != h:
+            raise ValueError(f"per-head decay must have shape [{h}], got {tuple(decay.shape)}")
+    elif tuple(decay.shape) != (b, L, h):
+        raise ValueError(f"decay must be [b, L, h] = {(b, L, h)} or [h], got {tuple(decay.shape)}")
+    if x.stride(-1) != 1 and d > 1:
+        x = x.contiguous()
+    if decay.dtype != torch.float32:
+        decay = decay.float()
+    return x, decay
+
+
+def n_tiles_of(x, decay, convention=CONV_NORTH_STAR):
+    """(tile_steps, n_tiles) the library uses for this problem."""
+    p = _problem(x, decay, x, convention=convention)
+    ts = lib().ema_b200_tile_steps(ctypes.byref(p))
+    if ts <= 0:
+        raise _lib.EmaB200Error("ema_b200_tile_steps", -3, "unsupported problem")
+    return ts, (x.shape[1] + ts - 1) // ts
+
+
+def ema_fwd(x, decay, *, chunk=0, prescaled_log=False, init_state=None, want_chunk_states=False,
+            want_tile_states=False, want_final=False, want_log_decay_sum=False, stop_below=0.0,
+            out=None, tile_states=None):
+    """Forward scan.  Returns a dict with 'y' and the requested extras.
+
+    x[b,L,h,d] (fp32|bf16, last dim contiguous), decay a[b,L,h] or a[h] (fp32).
+    prescaled_log=True selects the reference's (A_ema, X_ema) convention: decay = log a, x = (1-a) x.
+    `out` / `tile_states` let a caller re-scan a prefix in place (sequence-parallel fix-up).
+    """
+    x, decay = _check_inputs(x, decay)
+    dev = require_cuda(x, decay, init_state, out, tile_states)
+    b, L, h, d = x.shape
+    conv = CONV_PRESCALED_LOG if prescaled_log else CONV_NORTH_STAR
+    y = out if out is not None else torch.empty((b, L, h, d), dtype=x.dtype, device=dev)
+    p = _problem(x, decay, y, convention=conv, chunk=chunk)
+    L_ = lib()
+    res = {"y": y}
+    cs = ts = fin = lds = None
+    if want_chunk_states:
+        if chunk <= 0:
+            raise ValueError("chunk must be positive to return chunk states")
+        cs = torch.empty((b, h, (L + chunk - 1) // chunk, d), dtype=torch.float32, device=dev)
+        res["chunk_states"] = cs
+    if want_tile_states or tile_states is not None:
+        tsteps = L_.ema_b200_tile_steps(ctypes.byref(p))
+        nt = (L + tsteps - 1) // tsteps if tsteps > 0 else 0
+        ts = tile_states if tile_states is not None else torch.empty((b * h, nt, d), dtype=torch.float32, device=dev)
+        res["tile_states"] = ts
+    if want_final:
+        fin = torch.empty((b, h, d), dtype=torch.float32, device=dev)
+        res["final_state"] = fin
+    if want_log_decay_sum:
+        lds = torch.zeros((b, h), dtype=torch.float32, device=dev)
+        res["log_decay_sum"] = lds
+    if init_state is not None:
+        if tuple(init_state.shape) != (b, h, d) or init_state.dtype != torch.float32:
+            raise ValueError("init_state must be fp32 [b, h, d]")
+        init_state = init_state.contiguous()
+    with torch.cuda.device(dev):
+        rc = L_.ema_b200_fwd(ctypes.byref(p), ptr(x), ptr(decay), ptr(y), ptr(cs), ptr(ts), ptr(init_state),
+                             ptr(fin), ptr(lds), ctypes.c_float(stop_below), stream_ptr(dev))
+    check("ema_b200_fwd", rc)
+    return res
+
+
+def ema_bwd(x, decay, dy, tile_states, *, prescaled_log=False, dfinal_state=None, want_dinit=False,
+            stop_below=0.0, dx=None, workspace=None, ddecay=None):
+    """Backward scan.  Returns a dict with 'dx', 'ddecay' (shaped like decay) and optionally 'dinit_state'.
+
+    `dx`, `workspace`, `ddecay` let a caller re-scan a suffix in place (sequence-parallel fix-up):
+    the workspace keeps the partial sums of the first pass, so it must be the same tensor.
+    """
+    x, decay = _check_inputs(x, decay)
+    if dy.shape != x.shape or dy.dtype != x.dtype:
+        raise ValueError("dy must match x in shape and dtype")
+    if dy.stride(-1) != 1 and dy.shape[-1] > 1:
+        dy = dy.contiguous()
+    decay = decay.contiguous()
+    dev = require_cuda(x, decay, dy, tile_states, dfinal_state)
+    b, L, h, d = x.shape
+    conv = CONV_PRESCALED_LOG if prescaled_log else CONV_NORTH_STAR
+    if dx is None:
+        dx = torch.empty((b, L, h, d), dtype=x.dtype, device=dev)
+    if ddecay is None:
+        ddecay = torch.empty_like(decay)
+    p = _problem(x, decay, dx, dy=dy, convention=conv)
+    L_ = lib()
+    nbytes = L_.ema_b200_bwd_workspace_bytes(ctypes.byref(p))
+    if workspace is None:
+        workspace = torch.empty(((nbytes + 3) // 4,), dtype=torch.float32, device=dev)
+    dinit = torch.empty((b, h, d), dtype=torch.float32, device=dev) if want_dinit else None
+    if dfinal_state is not None:
+        if tuple(dfinal_state.shape) != (b, h, d) or dfinal_state.dtype != torch.float32:
+            raise ValueError("dfinal_state must be fp32 [b, h, d]")
+        dfinal_state = dfinal_state.contiguous()
+    with torch.cuda.device(dev):
+        rc = L_.ema_b200_bwd(ctypes.byref(p), ptr(x), ptr(decay), ptr(dy), ptr(tile_states), ptr(dx),
+                             ptr(ddecay), ptr(dfinal_state), ptr(dinit), ctypes.c_float(stop_below),
+                             ptr(workspace), ctypes.c_size_t(workspace.numel() * 4), stream_ptr(dev))
+    check("ema_b200_bwd", rc)
+    res = {"dx": dx, "ddecay": ddecay, "workspace": workspace}
+    if want_dinit:
+        res["dinit_state"] = dinit
+    return res
+
+
+class EmaFunction(torch.autograd.Function):
+    """y_t = a_t y_{t-1} + (1 - a_t) x_t with gradients for x and a."""
+
+    @staticmethod
+    def forward(ctx, x, a):
+        r = ema_fwd(x, a, want_tile_states=True)
+        ctx.save_for_backward(x, a, r["tile_states"])
+        return r["y"]
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, a, tile_states = ctx.saved_tensors
+        r = ema_bwd(x, a, dy, tile_states)
+        da = r["ddecay"]
+        return r["dx"], (da.to(a.dtype) if da.dtype != a.dtype else da)
+
+
+def ema(x, a):
+    """EMA over the sequence axis of x[b, L, h, d] with decay a[b, L, h] or a[h]; differentiable."""
+    return EmaFunction.apply(x, a)
+
+
+# ---- the reference's folded layout ------------------------------------------------------------
+
+def ema_scan_folded_fwd(A, X, chunk_size, want_states=True):
+    """(out[B,L,T], chunk_start_states[B,C,T] fp32, final[B,T] fp32) for A[B,L] = log a, X[B,L,T] = u.
+
+    Same quantities as _ema_matmul_scan_combined_fwd (kernels/ema_kernels/ema_combined_fwd.py:12-47).
+    """
+    if X.dim() != 3 or A.dim() != 2 or A.shape != X.shape[:2]:
+        raise ValueError(f"expected X[B,L,T] and A[B,L], got {tuple(X.shape)} and {tuple(A.shape)}")
+    r = ema_fwd(X.unsqueeze(2), A.unsqueeze(2), chunk=chunk_size, prescaled_log=True,
+                want_chunk_states=want_states, want_final=True)
+    states = r["chunk_states"].squeeze(1) if want_states else None
+    return r["y"].squeeze(2), states, r["final_state"].squeeze(1)
+
+
+def ema_scan_folded_bwd(dout, X, A, want_out=False):
+    """(dX[B,L,T], dA[B,L] fp32[, out]) for the folded layout; the forward states are recomputed."""
+    X4, A4 = X.unsqueeze(2), A.unsqueeze(2)
+    f = ema_fwd(X4, A4, prescaled_log=True, want_tile_states=True)
+    r = ema_bwd(X4, A4, dout.unsqueeze(2), f["tile_states"], prescaled_log=True)
+    res = (r["dx"].squeeze(2), r["ddecay"].squeeze(2))
+    return res + (f["y"].squeeze(2),) if want_out else res

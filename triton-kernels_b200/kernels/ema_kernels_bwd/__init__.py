@@ -1,0 +1,1 @@
+"""Backward stages of the chunked EMA (reference: kernels/ema_kernels_bwd/)."""
