@@ -79,6 +79,16 @@ int ema_b200_version(void);
 int ema_b200_last_cuda_error(void);
 const char *ema_b200_error_string(int code);
 
+/* Status word the tensor-core kernels write when a bounded device-side wait runs out: EMA_OK or
+ * EMA_ERR_TIMEOUT.  Synchronises the device; clear != 0 resets the word.  Kernels never trap or spin
+ * forever: after a timeout they finish their loops without waiting and the call's results are void. */
+int ema_b200_device_status(int clear);
+
+/* Which kernels bf16 problems run on: 0 = tensor-core path wherever the layout allows it (default),
+ * 1 = CUDA-core path only.  fp32 problems always take the CUDA-core path (exactness).  Meant for A/B
+ * measurements and tests; the environment variable EMA_B200_PATH=fma sets the same switch at load. */
+int ema_b200_set_path(int path);
+
 /* Number of time steps one internal tile covers for this problem.  The forward writes one saved
  * state per tile and the backward consumes them, so both report the same value for the same
  * (dtype, d, strides).  n_tiles = ceil(L / tile_steps). */

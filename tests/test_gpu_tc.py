@@ -1,0 +1,105 @@
+"""The tensor-core (tcgen05 + TMA) path for bf16 problems: against the CPU oracle, against the
+CUDA-core path on the same inputs, and the device status word (no bounded wait may run out)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_close_bf16, make_inputs, oracle_fwd_bwd
+from oracle import ema_oracle as eo
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _lib(ema_lib):
+    assert torch.cuda.is_available()
+    ema_lib.ema_b200_set_path(0)
+    yield ema_lib
+    ema_lib.ema_b200_set_path(0)
+    assert ema_lib.ema_b200_device_status(1) == 0, "a device-side wait timed out during these tests"
+
+
+def _E():
+    import ema_b200
+    return ema_b200
+
+
+TC_SHAPES = [
+    (1, 128, 1, 64),     # exactly one tile, one item
+    (1, 40, 1, 8),       # a fraction of a tile, d far below the 64-channel box
+    (2, 129, 2, 24),     # ragged by one step, d not a multiple of 64
+    (1, 640, 3, 128),    # several tiles, several channel tiles, three heads
+    (5, 300, 2, 1024),   # 160 work items: every CTA walks two of them
+    (2, 1111, 4, 256),
+]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+@pytest.mark.parametrize("per_head", [False, True])
+def test_tc_forward_matches_oracle(shape, per_head, _lib):
+    b, L, h, d = shape
+    x, a, dy, np_in = make_inputs(500 + L + d, b, L, h, d, per_head=per_head, dtype=torch.bfloat16)
+    y_ref = eo.fwd(np_in[0], np_in[1], acc64=True)
+    r = _E().ema_fwd(x, a, want_final=True)
+    assert_close_bf16(r["y"], y_ref, "y")
+    assert_close_bf16(r["final_state"], np.ascontiguousarray(y_ref[:, -1]), "final state", rel=1e-2)
+    assert _lib.ema_b200_device_status(1) == 0
+
+
+@pytest.mark.parametrize("per_head", [False, True])
+def test_tc_equals_fma_path(per_head, _lib):
+    """Same inputs through both kernel families: bf16 outputs agree to bf16 rounding, fp32 side
+    outputs (saved states, final state, log-decay sum) to 2e-3 of their scale."""
+    E = _E()
+    b, L, h, d = 2, 700, 2, 192
+    x, a, _, _ = make_inputs(77, b, L, h, d, per_head=per_head, dtype=torch.bfloat16)
+    init = torch.randn(b, h, d, device="cuda")
+    kw = dict(chunk=100, want_chunk_states=True, want_tile_states=True, want_final=True,
+              want_log_decay_sum=True, init_state=init)
+    _lib.ema_b200_set_path(1)
+    f = E.ema_fwd(x, a, **kw)
+    _lib.ema_b200_set_path(0)
+    t = E.ema_fwd(x, a, **kw)
+    for key, rel in (("y", 1.6e-2), ("chunk_states", 2e-3), ("tile_states", 2e-3), ("final_state", 2e-3),
+                     ("log_decay_sum", 1e-4)):
+        ref = f[key].float().cpu().numpy()
+        assert_close_bf16(t[key], ref, key, rel=rel)
+    assert _lib.ema_b200_device_status(1) == 0
+
+
+def test_tc_prescaled_log_convention(_lib):
+    E = _E()
+    b, L, h, d = 2, 300, 1, 64
+    rs = np.random.RandomState(5)
+    A = (-0.05 * rs.random_sample((b, L, h))).astype(np.float32)
+    U = torch.tensor(rs.standard_normal((b, L, h, d)).astype(np.float32)).to(torch.bfloat16)
+    y_ref = eo.fwd(U.float().numpy(), A, convention=eo.REFERENCE, acc64=True)
+    r = E.ema_fwd(U.cuda(), torch.tensor(A).cuda(), prescaled_log=True)
+    assert_close_bf16(r["y"], y_ref, "y")
+
+
+def test_tc_forward_feeds_backward(_lib):
+    """States saved by the tensor-core forward drive the backward (dx, da against the oracle)."""
+    b, L, h, d = 2, 520, 2, 128
+    for per_head in (False, True):
+        x, a, dy, np_in = make_inputs(91, b, L, h, d, per_head=per_head, dtype=torch.bfloat16)
+        y_ref, dx_ref, da_ref = oracle_fwd_bwd(np_in)
+        x.requires_grad_(True)
+        a.requires_grad_(True)
+        y = _E().ema(x, a)
+        y.backward(dy)
+        assert_close_bf16(y, y_ref, "y")
+        assert_close_bf16(x.grad, dx_ref, "dx")
+        assert_close_bf16(a.grad, da_ref, "da")
+    assert _lib.ema_b200_device_status(1) == 0
+
+
+def test_tc_strided_views(_lib):
+    """[b,h,L,d] storage viewed as [b,L,h,d]: the tensor map carries the strides, no copy is made."""
+    E = _E()
+    b, L, h, d = 2, 260, 2, 64
+    xs = torch.randn(b, h, L, d, device="cuda").to(torch.bfloat16).permute(0, 2, 1, 3)
+    a = torch.sigmoid(2 + 4 * torch.rand(b, L, h, device="cuda"))
+    y1 = E.ema_fwd(xs, a)["y"]
+    y2 = E.ema_fwd(xs.contiguous(), a)["y"]
+    assert torch.equal(y1, y2)

@@ -1,6 +1,7 @@
 // C-ABI entry points of the fused path: argument checks, kernel selection, launches.
 #include "ema_common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace ema {
@@ -33,6 +34,17 @@ int pick_vec(const ema_b200_problem *p, const void *x, const void *out, const vo
     ok = ok && aligned(x, 4 * es) && aligned(out, 4 * es);
     if (dy) ok = ok && strides_ok(p->g_sb, p->g_sl, p->g_sh) && aligned(dy, 4 * es);
     return ok ? 4 : 1;
+}
+
+// Kernel family for bf16 problems: 0 = tensor cores where the layout allows (default), 1 = CUDA cores
+// only.  Set by ema_b200_set_path or, once, by the environment variable EMA_B200_PATH=fma.
+int g_path = -1;
+bool tc_enabled() {
+    if (g_path < 0) {
+        const char *e = std::getenv("EMA_B200_PATH");
+        g_path = (e && std::strcmp(e, "fma") == 0) ? 1 : 0;
+    }
+    return g_path == 0;
 }
 
 void fill_params(FusedParams &fp, const ema_b200_problem *p, int vec) {
@@ -73,6 +85,14 @@ extern "C" const char *ema_b200_error_string(int code) {
     }
 }
 
+extern "C" int ema_b200_device_status(int clear) { return read_tc_status(clear); }
+
+extern "C" int ema_b200_set_path(int path) {
+    if (path != 0 && path != 1) return EMA_ERR_BADARG;
+    g_path = path;
+    return EMA_OK;
+}
+
 extern "C" int ema_b200_tile_steps(const ema_b200_problem *p) {
     if (check_problem(p) != EMA_OK) return 0;
     return kFmaTile;
@@ -101,15 +121,17 @@ extern "C" int ema_b200_fwd(const ema_b200_problem *p, const void *x, const floa
                             float *final_state, float *log_decay_sum, float stop_below, void *stream) {
     int rc = check_problem(p);
     if (rc) return rc;
-    if (!x || !decay) return EMA_ERR_BADARG;
-    if (!y && !chunk_states && !tile_states && !final_state) return EMA_ERR_BADARG;
     if (chunk_states && p->chunk <= 0) return EMA_ERR_BADARG;
     if (!(stop_below >= 0.f)) return EMA_ERR_BADARG;
     const size_t es = p->dtype == EMA_F32 ? 4 : 2;
     if (!aligned(x, es) || !aligned(y, es) || !aligned(decay, 4)) return EMA_ERR_ALIGN;
     auto st = static_cast<cudaStream_t>(stream);
     const int64_t rows = p->b * p->h;
-    if (rows == 0 || p->d == 0) return EMA_OK;
+    if (rows == 0 || p->d == 0) return EMA_OK;  // empty tensors carry null pointers: nothing to do
+    if (p->L > 0) {
+        if (!x || !decay) return EMA_ERR_BADARG;
+        if (!y && !chunk_states && !tile_states && !final_state) return EMA_ERR_BADARG;
+    }
     if (p->L == 0) {
         // nothing to scan: the state passes through
         cudaError_t e = cudaSuccess;
@@ -130,6 +152,12 @@ extern "C" int ema_b200_fwd(const ema_b200_problem *p, const void *x, const floa
     fp.log_decay_sum = log_decay_sum;
     fp.stop_below = stop_below;
     if (rows * fp.n_dtiles >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;
+    if (p->dtype == EMA_BF16 && y && stop_below == 0.f && tc_enabled() &&
+        tc_tensor_ok(x, p->d, p->x_sb, p->x_sl, p->x_sh, p->b, p->L, p->h) &&
+        tc_tensor_ok(y, p->d, p->y_sb, p->y_sl, p->y_sh, p->b, p->L, p->h)) {
+        rc = launch_fused_fwd_tc(fp, st);
+        if (rc != EMA_ERR_UNSUPPORTED) return rc;  // a tensor map the driver refuses falls through to the FMA path
+    }
     return launch_fused_fwd_fma(fp, p->dtype, vec, st);
 }
 
@@ -139,7 +167,8 @@ extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const floa
                             void *stream) {
     int rc = check_problem(p);
     if (rc) return rc;
-    if (!x || !decay || !dy || !dx || !ddecay || !tile_states) return EMA_ERR_BADARG;
+    const bool empty = p->b * p->h == 0 || p->L == 0 || p->d == 0;
+    if (!empty && (!x || !decay || !dy || !dx || !ddecay || !tile_states)) return EMA_ERR_BADARG;
     if (!(stop_below >= 0.f)) return EMA_ERR_BADARG;
     const size_t es = p->dtype == EMA_F32 ? 4 : 2;
     if (!aligned(x, es) || !aligned(dy, es) || !aligned(dx, es) || !aligned(decay, 4) || !aligned(ddecay, 4))
@@ -151,7 +180,7 @@ extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const floa
     if (rows == 0) return EMA_OK;
     if (p->L == 0 || p->d == 0) {
         cudaError_t e = cudaSuccess;
-        if (p->decay_mode == EMA_DECAY_PER_HEAD) {
+        if (p->decay_mode == EMA_DECAY_PER_HEAD && ddecay) {
             // ddecay[h] may be strided: clear element by element through a 2-D memset
             e = cudaMemset2DAsync(ddecay, static_cast<size_t>(p->a_sh > 0 ? p->a_sh : 1) * 4, 0, 4,
                                   static_cast<size_t>(p->h), st);

@@ -51,6 +51,8 @@ def lib():
         "ema_b200_version": (ci, []),
         "ema_b200_last_cuda_error": (ci, []),
         "ema_b200_error_string": (ctypes.c_char_p, [ci]),
+        "ema_b200_device_status": (ci, [ci]),
+        "ema_b200_set_path": (ci, [ci]),
         "ema_b200_tile_steps": (ci, [pp]),
         "ema_b200_tile_states_bytes": (sz, [pp]),
         "ema_b200_bwd_workspace_bytes": (sz, [pp]),
