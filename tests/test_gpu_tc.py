@@ -49,7 +49,8 @@ def test_tc_forward_matches_oracle(shape, per_head, _lib):
 @pytest.mark.parametrize("per_head", [False, True])
 def test_tc_equals_fma_path(per_head, _lib):
     """Same inputs through both kernel families: bf16 outputs agree to bf16 rounding, fp32 side
-    outputs (saved states, final state, log-decay sum) to 2e-3 of their scale."""
+    outputs (saved states, final state, log-decay sum) to 5e-3 of their scale: the tensor-core path
+    rounds the decay matrix to bf16 (8 mantissa bits), the CUDA-core path keeps decays in fp32."""
     E = _E()
     b, L, h, d = 2, 700, 2, 192
     x, a, _, _ = make_inputs(77, b, L, h, d, per_head=per_head, dtype=torch.bfloat16)
@@ -60,7 +61,7 @@ def test_tc_equals_fma_path(per_head, _lib):
     f = E.ema_fwd(x, a, **kw)
     _lib.ema_b200_set_path(0)
     t = E.ema_fwd(x, a, **kw)
-    for key, rel in (("y", 1.6e-2), ("chunk_states", 2e-3), ("tile_states", 2e-3), ("final_state", 2e-3),
+    for key, rel in (("y", 1.6e-2), ("chunk_states", 5e-3), ("tile_states", 5e-3), ("final_state", 5e-3),
                      ("log_decay_sum", 1e-4)):
         ref = f[key].float().cpu().numpy()
         assert_close_bf16(t[key], ref, key, rel=rel)
