@@ -104,3 +104,38 @@ def test_tc_strided_views(_lib):
     y1 = E.ema_fwd(xs, a)["y"]
     y2 = E.ema_fwd(xs.contiguous(), a)["y"]
     assert torch.equal(y1, y2)
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+@pytest.mark.parametrize("per_head", [False, True])
+def test_tc_backward_matches_oracle(shape, per_head, _lib):
+    b, L, h, d = shape
+    x, a, dy, np_in = make_inputs(900 + L + d, b, L, h, d, per_head=per_head, dtype=torch.bfloat16)
+    _, dx_ref, da_ref = oracle_fwd_bwd(np_in)
+    E = _E()
+    f = E.ema_fwd(x, a, want_tile_states=True)
+    g = E.ema_bwd(x, a, dy, f["tile_states"])
+    assert_close_bf16(g["dx"], dx_ref, "dx")
+    assert_close_bf16(g["ddecay"], da_ref, "da")
+    assert _lib.ema_b200_device_status(1) == 0
+
+
+@pytest.mark.parametrize("per_head", [False, True])
+@pytest.mark.parametrize("prescaled", [False, True])
+def test_tc_backward_equals_fma_path(per_head, prescaled, _lib):
+    """Both kernel families on the same inputs and the same saved states, including the adjoint entering
+    from the right (dfinal) and the one leaving on the left (dinit)."""
+    E = _E()
+    b, L, h, d = 2, 450, 2, 192
+    x, a, dy, _ = make_inputs(78, b, L, h, d, per_head=per_head, dtype=torch.bfloat16)
+    if prescaled:
+        a = torch.log(a)
+    dfin = torch.randn(b, h, d, device="cuda")
+    _lib.ema_b200_set_path(1)
+    f = E.ema_fwd(x, a, want_tile_states=True, prescaled_log=prescaled)
+    gf = E.ema_bwd(x, a, dy, f["tile_states"], dfinal_state=dfin, want_dinit=True, prescaled_log=prescaled)
+    _lib.ema_b200_set_path(0)
+    gt = E.ema_bwd(x, a, dy, f["tile_states"], dfinal_state=dfin, want_dinit=True, prescaled_log=prescaled)
+    for key, rel in (("dx", 1.6e-2), ("ddecay", 5e-3), ("dinit_state", 5e-3)):
+        assert_close_bf16(gt[key], gf[key].float().cpu().numpy(), key, rel=rel)
+    assert _lib.ema_b200_device_status(1) == 0

@@ -201,7 +201,19 @@ extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const floa
     fp.da_partial = static_cast<float *>(workspace);
     fp.stop_below = stop_below;
     if (rows * fp.n_dtiles >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;
-    rc = launch_fused_bwd_fma(fp, p->dtype, vec, st);
-    if (rc) return rc;
+    bool done = false;
+    if (p->dtype == EMA_BF16 && stop_below == 0.f && tc_enabled() && vec == 4 &&
+        tc_tensor_ok(x, p->d, p->x_sb, p->x_sl, p->x_sh, p->b, p->L, p->h) &&
+        tc_tensor_ok(dy, p->d, p->g_sb, p->g_sl, p->g_sh, p->b, p->L, p->h) &&
+        tc_tensor_ok(dx, p->d, p->y_sb, p->y_sl, p->y_sh, p->b, p->L, p->h)) {
+        // same partial-sum layout as the CUDA-core kernel at vec = 4 (64-channel tiles, 64-step slots)
+        rc = launch_fused_bwd_tc(fp, st);
+        if (rc && rc != EMA_ERR_UNSUPPORTED) return rc;
+        done = rc == EMA_OK;
+    }
+    if (!done) {
+        rc = launch_fused_bwd_fma(fp, p->dtype, vec, st);
+        if (rc) return rc;
+    }
     return launch_da_reduce(fp, ddecay, kFmaTile, st);
 }

@@ -162,6 +162,7 @@ int launch_da_reduce(const FusedParams &p, float *ddecay, int tile_steps, cudaSt
 // tensor-core path (bf16): eligibility of one [b,L,h,d] tensor for TMA, launches, device status word
 bool tc_tensor_ok(const void *base, int64_t d, int64_t sb, int64_t sl, int64_t sh, int64_t b, int64_t L, int64_t h);
 int launch_fused_fwd_tc(const FusedParams &p, cudaStream_t stream);
+int launch_fused_bwd_tc(const FusedParams &p, cudaStream_t stream);
 int read_tc_status(int clear);
 
 }  // namespace ema

@@ -387,6 +387,369 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------------------------
+// Per tile (walked from the end of the sequence to its start), with h the saved state entering the tile
+// and g the adjoint entering it from the right:
+//     Z = A1 X  + Eprev h^T      Z_m = y_{m-1} - x_m  (north-star) or y_{m-1} (pre-scaled)
+//     Lam = U dY + F g^T         Lam_m = lambda_m
+// A1[m,k] = p_k prod_{j=k+1..m-1} a_j (k < m), A1[m,m] = -1 | 0;  U[m,k] = prod_{j=m+1..k} a_j (k >= m);
+// Eprev_m = prod_{j<m} a_j;  F_m = prod_{j=m+1..128} a_j (a_128 = first decay of the next tile, 1 past L).
+// Then dx_m = p_m Lam_m, ddecay_m = sum_c Lam_mc Z_mc (times a_m for the log-decay convention), and row 0
+// of Lam is the adjoint handed to the previous tile.
+
+// Upper-triangular row r of U, left to right from the diagonal; returns prod_{j=r+1..127} a_j.
+__device__ __forceinline__ float build_upper_row(uint8_t *mat, int r, const float *a_sm) {
+    float run = 1.f;
+    for (int c = 0; c < QT / 8; ++c) {
+        if (c < (r >> 3)) continue;
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int k = c * 8 + e;
+            float val = 0.f;
+            if (k == r) {
+                val = 1.f;
+            } else if (k > r) {
+                run *= a_sm[k];
+                val = run;
+            }
+            v[e] = val;
+        }
+        const uint4 q = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                                   pack_bf16x2(v[6], v[7]));
+        *reinterpret_cast<uint4 *>(mat + (c >> 3) * (QT * 128) + sw128_offset(r, c & 7)) = q;
+    }
+    return run;
+}
+
+struct TcBwdParams {
+    const float *decay;
+    const float *tile_states;
+    const float *dfinal_state;
+    float *dinit_state;
+    float *da_partial;
+    int64_t b, L, h, d;
+    int64_t a_sb, a_sl, a_sh;
+    int decay_mode, convention;
+    int n_tiles, n_tiles64, n_dtiles, n_items;
+    int64_t head_partial_offset;
+};
+
+constexpr int kBwdStages = 3;
+struct BwdSmem {
+    static constexpr int mat_a1 = 0;
+    static constexpr int mat_u = mat_a1 + kMatBytes;
+    static constexpr int xg = mat_u + kMatBytes;                       // stages of [x tile | dy tile]
+    static constexpr int ostage = xg + kBwdStages * 2 * kTileBytes;    // dx staging, 2 buffers
+    static constexpr int hs = ostage + 2 * kTileBytes;                 // float[2][64] saved state entering the tile
+    static constexpr int g = hs + 2 * DT * 4;                          // float[2][64] adjoint carry
+    static constexpr int rowsc = g + 2 * DT * 4;                       // float[4][4][128]: Eprev, F, p, a per build
+    static constexpr int a = rowsc + 4 * 4 * QT * 4;                   // float[129]
+    static constexpr int pw = a + (QT + 4) * 4;                        // float[128]
+    static constexpr int bars = pw + QT * 4;
+    static constexpr int n_bars = 2 * kBwdStages + 4 + 2;
+    static constexpr int tmem_slot = bars + n_bars * 8;
+    static constexpr int abort_flag = tmem_slot + 4;
+    static constexpr int total = abort_flag + 4;
+};
+constexpr int kBwdSmemBytes = BwdSmem::total + 1024;
+static_assert(kBwdSmemBytes <= 227 * 1024, "backward shared memory exceeds the per-CTA limit");
+
+__global__ void __launch_bounds__(kThreads, 1)
+ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_g,
+                  const __grid_constant__ CUtensorMap tm_o, const TcBwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t sbase = smem_u32(smem);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool per_step = p.decay_mode == EMA_DECAY_PER_STEP;
+    const int conv = p.convention;
+    const int L = static_cast<int>(p.L);
+
+    float *hs_sm = reinterpret_cast<float *>(smem + BwdSmem::hs);
+    float *g_sm = reinterpret_cast<float *>(smem + BwdSmem::g);
+    float *rowsc = reinterpret_cast<float *>(smem + BwdSmem::rowsc);
+    float *a_sm = reinterpret_cast<float *>(smem + BwdSmem::a);
+    float *p_sm = reinterpret_cast<float *>(smem + BwdSmem::pw);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + BwdSmem::abort_flag);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + BwdSmem::tmem_slot);
+    auto bar = [&](int i) { return sbase + BwdSmem::bars + i * 8; };
+    constexpr int B_FULL = 0, B_EMPTY = kBwdStages, B_ACC_FULL = 2 * kBwdStages, B_ACC_EMPTY = B_ACC_FULL + 2,
+                  B_MAT_FULL = B_ACC_EMPTY + 2, B_MAT_EMPTY = B_MAT_FULL + 1;
+    constexpr uint32_t kTmemCols = 256;  // 2 stages x (Z | Lam) x 64 columns
+
+    if (tid == 0) {
+        for (int i = 0; i < kBwdStages; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), 128); }
+        mbar_init(bar(B_MAT_FULL), 128);
+        mbar_init(bar(B_MAT_EMPTY), 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tmap(&tm_x);
+        prefetch_tmap(&tm_g);
+        prefetch_tmap(&tm_o);
+    }
+    for (int i = tid; i < 2 * kMatBytes / 16; i += kThreads)
+        reinterpret_cast<uint4 *>(smem + BwdSmem::mat_a1)[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (warp == 1) {
+        tmem_alloc(sbase + BwdSmem::tmem_slot, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int64_t n_items = p.n_items;
+    auto decay_a = [&](float v) { return conv ? expf(v) : v; };
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
+                const int dtile = static_cast<int>(item % p.n_dtiles);
+                const int64_t row = item / p.n_dtiles;
+                const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
+                for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
+                    const int s = it % kBwdStages;
+                    const uint32_t ph = (it / kBwdStages) & 1;
+                    if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 11)) break;
+                    mbar_expect_tx(bar(B_FULL + s), 2 * kTileBytes);
+                    const uint32_t dst = sbase + BwdSmem::xg + s * 2 * kTileBytes;
+                    tma_load_4d(dst, &tm_x, bar(B_FULL + s), dtile * DT, hi, k * QT, bi);
+                    tma_load_4d(dst + kTileBytes, &tm_g, bar(B_FULL + s), dtile * DT, hi, k * QT, bi);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            uint32_t it = 0, mt = 0;
+            int cur_head = -1;
+            for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
+                const int hi = static_cast<int>((item / p.n_dtiles) % p.h);
+                for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
+                    const int s = it % kBwdStages;
+                    const uint32_t ph = (it / kBwdStages) & 1;
+                    const int acc = it & 1;
+                    const uint32_t aph = (it >> 1) & 1;
+                    const bool new_mat = per_step || hi != cur_head;
+                    if (new_mat) {
+                        // single matrix buffer: hand it back to the builders once the MMAs issued so far are done
+                        if (!per_step && mt > 0) umma_commit(bar(B_MAT_EMPTY));
+                        if (!mbar_wait(bar(B_MAT_FULL), mt & 1, abort_flag, 12)) break;
+                        cur_head = hi;
+                        ++mt;
+                    }
+                    if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 13)) break;
+                    if (!mbar_wait(bar(B_ACC_EMPTY + acc), aph ^ 1, abort_flag, 14)) break;
+                    tc_fence_after_sync();
+                    const uint32_t x_base = sbase + BwdSmem::xg + s * 2 * kTileBytes;
+                    const uint32_t d_z = tmem_base + acc * 2 * DT, d_l = d_z + DT;
+#pragma unroll
+                    for (int kb = 0; kb < QT / 16; ++kb) {
+                        const uint32_t koff = (kb >> 2) * (QT * 128) + (kb & 3) * 32;
+                        umma_bf16(d_z, make_desc_sw128(sbase + BwdSmem::mat_a1 + koff, 16, 1024),
+                                  make_desc_sw128(x_base + kb * 2048, kTileBytes, 1024), kIdesc, kb > 0 ? 1u : 0u);
+                    }
+#pragma unroll
+                    for (int kb = 0; kb < QT / 16; ++kb) {
+                        const uint32_t koff = (kb >> 2) * (QT * 128) + (kb & 3) * 32;
+                        umma_bf16(d_l, make_desc_sw128(sbase + BwdSmem::mat_u + koff, 16, 1024),
+                                  make_desc_sw128(x_base + kTileBytes + kb * 2048, kTileBytes, 1024), kIdesc,
+                                  kb > 0 ? 1u : 0u);
+                    }
+                    umma_commit(bar(B_EMPTY + s));
+                    umma_commit(bar(B_ACC_FULL + acc));
+                    if (per_step) umma_commit(bar(B_MAT_EMPTY));
+                }
+            }
+        }
+    } else if (tid < kBuildThread0) {
+        // ---------------- epilogue ----------------
+        const int q = warp & 3;
+        const int m = q * 32 + lane;
+        const bool e0 = tid == kEpiThread0;
+        uint32_t it = 0, mt = 0;
+        int cur_head = -1;
+        for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+            const int dtile = static_cast<int>(item % p.n_dtiles);
+            const int64_t row = item / p.n_dtiles;
+            const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
+            const int c0 = dtile * DT;
+            const bool ch_ok = m < DT && c0 + m < p.d;
+            // saved state of the first (rightmost) tile and the adjoint entering the sequence from the right
+            float hs_next = 0.f;
+            if (m < DT) {
+                hs_sm[(it & 1) * DT + m] =
+                    ch_ok ? p.tile_states[(row * p.n_tiles64 + 2 * (p.n_tiles - 1)) * p.d + c0 + m] : 0.f;
+                g_sm[(it & 1) * DT + m] = (p.dfinal_state && ch_ok) ? p.dfinal_state[row * p.d + c0 + m] : 0.f;
+            }
+            bar_sync(1, 128);
+            for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
+                const int acc = it & 1, par = it & 1;
+                const uint32_t aph = (it >> 1) & 1;
+                if (per_step || hi != cur_head) { cur_head = hi; ++mt; }
+                // prefetch the saved state of the next tile to the left while this one is being finished
+                if (m < DT && k > 0)
+                    hs_next = ch_ok ? p.tile_states[(row * p.n_tiles64 + 2 * (k - 1)) * p.d + c0 + m] : 0.f;
+                mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 15);
+                __syncwarp();
+                tc_fence_after_sync();
+                const float *rs = rowsc + ((mt - 1) & 3) * 4 * QT;
+                const float Eprev = rs[m], a_m = rs[3 * QT + m], p_m = rs[2 * QT + m];
+                // F: per-head decays use one Toeplitz table; the rightmost tile of a ragged sequence stops at L
+                float F = rs[QT + m];
+                if (!per_step && k == p.n_tiles - 1) {
+                    const int lim = L - k * QT;  // valid rows in this tile
+                    // prod_{j=m+1..lim-1} a = F_m / a^(128 - lim + 1); recomputed exactly by repeated multiply
+                    float f = 1.f;
+                    for (int j = m + 1; j < lim; ++j) f *= a_m;
+                    F = f;
+                }
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * 2 * DT;
+                const float *hin = hs_sm + par * DT;
+                const float *gin = g_sm + par * DT;
+                const int t = k * QT + m;
+                float dacc = 0.f;
+                uint8_t *stg = smem + BwdSmem::ostage + (it & 1) * kTileBytes;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    float z[32], lam[32];
+                    tmem_ld32(taddr + half * 32, z);
+                    tmem_ld32(taddr + DT + half * 32, lam);
+                    tmem_ld_wait();
+                    if (half == 1) {
+                        tc_fence_before_sync();
+                        mbar_arrive(bar(B_ACC_EMPTY + acc));
+                    }
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        const float4 hv = *reinterpret_cast<const float4 *>(hin + half * 32 + c);
+                        const float4 gv = *reinterpret_cast<const float4 *>(gin + half * 32 + c);
+                        z[c] = fmaf(Eprev, hv.x, z[c]);         lam[c] = fmaf(F, gv.x, lam[c]);
+                        z[c + 1] = fmaf(Eprev, hv.y, z[c + 1]); lam[c + 1] = fmaf(F, gv.y, lam[c + 1]);
+                        z[c + 2] = fmaf(Eprev, hv.z, z[c + 2]); lam[c + 2] = fmaf(F, gv.z, lam[c + 2]);
+                        z[c + 3] = fmaf(Eprev, hv.w, z[c + 3]); lam[c + 3] = fmaf(F, gv.w, lam[c + 3]);
+                    }
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) dacc = fmaf(lam[c], z[c], dacc);
+                    if (m == 0) {
+                        float *gout = g_sm + (par ^ 1) * DT + half * 32;
+#pragma unroll
+                        for (int c = 0; c < 32; c += 4)
+                            *reinterpret_cast<float4 *>(gout + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
+                        if (k == 0 && p.dinit_state) {
+                            float *di = p.dinit_state + row * p.d + c0 + half * 32;
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                if (c0 + half * 32 + c < p.d) di[c] = a_m * lam[c];
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 qv = make_uint4(pack_bf16x2(p_m * lam[8 * j], p_m * lam[8 * j + 1]),
+                                                    pack_bf16x2(p_m * lam[8 * j + 2], p_m * lam[8 * j + 3]),
+                                                    pack_bf16x2(p_m * lam[8 * j + 4], p_m * lam[8 * j + 5]),
+                                                    pack_bf16x2(p_m * lam[8 * j + 6], p_m * lam[8 * j + 7]));
+                        *reinterpret_cast<uint4 *>(stg + sw128_offset(m, half * 4 + j)) = qv;
+                    }
+                }
+                if (conv) dacc *= a_m;
+                if (t >= L) dacc = 0.f;
+                const int64_t blk = row * p.n_dtiles + dtile;
+                if (per_step) {
+                    if (t < L) p.da_partial[blk * (static_cast<int64_t>(p.n_tiles64) * 64) + t] = dacc;
+                } else {
+                    float wsum = dacc;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+                    const int k64 = 2 * k + (q >> 1);
+                    if (lane == 0 && k64 < p.n_tiles64) {
+                        float *dst = p.da_partial + p.head_partial_offset + (blk * p.n_tiles64 + k64) * 4 + (q & 1) * 2;
+                        dst[0] = wsum;
+                        dst[1] = 0.f;
+                    }
+                }
+                if (m < DT) hs_sm[(par ^ 1) * DT + m] = hs_next;
+                fence_proxy_async();
+                if (e0) tma_store_wait_read<0>();
+                bar_sync(1, 128);
+                if (e0) {
+                    tma_store_4d(&tm_o, sbase + BwdSmem::ostage + (it & 1) * kTileBytes, c0, hi, k * QT, bi);
+                    tma_store_commit();
+                }
+            }
+        }
+        if (e0) tma_store_wait_all();
+    } else {
+        // ---------------- matrix builders ----------------
+        const int r = tid - kBuildThread0;
+        uint32_t mt = 0;
+        int cur_head = -1;
+        const float diag = conv ? 0.f : -1.f;
+        auto build = [&](float a_r, float a_edge) {
+            // a_r: decay of step r of the tile; a_edge: decay of the step right after the tile
+            bar_sync(2, 128);
+            a_sm[r] = a_r;
+            p_sm[r] = conv ? 1.f : 1.f - a_r;
+            if (r == 0) a_sm[QT] = a_edge;
+            bar_sync(2, 128);
+            mbar_wait(bar(B_MAT_EMPTY), (mt & 1) ^ 1, abort_flag, 16);
+            const float Eprev = build_lower_row<1>(smem + BwdSmem::mat_a1, r, a_sm, p_sm, diag);
+            const float Fr = build_upper_row(smem + BwdSmem::mat_u, r, a_sm) * a_sm[QT];
+            float *rs = rowsc + (mt & 3) * 4 * QT;
+            rs[r] = Eprev;
+            rs[QT + r] = Fr;
+            rs[2 * QT + r] = p_sm[r];
+            rs[3 * QT + r] = a_r;
+            fence_proxy_async();
+            mbar_arrive(bar(B_MAT_FULL));
+            ++mt;
+        };
+        for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+            const int64_t row = item / p.n_dtiles;
+            const int64_t bi = row / p.h, hi = row % p.h;
+            const float *arow = p.decay + (per_step ? bi * p.a_sb + hi * p.a_sh : hi * p.a_sh);
+            if (!per_step) {
+                if (static_cast<int>(hi) != cur_head) {
+                    cur_head = static_cast<int>(hi);
+                    const float a = decay_a(arow[0]);
+                    build(a, a);
+                }
+                continue;
+            }
+            auto load_a = [&](int t) { return (t >= 0 && t < L) ? decay_a(arow[static_cast<int64_t>(t) * p.a_sl]) : 1.f; };
+            float a_next = load_a((p.n_tiles - 1) * QT + r);
+            float edge_next = 1.f;  // decay of step n_tiles*128 >= L
+            for (int k = p.n_tiles - 1; k >= 0; --k) {
+                const float a = a_next, edge = edge_next;
+                if (k > 0) {
+                    a_next = load_a((k - 1) * QT + r);
+                    edge_next = load_a(k * QT);
+                }
+                build(a, edge);
+            }
+        }
+    }
+
+    // ---------------- teardown ----------------
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
 }  // namespace tc
 
 // ---------------------------------------------------------------------------------------------
@@ -482,6 +845,38 @@ int launch_fused_fwd_tc(const FusedParams &fp, cudaStream_t stream) {
                                          tc::kFwdSmemBytes);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     tc::ema_fwd_tc_kernel<<<grid, tc::kThreads, tc::kFwdSmemBytes, stream>>>(tm_x, tm_y, p);
+    return check_launch();
+}
+
+int launch_fused_bwd_tc(const FusedParams &fp, cudaStream_t stream) {
+    CUtensorMap tm_x, tm_g, tm_o;
+    int rc = make_tmap(&tm_x, fp.x, fp.b, fp.L, fp.h, fp.d, fp.x_sb, fp.x_sl, fp.x_sh);
+    if (rc) return rc;
+    rc = make_tmap(&tm_g, fp.dy, fp.b, fp.L, fp.h, fp.d, fp.g_sb, fp.g_sl, fp.g_sh);
+    if (rc) return rc;
+    rc = make_tmap(&tm_o, fp.out, fp.b, fp.L, fp.h, fp.d, fp.o_sb, fp.o_sl, fp.o_sh);
+    if (rc) return rc;
+    tc::TcBwdParams p;
+    p.decay = fp.decay;
+    p.tile_states = fp.tile_states;
+    p.dfinal_state = fp.dfinal_state;
+    p.dinit_state = fp.dinit_state;
+    p.da_partial = fp.da_partial;
+    p.b = fp.b; p.L = fp.L; p.h = fp.h; p.d = fp.d;
+    p.a_sb = fp.a_sb; p.a_sl = fp.a_sl; p.a_sh = fp.a_sh;
+    p.decay_mode = fp.decay_mode; p.convention = fp.convention;
+    p.n_tiles = static_cast<int>((fp.L + tc::QT - 1) / tc::QT);
+    p.n_tiles64 = fp.n_tiles;
+    p.n_dtiles = static_cast<int>((fp.d + tc::DT - 1) / tc::DT);
+    p.n_items = static_cast<int>(fp.b * fp.h * p.n_dtiles);
+    p.head_partial_offset = kHeadPartialOffset(fp.b * fp.h);
+    const int sms = sm_count();
+    const int rounds = (p.n_items + sms - 1) / sms;
+    const int grid = (p.n_items + rounds - 1) / rounds;
+    cudaError_t e = cudaFuncSetAttribute(tc::ema_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         tc::kBwdSmemBytes);
+    if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
+    tc::ema_bwd_tc_kernel<<<grid, tc::kThreads, tc::kBwdSmemBytes, stream>>>(tm_x, tm_g, tm_o, p);
     return check_launch();
 }
 
