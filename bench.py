@@ -229,6 +229,8 @@ def run_gpu(args):
     # ---- end to end through the public API with host buffers (pinned), copies inside the timing
     e2e = None
     try:
+        if args.no_e2e:
+            raise RuntimeError("skipped (--no-e2e)")
         hx, hdy = x.cpu().pin_memory(), dy.cpu().pin_memory()
         ha = a.cpu().pin_memory()
         hy, hdx = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
@@ -340,6 +342,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 10:

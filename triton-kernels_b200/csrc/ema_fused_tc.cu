@@ -10,8 +10,8 @@
 //
 // One persistent CTA per SM walks its work items (scan row, 64-channel tile) and, inside an item, the
 // tiles in sequence order.  Warp roles:  warp 0 TMA producer;  warp 1 MMA issuer (owns TMEM);
-// warps 2-5 epilogue (one TMEM lane quadrant each);  warps 6-9 build G (once for a time-invariant
-// decay, per tile otherwise, with running products: no exp, no division).
+// warps 2-9 epilogue (a TMEM lane quadrant and one half of the 64 channels each);  warps 10-13 build G
+// (once for a time-invariant decay, per tile otherwise, with running products: no exp, no division).
 // Every wait on an mbarrier is bounded (ema_tc_common.cuh); after a timeout the roles run their
 // loops to the end without waiting, the CTA tears down normally and the host sees EMA_ERR_TIMEOUT.
 #include "ema_common.cuh"
@@ -24,9 +24,10 @@ constexpr int QT = 128;              // steps per tile = MMA M = MMA K extent
 constexpr int DT = 64;               // channels per tile = MMA N
 constexpr int kTileBytes = QT * DT * 2;
 constexpr int kMatBytes = QT * QT * 2;
-constexpr int kThreads = 320;
-constexpr int kEpiThread0 = 64;      // warps 2-5
-constexpr int kBuildThread0 = 192;   // warps 6-9
+constexpr int kThreads = 448;      // 14 warps: TMA, MMA, 8 epilogue, 4 builders
+constexpr int kEpiThread0 = 64;    // warps 2-9
+constexpr int kEpiThreads = 256;
+constexpr int kBuildThread0 = 320;  // warps 10-13
 constexpr uint32_t kIdesc = make_idesc_bf16(QT, DT, 0, 1);
 
 struct TcParams {
@@ -87,7 +88,7 @@ __device__ __forceinline__ float build_lower_row(uint8_t *mat, int r, const floa
 // ---------------------------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------------------------
-constexpr int kFwdStages = 4;
+constexpr int kFwdStages = 7;  // 7 x 16 KB of loads in flight per SM: HBM latency under load is ~3 us
 constexpr int kFwdMatBufs = 2;
 struct FwdSmem {
     static constexpr int mat = 0;
@@ -98,7 +99,8 @@ struct FwdSmem {
     static constexpr int a = e + 4 * QT * 4;                 // float[128]
     static constexpr int pw = a + QT * 4;                    // float[128]
     static constexpr int red = pw + QT * 4;                  // float[4]
-    static constexpr int bars = red + 16;                    // uint64[...]
+    static constexpr int mid = red + 16;                     // float[2][64]: state after row 63
+    static constexpr int bars = mid + 2 * DT * 4;            // uint64[...]
     static constexpr int n_bars = 2 * kFwdStages + 4 + 2 * kFwdMatBufs;
     static constexpr int tmem_slot = bars + n_bars * 8;
     static constexpr int abort_flag = tmem_slot + 4;
@@ -122,6 +124,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     float *a_sm = reinterpret_cast<float *>(smem + FwdSmem::a);
     float *p_sm = reinterpret_cast<float *>(smem + FwdSmem::pw);
     float *red_sm = reinterpret_cast<float *>(smem + FwdSmem::red);
+    float *mid_sm = reinterpret_cast<float *>(smem + FwdSmem::mid);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + FwdSmem::abort_flag);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + FwdSmem::tmem_slot);
     auto bar = [&](int i) { return sbase + FwdSmem::bars + i * 8; };
@@ -131,7 +134,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 
     if (tid == 0) {
         for (int i = 0; i < kFwdStages; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), 128); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiThreads); }
         for (int i = 0; i < kFwdMatBufs; ++i) { mbar_init(bar(B_MAT_FULL + i), 128); mbar_init(bar(B_MAT_EMPTY + i), 1); }
         *abort_flag = 0;
         fence_barrier_init();
@@ -212,8 +215,12 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
     } else if (tid < kBuildThread0) {
         // ---------------- epilogue ----------------
-        const int q = warp & 3;           // TMEM lane quadrant this warp may read
-        const int m = q * 32 + lane;      // row of the tile = TMEM lane
+        // 8 warps: TMEM lane quadrant q = warp % 4 (hardware rule), column half = 0 for warps 2-5, 1 for 6-9.
+        // Thread (q, lane, half) owns row m = 32 q + lane and channels [32 half, 32 half + 32) of the tile.
+        const int q = warp & 3;
+        const int half = (warp - kEpiThread0 / 32) >> 2;
+        const int m = q * 32 + lane;
+        const int cb = half * 32;
         const bool e0 = tid == kEpiThread0;
         uint32_t it = 0, mt = 0;
         int cur_head = -1;
@@ -222,13 +229,13 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const int64_t row = item / p.n_dtiles;
             const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
             const int c0 = dtile * DT;
-            if (m < DT) {
+            if (m < DT && half == 0) {
                 const bool ok = c0 + m < p.d;
                 const float v = (p.init_state && ok) ? p.init_state[row * p.d + c0 + m] : 0.f;
                 h_sm[(it & 1) * DT + m] = v;
                 if (p.chunk_states && ok) p.chunk_states[(row * p.n_chunks) * p.d + c0 + m] = v;
             }
-            bar_sync(1, 128);
+            bar_sync(1, kEpiThreads);
             for (int k = 0; k < p.n_tiles; ++k, ++it) {
                 const int acc = it & 1, par = it & 1;
                 const uint32_t aph = (it >> 1) & 1;
@@ -238,73 +245,71 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 __syncwarp();  // the polling loop may leave the lanes diverged; tcgen05.ld is warp-collective
                 tc_fence_after_sync();
                 const float E = e_sm[((mt - 1) & 3) * QT + m];
-                float y[DT];
-                {
-                    float lo[32], hi32[32];
-                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * DT;
-                    tmem_ld32(taddr, lo);
-                    tmem_ld32(taddr + 32, hi32);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) { y[c] = lo[c]; y[32 + c] = hi32[c]; }
-                }
+                float y[32];
+                tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * DT + cb, y);
+                tmem_ld_wait();
                 tc_fence_before_sync();
                 mbar_arrive(bar(B_ACC_EMPTY + acc));
 
                 const float *hin = h_sm + par * DT;
 #pragma unroll
-                for (int c = 0; c < DT; c += 4) {
-                    const float4 hv = *reinterpret_cast<const float4 *>(hin + c);
+                for (int c = 0; c < 32; c += 4) {
+                    const float4 hv = *reinterpret_cast<const float4 *>(hin + cb + c);
                     y[c] = fmaf(E, hv.x, y[c]);
                     y[c + 1] = fmaf(E, hv.y, y[c + 1]);
                     y[c + 2] = fmaf(E, hv.z, y[c + 2]);
                     y[c + 3] = fmaf(E, hv.w, y[c + 3]);
                 }
                 const int t = k * QT + m;
-                if (m == QT - 1) {
-                    float *hout = h_sm + (par ^ 1) * DT;
+                if (m == QT - 1) {  // the last row is the state handed to the next tile
+                    float *hout = h_sm + (par ^ 1) * DT + cb;
 #pragma unroll
-                    for (int c = 0; c < DT; c += 4)
+                    for (int c = 0; c < 32; c += 4)
                         *reinterpret_cast<float4 *>(hout + c) = make_float4(y[c], y[c + 1], y[c + 2], y[c + 3]);
                 }
-                // saved states at 64-step granularity: entering state (slot 2k) and state after row 63 (slot 2k+1)
+                // saved states at 64-step granularity: the entering state is written straight from shared
+                // memory (one coalesced line); the state after row 63 goes through shared memory so that 64
+                // threads can write it the same way after the barrier
                 if (p.tile_states) {
-                    if (m < DT && c0 + m < p.d)
+                    if (half == 0 && m < DT && c0 + m < p.d)
                         p.tile_states[(row * p.n_tiles64 + 2 * k) * p.d + c0 + m] = hin[m];
-                    if (m == 63 && 2 * k + 1 < p.n_tiles64) {
-                        float *ts = p.tile_states + (row * p.n_tiles64 + 2 * k + 1) * p.d + c0;
+                    if (m == 63) {
+                        float *mo = mid_sm + par * DT + cb;
 #pragma unroll
-                        for (int c = 0; c < DT; ++c)
-                            if (c0 + c < p.d) ts[c] = y[c];
+                        for (int c = 0; c < 32; c += 4)
+                            *reinterpret_cast<float4 *>(mo + c) = make_float4(y[c], y[c + 1], y[c + 2], y[c + 3]);
                     }
                 }
                 if (p.chunk_states && t + 1 < L && (t + 1) % p.chunk == 0) {
-                    float *cs = p.chunk_states + (row * p.n_chunks + (t + 1) / p.chunk) * p.d + c0;
+                    float *cs = p.chunk_states + (row * p.n_chunks + (t + 1) / p.chunk) * p.d + c0 + cb;
 #pragma unroll
-                    for (int c = 0; c < DT; ++c)
-                        if (c0 + c < p.d) cs[c] = y[c];
+                    for (int c = 0; c < 32; ++c)
+                        if (c0 + cb + c < p.d) cs[c] = y[c];
                 }
                 if (p.final_state && t == L - 1) {
-                    float *fs = p.final_state + row * p.d + c0;
+                    float *fs = p.final_state + row * p.d + c0 + cb;
 #pragma unroll
-                    for (int c = 0; c < DT; ++c)
-                        if (c0 + c < p.d) fs[c] = y[c];
+                    for (int c = 0; c < 32; ++c)
+                        if (c0 + cb + c < p.d) fs[c] = y[c];
                 }
-                // bf16 row -> staging buffer in the TMA's 128-byte swizzle
+                // bf16 half-row -> staging buffer in the TMA's 128-byte swizzle
                 uint8_t *stg = smem + FwdSmem::ystage + (it & 1) * kTileBytes;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
+                for (int j = 0; j < 4; ++j) {
                     const uint4 qv = make_uint4(pack_bf16x2(y[8 * j], y[8 * j + 1]), pack_bf16x2(y[8 * j + 2], y[8 * j + 3]),
                                                 pack_bf16x2(y[8 * j + 4], y[8 * j + 5]), pack_bf16x2(y[8 * j + 6], y[8 * j + 7]));
-                    *reinterpret_cast<uint4 *>(stg + sw128_offset(m, j)) = qv;
+                    *reinterpret_cast<uint4 *>(stg + sw128_offset(m, half * 4 + j)) = qv;
                 }
                 fence_proxy_async();
                 if (e0) tma_store_wait_read<0>();  // the other staging buffer is free for the next tile
-                bar_sync(1, 128);
+                bar_sync(1, kEpiThreads);
                 if (e0) {
                     tma_store_4d(&tm_y, sbase + FwdSmem::ystage + (it & 1) * kTileBytes, c0, hi, k * QT, bi);
                     tma_store_commit();
                 }
+                // mid_sm[par] is rewritten two tiles later, i.e. after everybody has passed the next barrier
+                if (p.tile_states && half == 0 && m < DT && c0 + m < p.d && 2 * k + 1 < p.n_tiles64)
+                    p.tile_states[(row * p.n_tiles64 + 2 * k + 1) * p.d + c0 + m] = mid_sm[par * DT + m];
             }
         }
         if (e0) tma_store_wait_all();
@@ -446,7 +451,8 @@ struct BwdSmem {
     static constexpr int hs = ostage + 2 * kTileBytes;                 // float[2][64] saved state entering the tile
     static constexpr int g = hs + 2 * DT * 4;                          // float[2][64] adjoint carry
     static constexpr int rowsc = g + 2 * DT * 4;                       // float[4][4][128]: Eprev, F, p, a per build
-    static constexpr int a = rowsc + 4 * 4 * QT * 4;                   // float[129]
+    static constexpr int da = rowsc + 4 * 4 * QT * 4;                  // float[2][128] decay-gradient halves
+    static constexpr int a = da + 2 * QT * 4;                          // float[129]
     static constexpr int pw = a + (QT + 4) * 4;                        // float[128]
     static constexpr int bars = pw + QT * 4;
     static constexpr int n_bars = 2 * kBwdStages + 4 + 2;
@@ -471,6 +477,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     float *hs_sm = reinterpret_cast<float *>(smem + BwdSmem::hs);
     float *g_sm = reinterpret_cast<float *>(smem + BwdSmem::g);
     float *rowsc = reinterpret_cast<float *>(smem + BwdSmem::rowsc);
+    float *da_sm = reinterpret_cast<float *>(smem + BwdSmem::da);
     float *a_sm = reinterpret_cast<float *>(smem + BwdSmem::a);
     float *p_sm = reinterpret_cast<float *>(smem + BwdSmem::pw);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + BwdSmem::abort_flag);
@@ -482,7 +489,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 
     if (tid == 0) {
         for (int i = 0; i < kBwdStages; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), 128); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiThreads); }
         mbar_init(bar(B_MAT_FULL), 128);
         mbar_init(bar(B_MAT_EMPTY), 1);
         *abort_flag = 0;
@@ -570,8 +577,11 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
     } else if (tid < kBuildThread0) {
         // ---------------- epilogue ----------------
+        // thread (q, lane, half): row m = 32 q + lane, channels [32 half, 32 half + 32) of the tile
         const int q = warp & 3;
+        const int half = (warp - kEpiThread0 / 32) >> 2;
         const int m = q * 32 + lane;
+        const int cb = half * 32;
         const bool e0 = tid == kEpiThread0;
         uint32_t it = 0, mt = 0;
         int cur_head = -1;
@@ -580,108 +590,106 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const int64_t row = item / p.n_dtiles;
             const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
             const int c0 = dtile * DT;
-            const bool ch_ok = m < DT && c0 + m < p.d;
+            const int64_t blk = row * p.n_dtiles + dtile;
+            const bool loader = half == 0 && m < DT;         // these 64 threads move per-channel vectors
+            const bool ch_ok = loader && c0 + m < p.d;
             // saved state of the first (rightmost) tile and the adjoint entering the sequence from the right
             float hs_next = 0.f;
-            if (m < DT) {
+            if (loader) {
                 hs_sm[(it & 1) * DT + m] =
                     ch_ok ? p.tile_states[(row * p.n_tiles64 + 2 * (p.n_tiles - 1)) * p.d + c0 + m] : 0.f;
                 g_sm[(it & 1) * DT + m] = (p.dfinal_state && ch_ok) ? p.dfinal_state[row * p.d + c0 + m] : 0.f;
             }
-            bar_sync(1, 128);
+            bar_sync(1, kEpiThreads);
             for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
                 const int acc = it & 1, par = it & 1;
                 const uint32_t aph = (it >> 1) & 1;
                 if (per_step || hi != cur_head) { cur_head = hi; ++mt; }
                 // prefetch the saved state of the next tile to the left while this one is being finished
-                if (m < DT && k > 0)
+                if (loader && k > 0)
                     hs_next = ch_ok ? p.tile_states[(row * p.n_tiles64 + 2 * (k - 1)) * p.d + c0 + m] : 0.f;
                 mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 15);
                 __syncwarp();
                 tc_fence_after_sync();
                 const float *rs = rowsc + ((mt - 1) & 3) * 4 * QT;
                 const float Eprev = rs[m], a_m = rs[3 * QT + m], p_m = rs[2 * QT + m];
-                // F: per-head decays use one Toeplitz table; the rightmost tile of a ragged sequence stops at L
+                // F: a time-invariant decay uses one Toeplitz table; the rightmost tile of the sequence stops at
+                // step L-1, where the adjoint entering from the right applies undamped
                 float F = rs[QT + m];
                 if (!per_step && k == p.n_tiles - 1) {
                     const int lim = L - k * QT;  // valid rows in this tile
-                    // prod_{j=m+1..lim-1} a = F_m / a^(128 - lim + 1); recomputed exactly by repeated multiply
                     float f = 1.f;
                     for (int j = m + 1; j < lim; ++j) f *= a_m;
                     F = f;
                 }
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * 2 * DT;
-                const float *hin = hs_sm + par * DT;
-                const float *gin = g_sm + par * DT;
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * 2 * DT + cb;
+                float z[32], lam[32];
+                tmem_ld32(taddr, z);
+                tmem_ld32(taddr + DT, lam);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                mbar_arrive(bar(B_ACC_EMPTY + acc));
+
+                const float *hin = hs_sm + par * DT + cb;
+                const float *gin = g_sm + par * DT + cb;
                 const int t = k * QT + m;
                 float dacc = 0.f;
+#pragma unroll
+                for (int c = 0; c < 32; c += 4) {
+                    const float4 hv = *reinterpret_cast<const float4 *>(hin + c);
+                    const float4 gv = *reinterpret_cast<const float4 *>(gin + c);
+                    z[c] = fmaf(Eprev, hv.x, z[c]);         lam[c] = fmaf(F, gv.x, lam[c]);
+                    z[c + 1] = fmaf(Eprev, hv.y, z[c + 1]); lam[c + 1] = fmaf(F, gv.y, lam[c + 1]);
+                    z[c + 2] = fmaf(Eprev, hv.z, z[c + 2]); lam[c + 2] = fmaf(F, gv.z, lam[c + 2]);
+                    z[c + 3] = fmaf(Eprev, hv.w, z[c + 3]); lam[c + 3] = fmaf(F, gv.w, lam[c + 3]);
+                }
+#pragma unroll
+                for (int c = 0; c < 32; ++c) dacc = fmaf(lam[c], z[c], dacc);
+                if (m == 0) {  // row 0 of the adjoint is what the tile to the left receives
+                    float *gout = g_sm + (par ^ 1) * DT + cb;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4)
+                        *reinterpret_cast<float4 *>(gout + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
+                    if (k == 0 && p.dinit_state) {
+                        float *di = p.dinit_state + row * p.d + c0 + cb;
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (c0 + cb + c < p.d) di[c] = a_m * lam[c];
+                    }
+                }
                 uint8_t *stg = smem + BwdSmem::ostage + (it & 1) * kTileBytes;
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    float z[32], lam[32];
-                    tmem_ld32(taddr + half * 32, z);
-                    tmem_ld32(taddr + DT + half * 32, lam);
-                    tmem_ld_wait();
-                    if (half == 1) {
-                        tc_fence_before_sync();
-                        mbar_arrive(bar(B_ACC_EMPTY + acc));
-                    }
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
-                        const float4 hv = *reinterpret_cast<const float4 *>(hin + half * 32 + c);
-                        const float4 gv = *reinterpret_cast<const float4 *>(gin + half * 32 + c);
-                        z[c] = fmaf(Eprev, hv.x, z[c]);         lam[c] = fmaf(F, gv.x, lam[c]);
-                        z[c + 1] = fmaf(Eprev, hv.y, z[c + 1]); lam[c + 1] = fmaf(F, gv.y, lam[c + 1]);
-                        z[c + 2] = fmaf(Eprev, hv.z, z[c + 2]); lam[c + 2] = fmaf(F, gv.z, lam[c + 2]);
-                        z[c + 3] = fmaf(Eprev, hv.w, z[c + 3]); lam[c + 3] = fmaf(F, gv.w, lam[c + 3]);
-                    }
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) dacc = fmaf(lam[c], z[c], dacc);
-                    if (m == 0) {
-                        float *gout = g_sm + (par ^ 1) * DT + half * 32;
-#pragma unroll
-                        for (int c = 0; c < 32; c += 4)
-                            *reinterpret_cast<float4 *>(gout + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
-                        if (k == 0 && p.dinit_state) {
-                            float *di = p.dinit_state + row * p.d + c0 + half * 32;
-#pragma unroll
-                            for (int c = 0; c < 32; ++c)
-                                if (c0 + half * 32 + c < p.d) di[c] = a_m * lam[c];
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint4 qv = make_uint4(pack_bf16x2(p_m * lam[8 * j], p_m * lam[8 * j + 1]),
-                                                    pack_bf16x2(p_m * lam[8 * j + 2], p_m * lam[8 * j + 3]),
-                                                    pack_bf16x2(p_m * lam[8 * j + 4], p_m * lam[8 * j + 5]),
-                                                    pack_bf16x2(p_m * lam[8 * j + 6], p_m * lam[8 * j + 7]));
-                        *reinterpret_cast<uint4 *>(stg + sw128_offset(m, half * 4 + j)) = qv;
-                    }
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 qv = make_uint4(pack_bf16x2(p_m * lam[8 * j], p_m * lam[8 * j + 1]),
+                                                pack_bf16x2(p_m * lam[8 * j + 2], p_m * lam[8 * j + 3]),
+                                                pack_bf16x2(p_m * lam[8 * j + 4], p_m * lam[8 * j + 5]),
+                                                pack_bf16x2(p_m * lam[8 * j + 6], p_m * lam[8 * j + 7]));
+                    *reinterpret_cast<uint4 *>(stg + sw128_offset(m, half * 4 + j)) = qv;
                 }
                 if (conv) dacc *= a_m;
                 if (t >= L) dacc = 0.f;
-                const int64_t blk = row * p.n_dtiles + dtile;
                 if (per_step) {
-                    if (t < L) p.da_partial[blk * (static_cast<int64_t>(p.n_tiles64) * 64) + t] = dacc;
+                    // the two column halves of a row meet in shared memory; half 0 writes the sum after the barrier
+                    if (half == 1) da_sm[par * QT + m] = dacc;
                 } else {
                     float wsum = dacc;
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
                     const int k64 = 2 * k + (q >> 1);
-                    if (lane == 0 && k64 < p.n_tiles64) {
-                        float *dst = p.da_partial + p.head_partial_offset + (blk * p.n_tiles64 + k64) * 4 + (q & 1) * 2;
-                        dst[0] = wsum;
-                        dst[1] = 0.f;
-                    }
+                    if (lane == 0 && k64 < p.n_tiles64)
+                        p.da_partial[p.head_partial_offset + (blk * p.n_tiles64 + k64) * 4 + (q & 1) * 2 + half] = wsum;
                 }
-                if (m < DT) hs_sm[(par ^ 1) * DT + m] = hs_next;
+                if (loader) hs_sm[(par ^ 1) * DT + m] = hs_next;
                 fence_proxy_async();
                 if (e0) tma_store_wait_read<0>();
-                bar_sync(1, 128);
+                bar_sync(1, kEpiThreads);
                 if (e0) {
                     tma_store_4d(&tm_o, sbase + BwdSmem::ostage + (it & 1) * kTileBytes, c0, hi, k * QT, bi);
                     tma_store_commit();
                 }
+                // da_sm[par] is rewritten two tiles later, after everybody has passed the next barrier
+                if (per_step && half == 0 && t < L)
+                    p.da_partial[blk * (static_cast<int64_t>(p.n_tiles64) * 64) + t] = dacc + da_sm[par * QT + m];
             }
         }
         if (e0) tma_store_wait_all();
