@@ -154,7 +154,7 @@ extern "C" int ema_b200_fwd(const ema_b200_problem *p, const void *x, const floa
     if (rows * fp.n_dtiles >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;
     if (p->dtype == EMA_BF16 && y && stop_below == 0.f && tc_enabled() &&
         tc_tensor_ok(x, p->d, p->x_sb, p->x_sl, p->x_sh, p->b, p->L, p->h) &&
-        tc_tensor_ok(y, p->d, p->y_sb, p->y_sl, p->y_sh, p->b, p->L, p->h)) {
+        tc_tensor_ok(y, p->d, p->y_sb, p->y_sl, p->y_sh, p->b, p->L, p->h) && aligned(tile_states, 16)) {
         rc = launch_fused_fwd_tc(fp, st);
         if (rc != EMA_ERR_UNSUPPORTED) return rc;  // a tensor map the driver refuses falls through to the FMA path
     }
@@ -210,6 +210,8 @@ extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const floa
         rc = launch_fused_bwd_tc(fp, st);
         if (rc && rc != EMA_ERR_UNSUPPORTED) return rc;
         done = rc == EMA_OK;
+        // the tensor-core kernel keeps the two 32-channel halves of a tile apart in the per-step partial sums
+        if (done && p->decay_mode == EMA_DECAY_PER_STEP) fp.n_dtiles *= 2;
     }
     if (!done) {
         rc = launch_fused_bwd_fma(fp, p->dtype, vec, st);

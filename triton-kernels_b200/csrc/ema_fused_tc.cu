@@ -6,13 +6,18 @@
 // shared by all channels.  G is written to shared memory as bf16 (K-major, 128-byte swizzle), the x
 // tile [128 steps x 64 channels] lands next to it by TMA exactly as the MMA wants its B operand
 // (MN-major, 128-byte swizzle), tcgen05.mma accumulates Y in TMEM (fp32), and the epilogue warps add
-// the carry term in fp32, hand the last row on as the next carry, and TMA-store bf16 y.
+// the carry term in fp32, hand the last row on as the next carry, and bf16 y leaves by TMA store.
 //
 // One persistent CTA per SM walks its work items (scan row, 64-channel tile) and, inside an item, the
-// tiles in sequence order.  Warp roles:  warp 0 TMA producer;  warp 1 MMA issuer (owns TMEM);
-// warps 2-9 epilogue (a TMEM lane quadrant and one half of the 64 channels each);  warps 10-13 build G
-// (once for a time-invariant decay, per tile otherwise, with running products: no exp, no division).
-// Every wait on an mbarrier is bounded (ema_tc_common.cuh); after a timeout the roles run their
+// tiles in sequence order.  15 warps, each with one job:
+//   warp 0      TMA producer (x tiles, and dy tiles in the backward) into a ring of stages
+//   warp 1      MMA issuer; owns the TMEM allocation
+//   warps 2-9   epilogue: TMEM lane quadrant (warp % 4) x one half of the 64 channels
+//   warps 10-13 build the decay matrices (once per head for a time-invariant decay, per tile otherwise)
+//   warp 14     issues the TMA stores of finished tiles
+// The warps meet only through mbarriers: stage full/empty, accumulator full/empty, matrix full/empty,
+// carry ready (a ring of 4 so that the warp on the serial carry chain can run ahead of the others), and
+// staging full/empty.  Every wait is bounded (ema_tc_common.cuh): after a timeout the roles run their
 // loops to the end without waiting, the CTA tears down normally and the host sees EMA_ERR_TIMEOUT.
 #include "ema_common.cuh"
 #include "ema_tc_common.cuh"
@@ -24,11 +29,118 @@ constexpr int QT = 128;              // steps per tile = MMA M = MMA K extent
 constexpr int DT = 64;               // channels per tile = MMA N
 constexpr int kTileBytes = QT * DT * 2;
 constexpr int kMatBytes = QT * QT * 2;
-constexpr int kThreads = 448;      // 14 warps: TMA, MMA, 8 epilogue, 4 builders
-constexpr int kEpiThread0 = 64;    // warps 2-9
+constexpr int kThreads = 480;        // 15 warps
+constexpr int kEpiThread0 = 64;      // warps 2-9
 constexpr int kEpiThreads = 256;
-constexpr int kBuildThread0 = 320;  // warps 10-13
+constexpr int kEpiWarps = kEpiThreads / 32;
+constexpr int kBuildThread0 = 320;   // warps 10-13
+constexpr int kStoreThread = 448;    // warp 14, lane 0
+constexpr int kRing = 4;             // depth of the carry ring and of the per-row scalar tables
 constexpr uint32_t kIdesc = make_idesc_bf16(QT, DT, 0, 1);
+
+// named barriers (id 0 is __syncthreads)
+__device__ __forceinline__ void bar_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Decay matrices.  With cs[j] = sum_{i<=j} log2 a_i over the tile (cs[-1] = 0):
+//   LOWER, shift 0:  M[m,k] = p_k 2^(cs[m]   - cs[k]),  k <= m            forward G
+//   LOWER, shift 1:  M[m,k] = p_k 2^(cs[m-1] - cs[k]),  k <= m-1;  M[m,m] = diag      backward A1
+//   UPPER:           M[m,k] =     2^(cs[k]   - cs[m]),  k >= m                        backward U
+// Every element is independent (one ex2 each), so the 8256 elements of a triangle are dealt out evenly:
+// builder thread t takes every second 8-element chunk of the row pair (t % 64, 127 - t % 64), which
+// always holds 17 chunks.  Values are produced into registers first and stored once the matrix buffer
+// has been released by the MMAs that were reading it.
+// ---------------------------------------------------------------------------------------------
+constexpr int kMaxChunks = 9;
+struct RowChunks {
+    uint4 v[kMaxChunks];
+};
+
+// Calls f(row, chunk) for this thread's chunks, in a fixed order; returns their number.
+template <bool UPPER, typename F>
+__device__ __forceinline__ int for_my_chunks(int t, F f) {
+    const int pr = t & 63, sel = t >> 6;
+    const int row_long = UPPER ? pr : 127 - pr;   // the row of the pair with more chunks
+    const int row_short = 127 - row_long;
+    const int n_long = UPPER ? 16 - (row_long >> 3) : (row_long >> 3) + 1;
+    int n = 0;
+#pragma unroll
+    for (int s = 0; s < kMaxChunks; ++s) {   // s is a compile-time register index; i the position in the 17-chunk list
+        const int i = 2 * s + sel;
+        if (i >= 17) continue;
+        const bool in_long = i < n_long;
+        const int row = in_long ? row_long : row_short;
+        const int j = in_long ? i : i - n_long;                       // index inside the row's chunk list
+        const int chunk = UPPER ? (row >> 3) + j : j;
+        f(s, row, chunk);
+        ++n;
+    }
+    return n;
+}
+
+template <int SHIFT>
+__device__ __forceinline__ void compute_lower(int t, const float *cs_sm, const float *p_sm, float diag, RowChunks &out) {
+    for_my_chunks<false>(t, [&](int n, int m, int c) {
+        const float cm = (m - SHIFT >= 0) ? cs_sm[m - SHIFT] : 0.f;
+        const int top = m - SHIFT;
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int k = c * 8 + e;
+            float val = 0.f;
+            if (k <= top) val = p_sm[k] * ex2_approx(cm - cs_sm[k]);
+            else if (SHIFT == 1 && k == m) val = diag;
+            v[e] = val;
+        }
+        out.v[n] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                              pack_bf16x2(v[6], v[7]));
+    });
+}
+__device__ __forceinline__ void compute_upper(int t, const float *cs_sm, RowChunks &out) {
+    for_my_chunks<true>(t, [&](int n, int m, int c) {
+        const float cm = cs_sm[m];
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int k = c * 8 + e;
+            v[e] = (k >= m) ? ex2_approx(cs_sm[k] - cm) : 0.f;
+        }
+        out.v[n] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                              pack_bf16x2(v[6], v[7]));
+    });
+}
+template <bool UPPER>
+__device__ __forceinline__ void store_chunks(int t, uint8_t *mat, const RowChunks &in) {
+    for_my_chunks<UPPER>(t, [&](int n, int m, int c) {
+        *reinterpret_cast<uint4 *>(mat + (c >> 3) * (QT * 128) + sw128_offset(m, c & 7)) = in.v[n];
+    });
+}
+
+// Inclusive scan of one value per builder thread (128 threads, 4 warps) through shared memory.
+// Leaves cs_sm[r] = sum_{i<=r} v_i.  Two named-barrier syncs; the first also fences the previous use.
+__device__ __forceinline__ void builder_scan(float v, int r, float *cs_sm, float *warp_tot) {
+    const int lane = r & 31, w = r >> 5;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const float n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+    }
+    bar_sync(2, 128);  // everybody has finished reading the previous tile's tables
+    if (lane == 31) warp_tot[w] = v;
+    bar_sync(2, 128);
+    float off = 0.f;
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+        if (i < w) off += warp_tot[i];
+    cs_sm[r] = v + off;
+}
 
 struct TcParams {
     const float *decay;
@@ -38,75 +150,34 @@ struct TcParams {
     int64_t a_sb, a_sl, a_sh;
     int decay_mode, convention, chunk;
     int n_tiles;      // 128-step tiles
-    int n_tiles64;    // saved states per row (64-step granularity, shared with the FMA path)
+    int n_tiles64;    // saved states per row (64-step granularity, shared with the CUDA-core path)
     int n_dtiles, n_items;
     int64_t n_chunks;
 };
 
-// named barriers (id 0 is __syncthreads)
-__device__ __forceinline__ void bar_sync(int id, int nthreads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
-// ---------------------------------------------------------------------------------------------
-// Builder: thread r owns row r of a lower-triangular matrix.
-//   a_sm[j], p_sm[j]: decay and input weight of step j of the tile (a = 1, p = 0 is never needed:
-//   rows past the end multiply zero-filled x rows).
-//   SHIFT = 0:  M[r,k] = p_k prod_{j=k+1..r} a_j,  k <= r          (forward matrix G)
-//   SHIFT = 1:  M[r,k] = p_k prod_{j=k+1..r-1} a_j, k <= r-1;  M[r,r] = diag   (backward: y_{r-1} - x_r)
-// Returns the product of a over all steps the row spans: prod_{j<=r} a_j (SHIFT 0) or prod_{j<r} a_j.
-// The row is produced right to left in 8-element chunks, one 16-byte store per chunk.
-// ---------------------------------------------------------------------------------------------
-template <int SHIFT>
-__device__ __forceinline__ float build_lower_row(uint8_t *mat, int r, const float *a_sm, const float *p_sm,
-                                                 float diag) {
-    const int top = r - SHIFT;  // highest k with a scan term
-    float run = 1.f;
-    // every thread visits the chunks in the same order, so a_sm / p_sm reads are warp broadcasts
-    for (int c = QT / 8 - 1; c >= 0; --c) {
-        if (c > (r >> 3)) continue;
-        float v[8];
-#pragma unroll
-        for (int e = 7; e >= 0; --e) {
-            const int k = c * 8 + e;
-            float val = 0.f;
-            if (k <= top) {
-                val = p_sm[k] * run;
-                run *= a_sm[k];
-            } else if (SHIFT == 1 && k == r) {
-                val = diag;
-            }
-            v[e] = val;
-        }
-        const uint4 q = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                                   pack_bf16x2(v[6], v[7]));
-        *reinterpret_cast<uint4 *>(mat + (c >> 3) * (QT * 128) + sw128_offset(r, c & 7)) = q;
-    }
-    return run;
-}
-
 // ---------------------------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------------------------
-constexpr int kFwdStages = 7;  // 7 x 16 KB of loads in flight per SM: HBM latency under load is ~3 us
+constexpr int kFwdStages = 6;
 constexpr int kFwdMatBufs = 2;
 struct FwdSmem {
     static constexpr int mat = 0;
     static constexpr int x = mat + kFwdMatBufs * kMatBytes;
     static constexpr int ystage = x + kFwdStages * kTileBytes;
-    static constexpr int h = ystage + 2 * kTileBytes;       // float[2][64]
-    static constexpr int e = h + 2 * DT * 4;                 // float[4][128]
-    static constexpr int a = e + 4 * QT * 4;                 // float[128]
-    static constexpr int pw = a + QT * 4;                    // float[128]
-    static constexpr int red = pw + QT * 4;                  // float[4]
-    static constexpr int mid = red + 16;                     // float[2][64]: state after row 63
-    static constexpr int bars = mid + 2 * DT * 4;            // uint64[...]
-    static constexpr int n_bars = 2 * kFwdStages + 4 + 2 * kFwdMatBufs;
+    static constexpr int h = ystage + 2 * kTileBytes;        // float[kRing][64] carry entering a tile
+    static constexpr int e = h + kRing * DT * 4;              // float[kRing][128] E_m per build
+    static constexpr int cs = e + kRing * QT * 4;             // float[128] cumulative log2 decay
+    static constexpr int pw = cs + QT * 4;                    // float[128] input weights
+    static constexpr int wt = pw + QT * 4;                    // float[4] scan scratch
+    static constexpr int bars = wt + 16;
+    // stage full/empty, acc full/empty, matrix full/empty, carry ready, staging full/empty
+    static constexpr int n_bars = 2 * kFwdStages + 4 + 2 * kFwdMatBufs + kRing + 4;
     static constexpr int tmem_slot = bars + n_bars * 8;
     static constexpr int abort_flag = tmem_slot + 4;
     static constexpr int total = abort_flag + 4;
 };
 constexpr int kFwdSmemBytes = FwdSmem::total + 1024;  // + slack for the manual 1024-byte alignment
+static_assert(kFwdSmemBytes <= 227 * 1024, "forward shared memory exceeds the per-CTA limit");
 
 __global__ void __launch_bounds__(kThreads, 1)
 ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
@@ -121,21 +192,22 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 
     float *h_sm = reinterpret_cast<float *>(smem + FwdSmem::h);
     float *e_sm = reinterpret_cast<float *>(smem + FwdSmem::e);
-    float *a_sm = reinterpret_cast<float *>(smem + FwdSmem::a);
+    float *cs_sm = reinterpret_cast<float *>(smem + FwdSmem::cs);
     float *p_sm = reinterpret_cast<float *>(smem + FwdSmem::pw);
-    float *red_sm = reinterpret_cast<float *>(smem + FwdSmem::red);
-    float *mid_sm = reinterpret_cast<float *>(smem + FwdSmem::mid);
+    float *wt_sm = reinterpret_cast<float *>(smem + FwdSmem::wt);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + FwdSmem::abort_flag);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + FwdSmem::tmem_slot);
     auto bar = [&](int i) { return sbase + FwdSmem::bars + i * 8; };
-    // barrier indices
     constexpr int B_FULL = 0, B_EMPTY = kFwdStages, B_ACC_FULL = 2 * kFwdStages, B_ACC_EMPTY = B_ACC_FULL + 2,
-                  B_MAT_FULL = B_ACC_EMPTY + 2, B_MAT_EMPTY = B_MAT_FULL + kFwdMatBufs;
+                  B_MAT_FULL = B_ACC_EMPTY + 2, B_MAT_EMPTY = B_MAT_FULL + kFwdMatBufs,
+                  B_H = B_MAT_EMPTY + kFwdMatBufs, B_STG_FULL = B_H + kRing, B_STG_EMPTY = B_STG_FULL + 2;
 
     if (tid == 0) {
         for (int i = 0; i < kFwdStages; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiThreads); }
-        for (int i = 0; i < kFwdMatBufs; ++i) { mbar_init(bar(B_MAT_FULL + i), 128); mbar_init(bar(B_MAT_EMPTY + i), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiWarps); }
+        for (int i = 0; i < kFwdMatBufs; ++i) { mbar_init(bar(B_MAT_FULL + i), 4); mbar_init(bar(B_MAT_EMPTY + i), 1); }
+        for (int i = 0; i < kRing; ++i) mbar_init(bar(B_H + i), 2);           // one arrival per channel half
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_STG_FULL + i), kEpiWarps); mbar_init(bar(B_STG_EMPTY + i), 1); }
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tm_x);
@@ -154,7 +226,8 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
 
     const int64_t n_items = p.n_items;
-    auto decay_a = [&](float v) { return conv ? expf(v) : v; };
+    // log2 of the multiplicative decay of one step
+    auto log2_decay = [&](float v) { return conv ? v * 1.4426950408889634f : log2f(v); };
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -199,12 +272,13 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 3)) break;
                     if (!mbar_wait(bar(B_ACC_EMPTY + acc), aph ^ 1, abort_flag, 4)) break;
                     tc_fence_after_sync();
-                    const uint32_t a_base = sbase + FwdSmem::mat + mb_cur * kMatBytes;
-                    const uint32_t b_base = sbase + FwdSmem::x + s * kTileBytes;
+                    const uint64_t ad0 = make_desc_sw128(sbase + FwdSmem::mat + mb_cur * kMatBytes, 16, 1024);
+                    const uint64_t bd0 = make_desc_sw128(sbase + FwdSmem::x + s * kTileBytes, kTileBytes, 1024);
 #pragma unroll
                     for (int kb = 0; kb < QT / 16; ++kb) {
-                        const uint64_t ad = make_desc_sw128(a_base + (kb >> 2) * (QT * 128) + (kb & 3) * 32, 16, 1024);
-                        const uint64_t bd = make_desc_sw128(b_base + kb * 2048, kTileBytes, 1024);
+                        // descriptor start addresses are in 16-byte units: next K step inside / across 64-wide K blocks
+                        const uint64_t ad = ad0 + (((kb >> 2) * (QT * 128) + (kb & 3) * 32) >> 4);
+                        const uint64_t bd = bd0 + ((kb * 2048) >> 4);
                         umma_bf16(tmem_base + acc * DT, ad, bd, kIdesc, kb > 0 ? 1u : 0u);
                     }
                     umma_commit(bar(B_EMPTY + s));
@@ -215,43 +289,47 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
     } else if (tid < kBuildThread0) {
         // ---------------- epilogue ----------------
-        // 8 warps: TMEM lane quadrant q = warp % 4 (hardware rule), column half = 0 for warps 2-5, 1 for 6-9.
         // Thread (q, lane, half) owns row m = 32 q + lane and channels [32 half, 32 half + 32) of the tile.
+        // The two threads of row 127 are the serial carry chain: they publish the state entering the next
+        // tile as soon as they have it; nobody else waits for anything but that state and the accumulator.
         const int q = warp & 3;
         const int half = (warp - kEpiThread0 / 32) >> 2;
         const int m = q * 32 + lane;
         const int cb = half * 32;
-        const bool e0 = tid == kEpiThread0;
+        const bool loader = half == 0 && m < DT;   // 64 threads that move per-channel vectors
         uint32_t it = 0, mt = 0;
         int cur_head = -1;
         for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
             const int dtile = static_cast<int>(item % p.n_dtiles);
             const int64_t row = item / p.n_dtiles;
-            const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
+            const int hi = static_cast<int>(row % p.h);
             const int c0 = dtile * DT;
-            if (m < DT && half == 0) {
-                const bool ok = c0 + m < p.d;
-                const float v = (p.init_state && ok) ? p.init_state[row * p.d + c0 + m] : 0.f;
-                h_sm[(it & 1) * DT + m] = v;
-                if (p.chunk_states && ok) p.chunk_states[(row * p.n_chunks) * p.d + c0 + m] = v;
+            const bool ch_ok = loader && c0 + m < p.d;
+            float *ts_item = p.tile_states ? p.tile_states + row * p.n_tiles64 * p.d + c0 : nullptr;
+            if (loader) {
+                const float v = (p.init_state && ch_ok) ? p.init_state[row * p.d + c0 + m] : 0.f;
+                h_sm[(it & (kRing - 1)) * DT + m] = v;
+                if (p.chunk_states && ch_ok) p.chunk_states[(row * p.n_chunks) * p.d + c0 + m] = v;
             }
-            bar_sync(1, kEpiThreads);
+            bar_sync(1, kEpiThreads);  // once per item: the previous item is finished everywhere, the state is in place
+            if (m == QT - 1) mbar_arrive(bar(B_H + (it & (kRing - 1))));
             for (int k = 0; k < p.n_tiles; ++k, ++it) {
-                const int acc = it & 1, par = it & 1;
-                const uint32_t aph = (it >> 1) & 1;
-                const bool new_mat = per_step || hi != cur_head;
-                if (new_mat) { cur_head = hi; ++mt; }
+                const int acc = it & 1, slot = it & (kRing - 1), buf = it & 1;
+                const uint32_t aph = (it >> 1) & 1, hph = (it / kRing) & 1;
+                if (per_step || hi != cur_head) { cur_head = hi; ++mt; }
                 mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 5);
                 __syncwarp();  // the polling loop may leave the lanes diverged; tcgen05.ld is warp-collective
                 tc_fence_after_sync();
-                const float E = e_sm[((mt - 1) & 3) * QT + m];
+                const float E = e_sm[((mt - 1) & (kRing - 1)) * QT + m];
                 float y[32];
                 tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * DT + cb, y);
                 tmem_ld_wait();
                 tc_fence_before_sync();
-                mbar_arrive(bar(B_ACC_EMPTY + acc));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + acc));  // one arrival per warp
 
-                const float *hin = h_sm + par * DT;
+                mbar_wait(bar(B_H + slot), hph, abort_flag, 6);
+                const float *hin = h_sm + slot * DT;
 #pragma unroll
                 for (int c = 0; c < 32; c += 4) {
                     const float4 hv = *reinterpret_cast<const float4 *>(hin + cb + c);
@@ -260,24 +338,23 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     y[c + 2] = fmaf(E, hv.z, y[c + 2]);
                     y[c + 3] = fmaf(E, hv.w, y[c + 3]);
                 }
-                const int t = k * QT + m;
-                if (m == QT - 1) {  // the last row is the state handed to the next tile
-                    float *hout = h_sm + (par ^ 1) * DT + cb;
+                if (m == QT - 1 && k + 1 < p.n_tiles) {  // the last row is the state entering the next tile
+                    float *hout = h_sm + ((it + 1) & (kRing - 1)) * DT + cb;
 #pragma unroll
                     for (int c = 0; c < 32; c += 4)
                         *reinterpret_cast<float4 *>(hout + c) = make_float4(y[c], y[c + 1], y[c + 2], y[c + 3]);
+                    mbar_arrive(bar(B_H + ((it + 1) & (kRing - 1))));
                 }
-                // saved states at 64-step granularity: the entering state is written straight from shared
-                // memory (one coalesced line); the state after row 63 goes through shared memory so that 64
-                // threads can write it the same way after the barrier
-                if (p.tile_states) {
-                    if (half == 0 && m < DT && c0 + m < p.d)
-                        p.tile_states[(row * p.n_tiles64 + 2 * k) * p.d + c0 + m] = hin[m];
-                    if (m == 63) {
-                        float *mo = mid_sm + par * DT + cb;
+                const int t = k * QT + m;
+                // saved states at 64-step granularity: entering state (slot 2k) and state after row 63 (slot 2k+1)
+                if (ts_item) {
+                    if (ch_ok) ts_item[static_cast<int64_t>(2 * k) * p.d + m] = hin[m];
+                    if (m == 63 && 2 * k + 1 < p.n_tiles64) {
+                        float *ts = ts_item + static_cast<int64_t>(2 * k + 1) * p.d + cb;
 #pragma unroll
-                        for (int c = 0; c < 32; c += 4)
-                            *reinterpret_cast<float4 *>(mo + c) = make_float4(y[c], y[c + 1], y[c + 2], y[c + 3]);
+                        for (int c = 0; c < 32; c += 4)   // d is a multiple of 8: a float4 is all inside or all outside
+                            if (c0 + cb + c < p.d)
+                                *reinterpret_cast<float4 *>(ts + c) = make_float4(y[c], y[c + 1], y[c + 2], y[c + 3]);
                     }
                 }
                 if (p.chunk_states && t + 1 < L && (t + 1) % p.chunk == 0) {
@@ -292,8 +369,9 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     for (int c = 0; c < 32; ++c)
                         if (c0 + cb + c < p.d) fs[c] = y[c];
                 }
-                // bf16 half-row -> staging buffer in the TMA's 128-byte swizzle
-                uint8_t *stg = smem + FwdSmem::ystage + (it & 1) * kTileBytes;
+                // bf16 half-row -> staging buffer in the TMA's 128-byte swizzle, once the store of two tiles ago has read it
+                mbar_wait(bar(B_STG_EMPTY + buf), aph ^ 1, abort_flag, 7);
+                uint8_t *stg = smem + FwdSmem::ystage + buf * kTileBytes;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint4 qv = make_uint4(pack_bf16x2(y[8 * j], y[8 * j + 1]), pack_bf16x2(y[8 * j + 2], y[8 * j + 3]),
@@ -301,79 +379,80 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     *reinterpret_cast<uint4 *>(stg + sw128_offset(m, half * 4 + j)) = qv;
                 }
                 fence_proxy_async();
-                if (e0) tma_store_wait_read<0>();  // the other staging buffer is free for the next tile
-                bar_sync(1, kEpiThreads);
-                if (e0) {
-                    tma_store_4d(&tm_y, sbase + FwdSmem::ystage + (it & 1) * kTileBytes, c0, hi, k * QT, bi);
-                    tma_store_commit();
-                }
-                // mid_sm[par] is rewritten two tiles later, i.e. after everybody has passed the next barrier
-                if (p.tile_states && half == 0 && m < DT && c0 + m < p.d && 2 * k + 1 < p.n_tiles64)
-                    p.tile_states[(row * p.n_tiles64 + 2 * k + 1) * p.d + c0 + m] = mid_sm[par * DT + m];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_STG_FULL + buf));
             }
         }
-        if (e0) tma_store_wait_all();
-    } else {
+    } else if (tid < kStoreThread) {
         // ---------------- matrix builders ----------------
         const int r = tid - kBuildThread0;
         uint32_t mt = 0;
         int cur_head = -1;
+        // one build: scan log2 a, produce the matrix into registers, then store it when the buffer is free
+        auto build = [&](float l2, float pw) {
+            const int mb = mt % kFwdMatBufs;
+            builder_scan(l2, r, cs_sm, wt_sm);
+            p_sm[r] = pw;
+            bar_sync(2, 128);
+            RowChunks g;
+            compute_lower<0>(r, cs_sm, p_sm, 0.f, g);
+            const float E = exp2f(cs_sm[r]);
+            mbar_wait(bar(B_MAT_EMPTY + mb), ((mt / kFwdMatBufs) & 1) ^ 1, abort_flag, 8);
+            store_chunks<false>(r, smem + FwdSmem::mat + mb * kMatBytes, g);
+            e_sm[(mt & (kRing - 1)) * QT + r] = E;
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_MAT_FULL + mb));
+            ++mt;
+        };
         for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
             const int64_t row = item / p.n_dtiles;
             const int dtile = static_cast<int>(item % p.n_dtiles);
             const int64_t bi = row / p.h, hi = row % p.h;
             const float *arow = p.decay + (per_step ? bi * p.a_sb + hi * p.a_sh : hi * p.a_sh);
-            float logsum = 0.f;
             if (!per_step) {
+                const float v = arow[0];
                 if (static_cast<int>(hi) != cur_head) {
                     cur_head = static_cast<int>(hi);
-                    const float a = decay_a(arow[0]);
-                    const int mb = mt % kFwdMatBufs;
-                    bar_sync(2, 128);
-                    a_sm[r] = a;
-                    p_sm[r] = conv ? 1.f : 1.f - a;
-                    bar_sync(2, 128);
-                    mbar_wait(bar(B_MAT_EMPTY + mb), ((mt / kFwdMatBufs) & 1) ^ 1, abort_flag, 6);
-                    const float E = build_lower_row<0>(smem + FwdSmem::mat + mb * kMatBytes, r, a_sm, p_sm, 0.f);
-                    e_sm[(mt & 3) * QT + r] = E;
-                    fence_proxy_async();
-                    mbar_arrive(bar(B_MAT_FULL + mb));
-                    ++mt;
+                    build(log2_decay(v), conv ? 1.f : 1.f - v);
                 }
                 if (p.log_decay_sum && r == 0 && dtile == 0)
-                    p.log_decay_sum[row] = static_cast<float>(L) * logf(decay_a(arow[0]));
+                    p.log_decay_sum[row] = static_cast<float>(L) * (conv ? v : logf(v));
                 continue;
             }
-            float a_next = 1.f;
-            {
-                const int t = r;
-                if (t < L) a_next = decay_a(arow[static_cast<int64_t>(t) * p.a_sl]);
-            }
-            for (int k = 0; k < p.n_tiles; ++k, ++mt) {
-                const float a = a_next;
+            // per-step decay: the raw value of step r of the next tile is fetched one tile ahead
+            float logsum = 0.f;
+            float v_next = (r < L) ? arow[static_cast<int64_t>(r) * p.a_sl] : (conv ? 0.f : 1.f);
+            for (int k = 0; k < p.n_tiles; ++k) {
+                const float v = v_next;
                 if (k + 1 < p.n_tiles) {
                     const int t = (k + 1) * QT + r;
-                    a_next = t < L ? decay_a(arow[static_cast<int64_t>(t) * p.a_sl]) : 1.f;
+                    v_next = t < L ? arow[static_cast<int64_t>(t) * p.a_sl] : (conv ? 0.f : 1.f);
                 }
-                const int mb = mt % kFwdMatBufs;
-                bar_sync(2, 128);  // everyone has finished reading the previous tile's a_sm / p_sm / red_sm
-                a_sm[r] = a;
-                p_sm[r] = conv ? 1.f : 1.f - a;
-                if (p.log_decay_sum) {
-                    float lg = logf(a);
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) lg += __shfl_xor_sync(0xffffffffu, lg, o);
-                    if (lane == 0) red_sm[warp - kBuildThread0 / 32] = lg;
-                }
-                bar_sync(2, 128);
-                if (p.log_decay_sum && r == 0) logsum += (red_sm[0] + red_sm[1]) + (red_sm[2] + red_sm[3]);
-                mbar_wait(bar(B_MAT_EMPTY + mb), ((mt / kFwdMatBufs) & 1) ^ 1, abort_flag, 7);
-                const float E = build_lower_row<0>(smem + FwdSmem::mat + mb * kMatBytes, r, a_sm, p_sm, 0.f);
-                e_sm[(mt & 3) * QT + r] = E;
-                fence_proxy_async();
-                mbar_arrive(bar(B_MAT_FULL + mb));
+                build(log2_decay(v), conv ? 1.f : 1.f - v);
+                // cs_sm[127] now holds log2 of the product of this tile's decays
+                if (p.log_decay_sum && r == 0) logsum += cs_sm[QT - 1] * 0.6931471805599453f;
             }
             if (p.log_decay_sum && r == 0 && dtile == 0) p.log_decay_sum[row] = logsum;
+        }
+    } else {
+        // ---------------- TMA store issuer ----------------
+        if (tid == kStoreThread) {
+            uint32_t it = 0;
+            for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
+                const int dtile = static_cast<int>(item % p.n_dtiles);
+                const int64_t row = item / p.n_dtiles;
+                const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
+                for (int k = 0; k < p.n_tiles; ++k, ++it) {
+                    const int buf = it & 1;
+                    if (!mbar_wait(bar(B_STG_FULL + buf), (it >> 1) & 1, abort_flag, 9)) break;
+                    tma_store_4d(&tm_y, sbase + FwdSmem::ystage + buf * kTileBytes, dtile * DT, hi, k * QT, bi);
+                    tma_store_commit();
+                    tma_store_wait_read<0>();          // the staging buffer has been read: hand it back
+                    mbar_arrive(bar(B_STG_EMPTY + buf));
+                }
+            }
+            tma_store_wait_all();
         }
     }
 
@@ -403,32 +482,6 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 // Eprev_m = prod_{j<m} a_j;  F_m = prod_{j=m+1..128} a_j (a_128 = first decay of the next tile, 1 past L).
 // Then dx_m = p_m Lam_m, ddecay_m = sum_c Lam_mc Z_mc (times a_m for the log-decay convention), and row 0
 // of Lam is the adjoint handed to the previous tile.
-
-// Upper-triangular row r of U, left to right from the diagonal; returns prod_{j=r+1..127} a_j.
-__device__ __forceinline__ float build_upper_row(uint8_t *mat, int r, const float *a_sm) {
-    float run = 1.f;
-    for (int c = 0; c < QT / 8; ++c) {
-        if (c < (r >> 3)) continue;
-        float v[8];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const int k = c * 8 + e;
-            float val = 0.f;
-            if (k == r) {
-                val = 1.f;
-            } else if (k > r) {
-                run *= a_sm[k];
-                val = run;
-            }
-            v[e] = val;
-        }
-        const uint4 q = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                                   pack_bf16x2(v[6], v[7]));
-        *reinterpret_cast<uint4 *>(mat + (c >> 3) * (QT * 128) + sw128_offset(r, c & 7)) = q;
-    }
-    return run;
-}
-
 struct TcBwdParams {
     const float *decay;
     const float *tile_states;
@@ -448,14 +501,14 @@ struct BwdSmem {
     static constexpr int mat_u = mat_a1 + kMatBytes;
     static constexpr int xg = mat_u + kMatBytes;                       // stages of [x tile | dy tile]
     static constexpr int ostage = xg + kBwdStages * 2 * kTileBytes;    // dx staging, 2 buffers
-    static constexpr int hs = ostage + 2 * kTileBytes;                 // float[2][64] saved state entering the tile
-    static constexpr int g = hs + 2 * DT * 4;                          // float[2][64] adjoint carry
-    static constexpr int rowsc = g + 2 * DT * 4;                       // float[4][4][128]: Eprev, F, p, a per build
-    static constexpr int da = rowsc + 4 * 4 * QT * 4;                  // float[2][128] decay-gradient halves
-    static constexpr int a = da + 2 * QT * 4;                          // float[129]
-    static constexpr int pw = a + (QT + 4) * 4;                        // float[128]
-    static constexpr int bars = pw + QT * 4;
-    static constexpr int n_bars = 2 * kBwdStages + 4 + 2;
+    static constexpr int hs = ostage + 2 * kTileBytes;                 // float[kRing][64] saved state entering the tile
+    static constexpr int g = hs + kRing * DT * 4;                      // float[kRing][64] adjoint carry
+    static constexpr int rowsc = g + kRing * DT * 4;                   // float[kRing][4][128]: Eprev, F, p, a per build
+    static constexpr int cs = rowsc + kRing * 4 * QT * 4;              // float[128]
+    static constexpr int pw = cs + QT * 4;                             // float[128]
+    static constexpr int wt = pw + QT * 4;                             // float[4]
+    static constexpr int bars = wt + 16;
+    static constexpr int n_bars = 2 * kBwdStages + 4 + 2 + kRing + 4;
     static constexpr int tmem_slot = bars + n_bars * 8;
     static constexpr int abort_flag = tmem_slot + 4;
     static constexpr int total = abort_flag + 4;
@@ -477,21 +530,25 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     float *hs_sm = reinterpret_cast<float *>(smem + BwdSmem::hs);
     float *g_sm = reinterpret_cast<float *>(smem + BwdSmem::g);
     float *rowsc = reinterpret_cast<float *>(smem + BwdSmem::rowsc);
-    float *da_sm = reinterpret_cast<float *>(smem + BwdSmem::da);
-    float *a_sm = reinterpret_cast<float *>(smem + BwdSmem::a);
+    float *cs_sm = reinterpret_cast<float *>(smem + BwdSmem::cs);
     float *p_sm = reinterpret_cast<float *>(smem + BwdSmem::pw);
+    float *wt_sm = reinterpret_cast<float *>(smem + BwdSmem::wt);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + BwdSmem::abort_flag);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + BwdSmem::tmem_slot);
     auto bar = [&](int i) { return sbase + BwdSmem::bars + i * 8; };
     constexpr int B_FULL = 0, B_EMPTY = kBwdStages, B_ACC_FULL = 2 * kBwdStages, B_ACC_EMPTY = B_ACC_FULL + 2,
-                  B_MAT_FULL = B_ACC_EMPTY + 2, B_MAT_EMPTY = B_MAT_FULL + 1;
+                  B_MAT_FULL = B_ACC_EMPTY + 2, B_MAT_EMPTY = B_MAT_FULL + 1, B_G = B_MAT_EMPTY + 1,
+                  B_STG_FULL = B_G + kRing, B_STG_EMPTY = B_STG_FULL + 2;
     constexpr uint32_t kTmemCols = 256;  // 2 stages x (Z | Lam) x 64 columns
 
     if (tid == 0) {
         for (int i = 0; i < kBwdStages; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiThreads); }
-        mbar_init(bar(B_MAT_FULL), 128);
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiWarps); }
+        mbar_init(bar(B_MAT_FULL), 4);
         mbar_init(bar(B_MAT_EMPTY), 1);
+        // carry ready: the two halves of the adjoint row and the two warps that fetch the saved state
+        for (int i = 0; i < kRing; ++i) mbar_init(bar(B_G + i), 4);
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_STG_FULL + i), kEpiWarps); mbar_init(bar(B_STG_EMPTY + i), 1); }
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tm_x);
@@ -510,7 +567,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
 
     const int64_t n_items = p.n_items;
-    auto decay_a = [&](float v) { return conv ? expf(v) : v; };
+    auto log2_decay = [&](float v) { return conv ? v * 1.4426950408889634f : log2f(v); };
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -536,6 +593,8 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         if (lane == 0) {
             uint32_t it = 0, mt = 0;
             int cur_head = -1;
+            const uint64_t a1d0 = make_desc_sw128(sbase + BwdSmem::mat_a1, 16, 1024);
+            const uint64_t ud0 = make_desc_sw128(sbase + BwdSmem::mat_u, 16, 1024);
             for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
                 const int hi = static_cast<int>((item / p.n_dtiles) % p.h);
                 for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
@@ -543,8 +602,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     const uint32_t ph = (it / kBwdStages) & 1;
                     const int acc = it & 1;
                     const uint32_t aph = (it >> 1) & 1;
-                    const bool new_mat = per_step || hi != cur_head;
-                    if (new_mat) {
+                    if (per_step || hi != cur_head) {
                         // single matrix buffer: hand it back to the builders once the MMAs issued so far are done
                         if (!per_step && mt > 0) umma_commit(bar(B_MAT_EMPTY));
                         if (!mbar_wait(bar(B_MAT_FULL), mt & 1, abort_flag, 12)) break;
@@ -554,20 +612,18 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 13)) break;
                     if (!mbar_wait(bar(B_ACC_EMPTY + acc), aph ^ 1, abort_flag, 14)) break;
                     tc_fence_after_sync();
-                    const uint32_t x_base = sbase + BwdSmem::xg + s * 2 * kTileBytes;
+                    const uint64_t xd0 = make_desc_sw128(sbase + BwdSmem::xg + s * 2 * kTileBytes, kTileBytes, 1024);
+                    const uint64_t gd0 = xd0 + (kTileBytes >> 4);
                     const uint32_t d_z = tmem_base + acc * 2 * DT, d_l = d_z + DT;
 #pragma unroll
                     for (int kb = 0; kb < QT / 16; ++kb) {
-                        const uint32_t koff = (kb >> 2) * (QT * 128) + (kb & 3) * 32;
-                        umma_bf16(d_z, make_desc_sw128(sbase + BwdSmem::mat_a1 + koff, 16, 1024),
-                                  make_desc_sw128(x_base + kb * 2048, kTileBytes, 1024), kIdesc, kb > 0 ? 1u : 0u);
+                        const uint32_t koff = ((kb >> 2) * (QT * 128) + (kb & 3) * 32) >> 4;
+                        umma_bf16(d_z, a1d0 + koff, xd0 + ((kb * 2048) >> 4), kIdesc, kb > 0 ? 1u : 0u);
                     }
 #pragma unroll
                     for (int kb = 0; kb < QT / 16; ++kb) {
-                        const uint32_t koff = (kb >> 2) * (QT * 128) + (kb & 3) * 32;
-                        umma_bf16(d_l, make_desc_sw128(sbase + BwdSmem::mat_u + koff, 16, 1024),
-                                  make_desc_sw128(x_base + kTileBytes + kb * 2048, kTileBytes, 1024), kIdesc,
-                                  kb > 0 ? 1u : 0u);
+                        const uint32_t koff = ((kb >> 2) * (QT * 128) + (kb & 3) * 32) >> 4;
+                        umma_bf16(d_l, ud0 + koff, gd0 + ((kb * 2048) >> 4), kIdesc, kb > 0 ? 1u : 0u);
                     }
                     umma_commit(bar(B_EMPTY + s));
                     umma_commit(bar(B_ACC_FULL + acc));
@@ -577,41 +633,45 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
     } else if (tid < kBuildThread0) {
         // ---------------- epilogue ----------------
-        // thread (q, lane, half): row m = 32 q + lane, channels [32 half, 32 half + 32) of the tile
+        // thread (q, lane, half): row m = 32 q + lane, channels [32 half, 32 half + 32) of the tile.
+        // The two threads of row 0 are the serial carry chain (the adjoint handed to the tile on the left).
         const int q = warp & 3;
         const int half = (warp - kEpiThread0 / 32) >> 2;
         const int m = q * 32 + lane;
         const int cb = half * 32;
-        const bool e0 = tid == kEpiThread0;
+        const bool loader = half == 0 && m < DT;  // warps (q = 0, 1; half 0): fetch the saved states
         uint32_t it = 0, mt = 0;
         int cur_head = -1;
         for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
             const int dtile = static_cast<int>(item % p.n_dtiles);
             const int64_t row = item / p.n_dtiles;
-            const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
+            const int hi = static_cast<int>(row % p.h);
             const int c0 = dtile * DT;
             const int64_t blk = row * p.n_dtiles + dtile;
-            const bool loader = half == 0 && m < DT;         // these 64 threads move per-channel vectors
             const bool ch_ok = loader && c0 + m < p.d;
-            // saved state of the first (rightmost) tile and the adjoint entering the sequence from the right
+            const float *ts_item = p.tile_states + row * p.n_tiles64 * p.d + c0 + m;
+            // the adjoint partial sums: [blk][half][t] (per-step) or 4 slots per 64-step block (per-head)
+            float *dap_step = p.da_partial + (blk * 2 + half) * (static_cast<int64_t>(p.n_tiles64) * 64);
+            float *dap_head = p.da_partial + p.head_partial_offset + blk * p.n_tiles64 * 4;
             float hs_next = 0.f;
             if (loader) {
-                hs_sm[(it & 1) * DT + m] =
-                    ch_ok ? p.tile_states[(row * p.n_tiles64 + 2 * (p.n_tiles - 1)) * p.d + c0 + m] : 0.f;
-                g_sm[(it & 1) * DT + m] = (p.dfinal_state && ch_ok) ? p.dfinal_state[row * p.d + c0 + m] : 0.f;
+                const int slot0 = it & (kRing - 1);
+                hs_sm[slot0 * DT + m] = ch_ok ? ts_item[static_cast<int64_t>(2 * (p.n_tiles - 1)) * p.d] : 0.f;
+                g_sm[slot0 * DT + m] = (p.dfinal_state && ch_ok) ? p.dfinal_state[row * p.d + c0 + m] : 0.f;
             }
             bar_sync(1, kEpiThreads);
+            if (m == 0) mbar_arrive(bar(B_G + (it & (kRing - 1))));
+            if (loader && lane == 0) mbar_arrive(bar(B_G + (it & (kRing - 1))));
             for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
-                const int acc = it & 1, par = it & 1;
-                const uint32_t aph = (it >> 1) & 1;
+                const int acc = it & 1, slot = it & (kRing - 1), nslot = (it + 1) & (kRing - 1), buf = it & 1;
+                const uint32_t aph = (it >> 1) & 1, gph = (it / kRing) & 1;
                 if (per_step || hi != cur_head) { cur_head = hi; ++mt; }
                 // prefetch the saved state of the next tile to the left while this one is being finished
-                if (loader && k > 0)
-                    hs_next = ch_ok ? p.tile_states[(row * p.n_tiles64 + 2 * (k - 1)) * p.d + c0 + m] : 0.f;
+                if (loader && k > 0) hs_next = ch_ok ? ts_item[static_cast<int64_t>(2 * (k - 1)) * p.d] : 0.f;
                 mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 15);
                 __syncwarp();
                 tc_fence_after_sync();
-                const float *rs = rowsc + ((mt - 1) & 3) * 4 * QT;
+                const float *rs = rowsc + ((mt - 1) & (kRing - 1)) * 4 * QT;
                 const float Eprev = rs[m], a_m = rs[3 * QT + m], p_m = rs[2 * QT + m];
                 // F: a time-invariant decay uses one Toeplitz table; the rightmost tile of the sequence stops at
                 // step L-1, where the adjoint entering from the right applies undamped
@@ -628,36 +688,63 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 tmem_ld32(taddr + DT, lam);
                 tmem_ld_wait();
                 tc_fence_before_sync();
-                mbar_arrive(bar(B_ACC_EMPTY + acc));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + acc));
 
-                const float *hin = hs_sm + par * DT + cb;
-                const float *gin = g_sm + par * DT + cb;
-                const int t = k * QT + m;
+                mbar_wait(bar(B_G + slot), gph, abort_flag, 16);
+                const float *hin = hs_sm + slot * DT + cb;
+                const float *gin = g_sm + slot * DT + cb;
+#pragma unroll
+                for (int c = 0; c < 32; c += 4) {
+                    const float4 gv = *reinterpret_cast<const float4 *>(gin + c);
+                    lam[c] = fmaf(F, gv.x, lam[c]);
+                    lam[c + 1] = fmaf(F, gv.y, lam[c + 1]);
+                    lam[c + 2] = fmaf(F, gv.z, lam[c + 2]);
+                    lam[c + 3] = fmaf(F, gv.w, lam[c + 3]);
+                }
+                if (k > 0) {
+                    // publish what the tile on the left needs: row 0 of the adjoint, and its saved state
+                    if (m == 0) {
+                        float *gout = g_sm + nslot * DT + cb;
+#pragma unroll
+                        for (int c = 0; c < 32; c += 4)
+                            *reinterpret_cast<float4 *>(gout + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
+                        mbar_arrive(bar(B_G + nslot));
+                    }
+                    if (loader) {
+                        hs_sm[nslot * DT + m] = hs_next;
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(B_G + nslot));
+                    }
+                } else if (m == 0 && p.dinit_state) {
+                    float *di = p.dinit_state + row * p.d + c0 + cb;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (c0 + cb + c < p.d) di[c] = a_m * lam[c];
+                }
                 float dacc = 0.f;
 #pragma unroll
                 for (int c = 0; c < 32; c += 4) {
                     const float4 hv = *reinterpret_cast<const float4 *>(hin + c);
-                    const float4 gv = *reinterpret_cast<const float4 *>(gin + c);
-                    z[c] = fmaf(Eprev, hv.x, z[c]);         lam[c] = fmaf(F, gv.x, lam[c]);
-                    z[c + 1] = fmaf(Eprev, hv.y, z[c + 1]); lam[c + 1] = fmaf(F, gv.y, lam[c + 1]);
-                    z[c + 2] = fmaf(Eprev, hv.z, z[c + 2]); lam[c + 2] = fmaf(F, gv.z, lam[c + 2]);
-                    z[c + 3] = fmaf(Eprev, hv.w, z[c + 3]); lam[c + 3] = fmaf(F, gv.w, lam[c + 3]);
+                    dacc = fmaf(lam[c], fmaf(Eprev, hv.x, z[c]), dacc);
+                    dacc = fmaf(lam[c + 1], fmaf(Eprev, hv.y, z[c + 1]), dacc);
+                    dacc = fmaf(lam[c + 2], fmaf(Eprev, hv.z, z[c + 2]), dacc);
+                    dacc = fmaf(lam[c + 3], fmaf(Eprev, hv.w, z[c + 3]), dacc);
                 }
+                const int t = k * QT + m;
+                if (conv) dacc *= a_m;
+                if (t >= L) dacc = 0.f;
+                if (per_step) {
+                    if (t < L) dap_step[t] = dacc;
+                } else {
+                    float wsum = dacc;
 #pragma unroll
-                for (int c = 0; c < 32; ++c) dacc = fmaf(lam[c], z[c], dacc);
-                if (m == 0) {  // row 0 of the adjoint is what the tile to the left receives
-                    float *gout = g_sm + (par ^ 1) * DT + cb;
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4)
-                        *reinterpret_cast<float4 *>(gout + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
-                    if (k == 0 && p.dinit_state) {
-                        float *di = p.dinit_state + row * p.d + c0 + cb;
-#pragma unroll
-                        for (int c = 0; c < 32; ++c)
-                            if (c0 + cb + c < p.d) di[c] = a_m * lam[c];
-                    }
+                    for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
+                    const int k64 = 2 * k + (q >> 1);
+                    if (lane == 0 && k64 < p.n_tiles64) dap_head[k64 * 4 + (q & 1) * 2 + half] = wsum;
                 }
-                uint8_t *stg = smem + BwdSmem::ostage + (it & 1) * kTileBytes;
+                mbar_wait(bar(B_STG_EMPTY + buf), aph ^ 1, abort_flag, 17);
+                uint8_t *stg = smem + BwdSmem::ostage + buf * kTileBytes;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint4 qv = make_uint4(pack_bf16x2(p_m * lam[8 * j], p_m * lam[8 * j + 1]),
@@ -666,58 +753,44 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                                                 pack_bf16x2(p_m * lam[8 * j + 6], p_m * lam[8 * j + 7]));
                     *reinterpret_cast<uint4 *>(stg + sw128_offset(m, half * 4 + j)) = qv;
                 }
-                if (conv) dacc *= a_m;
-                if (t >= L) dacc = 0.f;
-                if (per_step) {
-                    // the two column halves of a row meet in shared memory; half 0 writes the sum after the barrier
-                    if (half == 1) da_sm[par * QT + m] = dacc;
-                } else {
-                    float wsum = dacc;
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
-                    const int k64 = 2 * k + (q >> 1);
-                    if (lane == 0 && k64 < p.n_tiles64)
-                        p.da_partial[p.head_partial_offset + (blk * p.n_tiles64 + k64) * 4 + (q & 1) * 2 + half] = wsum;
-                }
-                if (loader) hs_sm[(par ^ 1) * DT + m] = hs_next;
                 fence_proxy_async();
-                if (e0) tma_store_wait_read<0>();
-                bar_sync(1, kEpiThreads);
-                if (e0) {
-                    tma_store_4d(&tm_o, sbase + BwdSmem::ostage + (it & 1) * kTileBytes, c0, hi, k * QT, bi);
-                    tma_store_commit();
-                }
-                // da_sm[par] is rewritten two tiles later, after everybody has passed the next barrier
-                if (per_step && half == 0 && t < L)
-                    p.da_partial[blk * (static_cast<int64_t>(p.n_tiles64) * 64) + t] = dacc + da_sm[par * QT + m];
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_STG_FULL + buf));
             }
         }
-        if (e0) tma_store_wait_all();
-    } else {
+    } else if (tid < kStoreThread) {
         // ---------------- matrix builders ----------------
         const int r = tid - kBuildThread0;
         uint32_t mt = 0;
         int cur_head = -1;
         const float diag = conv ? 0.f : -1.f;
-        auto build = [&](float a_r, float a_edge) {
-            // a_r: decay of step r of the tile; a_edge: decay of the step right after the tile
+        // v: raw decay value of step r of the tile; v_edge: of the step right after the tile (identity past L)
+        auto build = [&](float v, float v_edge) {
+            const float l2 = log2_decay(v);
+            builder_scan(l2, r, cs_sm, wt_sm);
+            const float pw = conv ? 1.f : 1.f - v;
+            p_sm[r] = pw;
             bar_sync(2, 128);
-            a_sm[r] = a_r;
-            p_sm[r] = conv ? 1.f : 1.f - a_r;
-            if (r == 0) a_sm[QT] = a_edge;
-            bar_sync(2, 128);
-            mbar_wait(bar(B_MAT_EMPTY), (mt & 1) ^ 1, abort_flag, 16);
-            const float Eprev = build_lower_row<1>(smem + BwdSmem::mat_a1, r, a_sm, p_sm, diag);
-            const float Fr = build_upper_row(smem + BwdSmem::mat_u, r, a_sm) * a_sm[QT];
-            float *rs = rowsc + (mt & 3) * 4 * QT;
+            RowChunks ca, cu;
+            compute_lower<1>(r, cs_sm, p_sm, diag, ca);
+            compute_upper(r, cs_sm, cu);
+            const float cs_r = cs_sm[r];
+            const float Eprev = exp2f(cs_r - l2);                       // prod_{j<r} a_j
+            const float Fr = exp2f(cs_sm[QT - 1] - cs_r + log2_decay(v_edge));
+            mbar_wait(bar(B_MAT_EMPTY), (mt & 1) ^ 1, abort_flag, 18);
+            store_chunks<false>(r, smem + BwdSmem::mat_a1, ca);
+            store_chunks<true>(r, smem + BwdSmem::mat_u, cu);
+            float *rs = rowsc + (mt & (kRing - 1)) * 4 * QT;
             rs[r] = Eprev;
             rs[QT + r] = Fr;
-            rs[2 * QT + r] = p_sm[r];
-            rs[3 * QT + r] = a_r;
+            rs[2 * QT + r] = pw;
+            rs[3 * QT + r] = conv ? exp2f(l2) : v;
             fence_proxy_async();
-            mbar_arrive(bar(B_MAT_FULL));
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(B_MAT_FULL));
             ++mt;
         };
+        const float ident = conv ? 0.f : 1.f;  // raw value of an identity step
         for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
             const int64_t row = item / p.n_dtiles;
             const int64_t bi = row / p.h, hi = row % p.h;
@@ -725,22 +798,40 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             if (!per_step) {
                 if (static_cast<int>(hi) != cur_head) {
                     cur_head = static_cast<int>(hi);
-                    const float a = decay_a(arow[0]);
-                    build(a, a);
+                    build(arow[0], arow[0]);
                 }
                 continue;
             }
-            auto load_a = [&](int t) { return (t >= 0 && t < L) ? decay_a(arow[static_cast<int64_t>(t) * p.a_sl]) : 1.f; };
-            float a_next = load_a((p.n_tiles - 1) * QT + r);
-            float edge_next = 1.f;  // decay of step n_tiles*128 >= L
+            auto load_v = [&](int t) { return (t >= 0 && t < L) ? arow[static_cast<int64_t>(t) * p.a_sl] : ident; };
+            float v_next = load_v((p.n_tiles - 1) * QT + r);
+            float edge_next = ident;  // step n_tiles*128 is past the end
             for (int k = p.n_tiles - 1; k >= 0; --k) {
-                const float a = a_next, edge = edge_next;
+                const float v = v_next, edge = edge_next;
                 if (k > 0) {
-                    a_next = load_a((k - 1) * QT + r);
-                    edge_next = load_a(k * QT);
+                    v_next = load_v((k - 1) * QT + r);
+                    edge_next = load_v(k * QT);
                 }
-                build(a, edge);
+                build(v, edge);
             }
+        }
+    } else {
+        // ---------------- TMA store issuer ----------------
+        if (tid == kStoreThread) {
+            uint32_t it = 0;
+            for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
+                const int dtile = static_cast<int>(item % p.n_dtiles);
+                const int64_t row = item / p.n_dtiles;
+                const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
+                for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
+                    const int buf = it & 1;
+                    if (!mbar_wait(bar(B_STG_FULL + buf), (it >> 1) & 1, abort_flag, 19)) break;
+                    tma_store_4d(&tm_o, sbase + BwdSmem::ostage + buf * kTileBytes, dtile * DT, hi, k * QT, bi);
+                    tma_store_commit();
+                    tma_store_wait_read<0>();
+                    mbar_arrive(bar(B_STG_EMPTY + buf));
+                }
+            }
+            tma_store_wait_all();
         }
     }
 
