@@ -47,8 +47,8 @@ def _problem(**kw):
 
 def test_host_only_queries(ema_lib):
     p = _problem()
-    assert ema_lib.ema_b200_tile_steps(ctypes.byref(p)) == 64
-    assert ema_lib.ema_b200_tile_states_bytes(ctypes.byref(p)) == 4 * 4 * 64 * 4
+    assert ema_lib.ema_b200_tile_steps(ctypes.byref(p)) == 128
+    assert ema_lib.ema_b200_tile_states_bytes(ctypes.byref(p)) == 4 * 2 * 64 * 4
     assert ema_lib.ema_b200_bwd_workspace_bytes(ctypes.byref(p)) >= 4 * 256 * 4
     bad = _problem(dtype=7)
     assert ema_lib.ema_b200_tile_steps(ctypes.byref(bad)) == 0

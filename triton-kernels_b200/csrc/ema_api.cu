@@ -108,7 +108,9 @@ extern "C" size_t ema_b200_bwd_workspace_bytes(const ema_b200_problem *p) {
     if (check_problem(p) != EMA_OK) return 0;
     // sized for the narrowest channel tile (vec = 1) so that it never depends on pointer alignment
     const int64_t n_tiles = (p->L + kFmaTile - 1) / kFmaTile;
-    const int64_t n_dtiles = (p->d + kFmaCT - 1) / kFmaCT;
+    int64_t n_dtiles = (p->d + kFmaCT - 1) / kFmaCT;
+    const int64_t tc_slices = 2 * ((p->d + 127) / 128);  // the tensor-core kernel's slices per row
+    if (tc_slices > n_dtiles) n_dtiles = tc_slices;
     const int64_t rows = p->b * p->h;
     const int64_t per_step = rows * n_dtiles * n_tiles * kFmaTile;
     const int64_t per_head = kHeadPartialOffset(rows) + rows * n_dtiles * n_tiles * (kFmaThreads / 32);
@@ -210,8 +212,12 @@ extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const floa
         rc = launch_fused_bwd_tc(fp, st);
         if (rc && rc != EMA_ERR_UNSUPPORTED) return rc;
         done = rc == EMA_OK;
-        // the tensor-core kernel keeps the two 32-channel halves of a tile apart in the per-step partial sums
-        if (done && p->decay_mode == EMA_DECAY_PER_STEP) fp.n_dtiles *= 2;
+        // partial-sum slices of the tensor-core kernel: per 128-channel tile, two halves (per-step decay) or one
+        // block of four per 64 steps (per-head decay)
+        if (done) {
+            const int tc_dtiles = static_cast<int>((p->d + 127) / 128);
+            fp.n_dtiles = p->decay_mode == EMA_DECAY_PER_STEP ? 2 * tc_dtiles : tc_dtiles;
+        }
     }
     if (!done) {
         rc = launch_fused_bwd_fma(fp, p->dtype, vec, st);

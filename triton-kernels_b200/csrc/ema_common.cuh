@@ -144,12 +144,12 @@ inline int check_launch() {
     return EMA_OK;
 }
 
-// geometry of the FMA kernels: 128 threads = NS sub-blocks x CT channel threads
-constexpr int kFmaThreads = 128;
+// geometry of the FMA kernels: 256 threads = NS sub-blocks x CT channel threads
+constexpr int kFmaThreads = 256;
 constexpr int kFmaCT = 16;
 constexpr int kFmaSB = 8;
 constexpr int kFmaNS = kFmaThreads / kFmaCT;
-constexpr int kFmaTile = kFmaNS * kFmaSB;  // 64 time steps per tile
+constexpr int kFmaTile = kFmaNS * kFmaSB;  // 128 time steps per tile, like the tensor-core path
 
 // per-head decay gradient workspace: [rows doubles of row sums][partials], the partials starting
 // at this float offset (kept 16-byte aligned)

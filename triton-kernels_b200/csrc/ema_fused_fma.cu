@@ -3,7 +3,7 @@
 // This is the exact path: fp32 inputs (which must meet a 1e-4 absolute tolerance, out of reach of
 // a bf16/tf32 tensor-core contraction) and every shape or alignment the tensor-core path does not
 // take.  A CTA owns one scan row (b,h) and DT = 16*VEC channels and walks the sequence in tiles of
-// 64 steps.  Inside a tile the 128 threads form 8 sub-blocks of 8 steps x 16 channel threads:
+// 128 steps.  Inside a tile the 256 threads form 16 sub-blocks of 8 steps x 16 channel threads:
 //   phase 1  every sub-block scans its 8 steps from a zero state (local state S, decay product P)
 //   carry    state entering sub-block j = fold of (P_i, S_i), i < j, onto the state entering the tile
 //   phase 2  every sub-block re-runs its 8 steps from its true entering state and writes the result

@@ -4,38 +4,45 @@
 //     y_m = sum_{k<=m} p_k (prod_{j=k+1..m} a_j) x_k  +  (prod_{j<=m} a_j) h
 // i.e. Y = G X + E h^T with G a 128x128 lower-triangular matrix that depends on the decays only and is
 // shared by all channels.  G is written to shared memory as bf16 (K-major, 128-byte swizzle), the x
-// tile [128 steps x 64 channels] lands next to it by TMA exactly as the MMA wants its B operand
-// (MN-major, 128-byte swizzle), tcgen05.mma accumulates Y in TMEM (fp32), and the epilogue warps add
-// the carry term in fp32, hand the last row on as the next carry, and bf16 y leaves by TMA store.
+// tile [128 steps x 128 channels] lands next to it by TMA as two 64-channel blocks, exactly as the MMA
+// wants its B operand (MN-major, 128-byte swizzle), tcgen05.mma accumulates Y in TMEM (fp32), and the
+// epilogue warps add the carry term in fp32, hand the last row on as the next carry, and bf16 y leaves by
+// TMA store from the very shared-memory stage the x tile arrived in.
 //
-// One persistent CTA per SM walks its work items (scan row, 64-channel tile) and, inside an item, the
+// Why 128 channels per MMA: one M=128, K=16 tcgen05.mma costs about 120 cycles whatever N <= 128 is, and
+// a tile needs K = 128, i.e. 8 of them per product; at N = 64 that alone exceeds the time HBM needs to
+// move the tile.
+//
+// One persistent CTA per SM walks its work items (scan row, 128-channel tile) and, inside an item, the
 // tiles in sequence order.  15 warps, each with one job:
 //   warp 0      TMA producer (x tiles, and dy tiles in the backward) into a ring of stages
 //   warp 1      MMA issuer; owns the TMEM allocation
-//   warps 2-9   epilogue: TMEM lane quadrant (warp % 4) x one half of the 64 channels
+//   warps 2-9   epilogue: TMEM lane quadrant (warp % 4) x one half of the 128 channels
 //   warps 10-13 build the decay matrices (once per head for a time-invariant decay, per tile otherwise)
-//   warp 14     issues the TMA stores of finished tiles
+//   warp 14     issues the TMA stores of finished tiles and hands the stages back to the producer
 // The warps meet only through mbarriers: stage full/empty, accumulator full/empty, matrix full/empty,
 // carry ready (a ring of 4 so that the warp on the serial carry chain can run ahead of the others), and
-// staging full/empty.  Every wait is bounded (ema_tc_common.cuh): after a timeout the roles run their
-// loops to the end without waiting, the CTA tears down normally and the host sees EMA_ERR_TIMEOUT.
+// stage staged.  Every wait is bounded (ema_tc_common.cuh): after a timeout the roles run their loops to
+// the end without waiting, the CTA tears down normally and the host sees EMA_ERR_TIMEOUT.
 #include "ema_common.cuh"
 #include "ema_tc_common.cuh"
 
 namespace ema {
 namespace tc {
 
-constexpr int QT = 128;              // steps per tile = MMA M = MMA K extent
-constexpr int DT = 64;               // channels per tile = MMA N
-constexpr int kTileBytes = QT * DT * 2;
+constexpr int QT = 128;                    // steps per tile = MMA M = MMA K extent
+constexpr int DT = 128;                    // channels per tile = MMA N
+constexpr int kBlockCols = 64;             // channels per 128-byte-swizzled block (one TMA box)
+constexpr int kBlockBytes = QT * 128;      // [128 steps x 64 channels] bf16
+constexpr int kTileBytes = 2 * kBlockBytes;
 constexpr int kMatBytes = QT * QT * 2;
-constexpr int kThreads = 480;        // 15 warps
-constexpr int kEpiThread0 = 64;      // warps 2-9
+constexpr int kThreads = 480;              // 15 warps
+constexpr int kEpiThread0 = 64;            // warps 2-9
 constexpr int kEpiThreads = 256;
 constexpr int kEpiWarps = kEpiThreads / 32;
-constexpr int kBuildThread0 = 320;   // warps 10-13
-constexpr int kStoreThread = 448;    // warp 14, lane 0
-constexpr int kRing = 4;             // depth of the carry ring and of the per-row scalar tables
+constexpr int kBuildThread0 = 320;         // warps 10-13
+constexpr int kStoreThread = 448;          // warp 14, lane 0
+constexpr int kRing = 4;                   // depth of the carry ring and of the per-row scalar tables
 constexpr uint32_t kIdesc = make_idesc_bf16(QT, DT, 0, 1);
 
 // named barriers (id 0 is __syncthreads)
@@ -63,14 +70,13 @@ struct RowChunks {
     uint4 v[kMaxChunks];
 };
 
-// Calls f(row, chunk) for this thread's chunks, in a fixed order; returns their number.
+// Calls f(register slot, row, chunk) for this thread's chunks, in a fixed order.
 template <bool UPPER, typename F>
-__device__ __forceinline__ int for_my_chunks(int t, F f) {
+__device__ __forceinline__ void for_my_chunks(int t, F f) {
     const int pr = t & 63, sel = t >> 6;
     const int row_long = UPPER ? pr : 127 - pr;   // the row of the pair with more chunks
     const int row_short = 127 - row_long;
     const int n_long = UPPER ? 16 - (row_long >> 3) : (row_long >> 3) + 1;
-    int n = 0;
 #pragma unroll
     for (int s = 0; s < kMaxChunks; ++s) {   // s is a compile-time register index; i the position in the 17-chunk list
         const int i = 2 * s + sel;
@@ -80,24 +86,26 @@ __device__ __forceinline__ int for_my_chunks(int t, F f) {
         const int j = in_long ? i : i - n_long;                       // index inside the row's chunk list
         const int chunk = UPPER ? (row >> 3) + j : j;
         f(s, row, chunk);
-        ++n;
     }
-    return n;
 }
 
+// cs_sm and p_sm are 16-byte aligned; a chunk is 8 consecutive k, i.e. two float4 of each table.
 template <int SHIFT>
 __device__ __forceinline__ void compute_lower(int t, const float *cs_sm, const float *p_sm, float diag, RowChunks &out) {
     for_my_chunks<false>(t, [&](int n, int m, int c) {
         const float cm = (m - SHIFT >= 0) ? cs_sm[m - SHIFT] : 0.f;
         const int top = m - SHIFT;
+        const float4 ca = *reinterpret_cast<const float4 *>(cs_sm + c * 8), cb = *reinterpret_cast<const float4 *>(cs_sm + c * 8 + 4);
+        const float4 pa = *reinterpret_cast<const float4 *>(p_sm + c * 8), pb = *reinterpret_cast<const float4 *>(p_sm + c * 8 + 4);
+        const float cs8[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
+        const float p8[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
         float v[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const int k = c * 8 + e;
-            float val = 0.f;
-            if (k <= top) val = p_sm[k] * ex2_approx(cm - cs_sm[k]);
-            else if (SHIFT == 1 && k == m) val = diag;
-            v[e] = val;
+            // past the diagonal the exponent is positive: clamp it so that the discarded value stays finite
+            const float g = p8[e] * ex2_approx(fminf(cm - cs8[e], 0.f));
+            v[e] = (k <= top) ? g : ((SHIFT == 1 && k == m) ? diag : 0.f);
         }
         out.v[n] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
                               pack_bf16x2(v[6], v[7]));
@@ -106,11 +114,14 @@ __device__ __forceinline__ void compute_lower(int t, const float *cs_sm, const f
 __device__ __forceinline__ void compute_upper(int t, const float *cs_sm, RowChunks &out) {
     for_my_chunks<true>(t, [&](int n, int m, int c) {
         const float cm = cs_sm[m];
+        const float4 ca = *reinterpret_cast<const float4 *>(cs_sm + c * 8), cb = *reinterpret_cast<const float4 *>(cs_sm + c * 8 + 4);
+        const float cs8[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
         float v[8];
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const int k = c * 8 + e;
-            v[e] = (k >= m) ? ex2_approx(cs_sm[k] - cm) : 0.f;
+            const float g = ex2_approx(fminf(cs8[e] - cm, 0.f));
+            v[e] = (k >= m) ? g : 0.f;
         }
         out.v[n] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
                               pack_bf16x2(v[6], v[7]));
@@ -142,6 +153,17 @@ __device__ __forceinline__ void builder_scan(float v, int r, float *cs_sm, float
     cs_sm[r] = v + off;
 }
 
+// dst[0..min(32, n_valid)) = y; deliberately not inlined (see the forward epilogue)
+__device__ __noinline__ void store_row32(float *dst, const float (&y)[32], int n_valid) {
+#pragma unroll
+    for (int c = 0; c < 32; ++c)
+        if (c < n_valid) dst[c] = y[c];
+}
+
+// MMA descriptors of a [128 steps x 128 channels] tile: two 64-channel blocks kBlockBytes apart (LBO),
+// 8-step groups 1024 bytes apart (SBO); K step kb starts 16 rows = 2048 bytes further down.
+__device__ __forceinline__ uint64_t tile_desc(uint32_t addr) { return make_desc_sw128(addr, kBlockBytes, 1024); }
+
 struct TcParams {
     const float *decay;
     float *chunk_states, *tile_states, *final_state, *log_decay_sum;
@@ -149,8 +171,7 @@ struct TcParams {
     int64_t b, L, h, d;
     int64_t a_sb, a_sl, a_sh;
     int decay_mode, convention, chunk;
-    int n_tiles;      // 128-step tiles
-    int n_tiles64;    // saved states per row (64-step granularity, shared with the CUDA-core path)
+    int n_tiles;      // 128-step tiles; one saved state per tile and row (layout shared with the CUDA-core path)
     int n_dtiles, n_items;
     int64_t n_chunks;
 };
@@ -158,20 +179,19 @@ struct TcParams {
 // ---------------------------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------------------------
-constexpr int kFwdStages = 6;
+constexpr int kFwdStages = 4;
 constexpr int kFwdMatBufs = 2;
 struct FwdSmem {
     static constexpr int mat = 0;
-    static constexpr int x = mat + kFwdMatBufs * kMatBytes;
-    static constexpr int ystage = x + kFwdStages * kTileBytes;
-    static constexpr int h = ystage + 2 * kTileBytes;        // float[kRing][64] carry entering a tile
-    static constexpr int e = h + kRing * DT * 4;              // float[kRing][128] E_m per build
-    static constexpr int cs = e + kRing * QT * 4;             // float[128] cumulative log2 decay
-    static constexpr int pw = cs + QT * 4;                    // float[128] input weights
-    static constexpr int wt = pw + QT * 4;                    // float[4] scan scratch
+    static constexpr int x = mat + kFwdMatBufs * kMatBytes;   // stages: x tile in, y tile out
+    static constexpr int h = x + kFwdStages * kTileBytes;     // float[kRing][128] carry entering a tile
+    static constexpr int e = h + kRing * DT * 4;               // float[kRing][128] E_m per build
+    static constexpr int cs = e + kRing * QT * 4;              // float[128] cumulative log2 decay
+    static constexpr int pw = cs + QT * 4;                     // float[128] input weights
+    static constexpr int wt = pw + QT * 4;                     // float[4] scan scratch
     static constexpr int bars = wt + 16;
-    // stage full/empty, acc full/empty, matrix full/empty, carry ready, staging full/empty
-    static constexpr int n_bars = 2 * kFwdStages + 4 + 2 * kFwdMatBufs + kRing + 4;
+    // stage full/empty/staged, acc full/empty, matrix full/empty, carry ready
+    static constexpr int n_bars = 3 * kFwdStages + 4 + 2 * kFwdMatBufs + kRing;
     static constexpr int tmem_slot = bars + n_bars * 8;
     static constexpr int abort_flag = tmem_slot + 4;
     static constexpr int total = abort_flag + 4;
@@ -198,16 +218,20 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + FwdSmem::abort_flag);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + FwdSmem::tmem_slot);
     auto bar = [&](int i) { return sbase + FwdSmem::bars + i * 8; };
-    constexpr int B_FULL = 0, B_EMPTY = kFwdStages, B_ACC_FULL = 2 * kFwdStages, B_ACC_EMPTY = B_ACC_FULL + 2,
-                  B_MAT_FULL = B_ACC_EMPTY + 2, B_MAT_EMPTY = B_MAT_FULL + kFwdMatBufs,
-                  B_H = B_MAT_EMPTY + kFwdMatBufs, B_STG_FULL = B_H + kRing, B_STG_EMPTY = B_STG_FULL + 2;
+    constexpr int B_FULL = 0, B_EMPTY = kFwdStages, B_STAGED = 2 * kFwdStages, B_ACC_FULL = 3 * kFwdStages,
+                  B_ACC_EMPTY = B_ACC_FULL + 2, B_MAT_FULL = B_ACC_EMPTY + 2, B_MAT_EMPTY = B_MAT_FULL + kFwdMatBufs,
+                  B_H = B_MAT_EMPTY + kFwdMatBufs;
+    constexpr uint32_t kTmemCols = 2 * DT;
 
     if (tid == 0) {
-        for (int i = 0; i < kFwdStages; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
+        for (int i = 0; i < kFwdStages; ++i) {
+            mbar_init(bar(B_FULL + i), 1);
+            mbar_init(bar(B_EMPTY + i), 1);
+            mbar_init(bar(B_STAGED + i), kEpiWarps);
+        }
         for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiWarps); }
         for (int i = 0; i < kFwdMatBufs; ++i) { mbar_init(bar(B_MAT_FULL + i), 4); mbar_init(bar(B_MAT_EMPTY + i), 1); }
         for (int i = 0; i < kRing; ++i) mbar_init(bar(B_H + i), 2);           // one arrival per channel half
-        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_STG_FULL + i), kEpiWarps); mbar_init(bar(B_STG_EMPTY + i), 1); }
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tm_x);
@@ -217,7 +241,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     for (int i = tid; i < kFwdMatBufs * kMatBytes / 16; i += kThreads)
         reinterpret_cast<uint4 *>(smem + FwdSmem::mat)[i] = make_uint4(0u, 0u, 0u, 0u);
     if (warp == 1) {
-        tmem_alloc(sbase + FwdSmem::tmem_slot, 128);
+        tmem_alloc(sbase + FwdSmem::tmem_slot, kTmemCols);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -242,7 +266,9 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     const uint32_t ph = (it / kFwdStages) & 1;
                     if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 1)) break;
                     mbar_expect_tx(bar(B_FULL + s), kTileBytes);
-                    tma_load_4d(sbase + FwdSmem::x + s * kTileBytes, &tm_x, bar(B_FULL + s), dtile * DT, hi, k * QT, bi);
+                    const uint32_t dst = sbase + FwdSmem::x + s * kTileBytes;
+                    tma_load_4d(dst, &tm_x, bar(B_FULL + s), dtile * DT, hi, k * QT, bi);
+                    tma_load_4d(dst + kBlockBytes, &tm_x, bar(B_FULL + s), dtile * DT + kBlockCols, hi, k * QT, bi);
                 }
             }
         }
@@ -273,7 +299,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     if (!mbar_wait(bar(B_ACC_EMPTY + acc), aph ^ 1, abort_flag, 4)) break;
                     tc_fence_after_sync();
                     const uint64_t ad0 = make_desc_sw128(sbase + FwdSmem::mat + mb_cur * kMatBytes, 16, 1024);
-                    const uint64_t bd0 = make_desc_sw128(sbase + FwdSmem::x + s * kTileBytes, kTileBytes, 1024);
+                    const uint64_t bd0 = tile_desc(sbase + FwdSmem::x + s * kTileBytes);
 #pragma unroll
                     for (int kb = 0; kb < QT / 16; ++kb) {
                         // descriptor start addresses are in 16-byte units: next K step inside / across 64-wide K blocks
@@ -281,7 +307,6 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         const uint64_t bd = bd0 + ((kb * 2048) >> 4);
                         umma_bf16(tmem_base + acc * DT, ad, bd, kIdesc, kb > 0 ? 1u : 0u);
                     }
-                    umma_commit(bar(B_EMPTY + s));
                     umma_commit(bar(B_ACC_FULL + acc));
                     if (per_step) umma_commit(bar(B_MAT_EMPTY + mb_cur));
                 }
@@ -289,14 +314,14 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
     } else if (tid < kBuildThread0) {
         // ---------------- epilogue ----------------
-        // Thread (q, lane, half) owns row m = 32 q + lane and channels [32 half, 32 half + 32) of the tile.
-        // The two threads of row 127 are the serial carry chain: they publish the state entering the next
-        // tile as soon as they have it; nobody else waits for anything but that state and the accumulator.
+        // Thread (q, lane, half) owns row m = 32 q + lane and channels [64 half, 64 half + 64) of the tile,
+        // handled 32 at a time.  The two threads of row 127 are the serial carry chain: they publish the
+        // state entering the next tile as soon as they have it; nobody else waits for anything but that
+        // state and the accumulator.
         const int q = warp & 3;
         const int half = (warp - kEpiThread0 / 32) >> 2;
         const int m = q * 32 + lane;
-        const int cb = half * 32;
-        const bool loader = half == 0 && m < DT;   // 64 threads that move per-channel vectors
+        const bool loader = half == 0;   // 128 threads that move per-channel vectors: thread m <-> channel m
         uint32_t it = 0, mt = 0;
         int cur_head = -1;
         for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
@@ -305,7 +330,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const int hi = static_cast<int>(row % p.h);
             const int c0 = dtile * DT;
             const bool ch_ok = loader && c0 + m < p.d;
-            float *ts_item = p.tile_states ? p.tile_states + row * p.n_tiles64 * p.d + c0 : nullptr;
+            float *ts_item = p.tile_states ? p.tile_states + row * p.n_tiles * p.d + c0 : nullptr;
             if (loader) {
                 const float v = (p.init_state && ch_ok) ? p.init_state[row * p.d + c0 + m] : 0.f;
                 h_sm[(it & (kRing - 1)) * DT + m] = v;
@@ -314,73 +339,73 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             bar_sync(1, kEpiThreads);  // once per item: the previous item is finished everywhere, the state is in place
             if (m == QT - 1) mbar_arrive(bar(B_H + (it & (kRing - 1))));
             for (int k = 0; k < p.n_tiles; ++k, ++it) {
-                const int acc = it & 1, slot = it & (kRing - 1), buf = it & 1;
+                const int acc = it & 1, slot = it & (kRing - 1), s = it % kFwdStages;
                 const uint32_t aph = (it >> 1) & 1, hph = (it / kRing) & 1;
                 if (per_step || hi != cur_head) { cur_head = hi; ++mt; }
-                mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 5);
-                __syncwarp();  // the polling loop may leave the lanes diverged; tcgen05.ld is warp-collective
+                if (lane == 0) mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 5);  // one poller per warp
+                __syncwarp();
                 tc_fence_after_sync();
                 const float E = e_sm[((mt - 1) & (kRing - 1)) * QT + m];
-                float y[32];
-                tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * DT + cb, y);
-                tmem_ld_wait();
-                tc_fence_before_sync();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * DT + half * 64;
+                if (lane == 0) mbar_wait(bar(B_H + slot), hph, abort_flag, 6);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + acc));  // one arrival per warp
-
-                mbar_wait(bar(B_H + slot), hph, abort_flag, 6);
                 const float *hin = h_sm + slot * DT;
-#pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    const float4 hv = *reinterpret_cast<const float4 *>(hin + cb + c);
-                    y[c] = fmaf(E, hv.x, y[c]);
-                    y[c + 1] = fmaf(E, hv.y, y[c + 1]);
-                    y[c + 2] = fmaf(E, hv.z, y[c + 2]);
-                    y[c + 3] = fmaf(E, hv.w, y[c + 3]);
-                }
-                if (m == QT - 1 && k + 1 < p.n_tiles) {  // the last row is the state entering the next tile
-                    float *hout = h_sm + ((it + 1) & (kRing - 1)) * DT + cb;
-#pragma unroll
-                    for (int c = 0; c < 32; c += 4)
-                        *reinterpret_cast<float4 *>(hout + c) = make_float4(y[c], y[c + 1], y[c + 2], y[c + 3]);
-                    mbar_arrive(bar(B_H + ((it + 1) & (kRing - 1))));
-                }
                 const int t = k * QT + m;
-                // saved states at 64-step granularity: entering state (slot 2k) and state after row 63 (slot 2k+1)
-                if (ts_item) {
-                    if (ch_ok) ts_item[static_cast<int64_t>(2 * k) * p.d + m] = hin[m];
-                    if (m == 63 && 2 * k + 1 < p.n_tiles64) {
-                        float *ts = ts_item + static_cast<int64_t>(2 * k + 1) * p.d + cb;
+                // ACC_FULL says the MMAs have finished reading the x tile: its stage now takes the y tile
+                uint8_t *stg = smem + FwdSmem::x + s * kTileBytes + half * kBlockBytes;
 #pragma unroll
-                        for (int c = 0; c < 32; c += 4)   // d is a multiple of 8: a float4 is all inside or all outside
-                            if (c0 + cb + c < p.d)
-                                *reinterpret_cast<float4 *>(ts + c) = make_float4(y[c], y[c + 1], y[c + 2], y[c + 3]);
+                for (int pass = 0; pass < 2; ++pass) {
+                    float y[32];
+                    __syncwarp();  // single-thread branches of the previous pass have rejoined
+                    tmem_ld32(taddr + pass * 32, y);
+                    tmem_ld_wait();
+                    if (pass == 1) {
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + acc));  // one arrival per warp
+                    }
+                    const int cb = half * 64 + pass * 32;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        const float4 hv = *reinterpret_cast<const float4 *>(hin + cb + c);
+                        y[c] = fmaf(E, hv.x, y[c]);
+                        y[c + 1] = fmaf(E, hv.y, y[c + 1]);
+                        y[c + 2] = fmaf(E, hv.z, y[c + 2]);
+                        y[c + 3] = fmaf(E, hv.w, y[c + 3]);
+                    }
+                    if (m == QT - 1 && k + 1 < p.n_tiles) {  // the last row is the state entering the next tile
+                        float *hout = h_sm + ((it + 1) & (kRing - 1)) * DT + cb;
+#pragma unroll
+                        for (int c = 0; c < 32; c += 4)
+                            *reinterpret_cast<float4 *>(hout + c) = make_float4(y[c], y[c + 1], y[c + 2], y[c + 3]);
+                        if (pass == 1) mbar_arrive(bar(B_H + ((it + 1) & (kRing - 1))));
+                    }
+                    // rare side outputs (a chunk boundary, the last step): kept out of line so that they do not
+                    // cost the common path registers
+                    const bool at_chunk_end = p.chunk_states && t + 1 < L && (t + 1) % p.chunk == 0;
+                    const bool at_last_step = p.final_state && t == L - 1;
+                    if (at_chunk_end || at_last_step) {
+                        float tmp[32];  // a copy, so that y itself never has its address taken and stays in registers
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) tmp[c] = y[c];
+                        const int n_valid = static_cast<int>(p.d) - (c0 + cb);
+                        if (at_chunk_end)
+                            store_row32(p.chunk_states + (row * p.n_chunks + (t + 1) / p.chunk) * p.d + c0 + cb, tmp, n_valid);
+                        if (at_last_step) store_row32(p.final_state + row * p.d + c0 + cb, tmp, n_valid);
+                    }
+                    // bf16 -> the stage, in the TMA's 128-byte swizzle
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 qv = make_uint4(pack_bf16x2(y[8 * j], y[8 * j + 1]), pack_bf16x2(y[8 * j + 2], y[8 * j + 3]),
+                                                    pack_bf16x2(y[8 * j + 4], y[8 * j + 5]), pack_bf16x2(y[8 * j + 6], y[8 * j + 7]));
+                        *reinterpret_cast<uint4 *>(stg + sw128_offset(m, pass * 4 + j)) = qv;
                     }
                 }
-                if (p.chunk_states && t + 1 < L && (t + 1) % p.chunk == 0) {
-                    float *cs = p.chunk_states + (row * p.n_chunks + (t + 1) / p.chunk) * p.d + c0 + cb;
-#pragma unroll
-                    for (int c = 0; c < 32; ++c)
-                        if (c0 + cb + c < p.d) cs[c] = y[c];
-                }
-                if (p.final_state && t == L - 1) {
-                    float *fs = p.final_state + row * p.d + c0 + cb;
-#pragma unroll
-                    for (int c = 0; c < 32; ++c)
-                        if (c0 + cb + c < p.d) fs[c] = y[c];
-                }
-                // bf16 half-row -> staging buffer in the TMA's 128-byte swizzle, once the store of two tiles ago has read it
-                mbar_wait(bar(B_STG_EMPTY + buf), aph ^ 1, abort_flag, 7);
-                uint8_t *stg = smem + FwdSmem::ystage + buf * kTileBytes;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint4 qv = make_uint4(pack_bf16x2(y[8 * j], y[8 * j + 1]), pack_bf16x2(y[8 * j + 2], y[8 * j + 3]),
-                                                pack_bf16x2(y[8 * j + 4], y[8 * j + 5]), pack_bf16x2(y[8 * j + 6], y[8 * j + 7]));
-                    *reinterpret_cast<uint4 *>(stg + sw128_offset(m, half * 4 + j)) = qv;
-                }
+                // state entering the tile -> saved state k, one coalesced line per 32 threads
+                if (ts_item && ch_ok) ts_item[static_cast<int64_t>(k) * p.d + m] = hin[m];
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_STG_FULL + buf));
+                if (lane == 0) mbar_arrive(bar(B_STAGED + s));
             }
         }
     } else if (tid < kStoreThread) {
@@ -397,7 +422,8 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             RowChunks g;
             compute_lower<0>(r, cs_sm, p_sm, 0.f, g);
             const float E = exp2f(cs_sm[r]);
-            mbar_wait(bar(B_MAT_EMPTY + mb), ((mt / kFwdMatBufs) & 1) ^ 1, abort_flag, 8);
+            if (lane == 0) mbar_wait(bar(B_MAT_EMPTY + mb), ((mt / kFwdMatBufs) & 1) ^ 1, abort_flag, 8);
+            __syncwarp();
             store_chunks<false>(r, smem + FwdSmem::mat + mb * kMatBytes, g);
             e_sm[(mt & (kRing - 1)) * QT + r] = E;
             fence_proxy_async();
@@ -443,13 +469,16 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 const int dtile = static_cast<int>(item % p.n_dtiles);
                 const int64_t row = item / p.n_dtiles;
                 const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
+                const bool two = dtile * DT + kBlockCols < p.d;   // the second 64-channel block exists
                 for (int k = 0; k < p.n_tiles; ++k, ++it) {
-                    const int buf = it & 1;
-                    if (!mbar_wait(bar(B_STG_FULL + buf), (it >> 1) & 1, abort_flag, 9)) break;
-                    tma_store_4d(&tm_y, sbase + FwdSmem::ystage + buf * kTileBytes, dtile * DT, hi, k * QT, bi);
+                    const int s = it % kFwdStages;
+                    if (!mbar_wait(bar(B_STAGED + s), (it / kFwdStages) & 1, abort_flag, 9)) break;
+                    const uint32_t src = sbase + FwdSmem::x + s * kTileBytes;
+                    tma_store_4d(&tm_y, src, dtile * DT, hi, k * QT, bi);
+                    if (two) tma_store_4d(&tm_y, src + kBlockBytes, dtile * DT + kBlockCols, hi, k * QT, bi);
                     tma_store_commit();
-                    tma_store_wait_read<0>();          // the staging buffer has been read: hand it back
-                    mbar_arrive(bar(B_STG_EMPTY + buf));
+                    tma_store_wait_read<0>();          // the stage has been read: hand it back to the producer
+                    mbar_arrive(bar(B_EMPTY + s));
                 }
             }
             tma_store_wait_all();
@@ -467,7 +496,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     if (warp == 1) {
         __syncwarp();
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, 128);
+        tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 
@@ -481,7 +510,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 // A1[m,k] = p_k prod_{j=k+1..m-1} a_j (k < m), A1[m,m] = -1 | 0;  U[m,k] = prod_{j=m+1..k} a_j (k >= m);
 // Eprev_m = prod_{j<m} a_j;  F_m = prod_{j=m+1..128} a_j (a_128 = first decay of the next tile, 1 past L).
 // Then dx_m = p_m Lam_m, ddecay_m = sum_c Lam_mc Z_mc (times a_m for the log-decay convention), and row 0
-// of Lam is the adjoint handed to the previous tile.
+// of Lam is the adjoint handed to the previous tile.  dx leaves from the stage the dy tile arrived in.
 struct TcBwdParams {
     const float *decay;
     const float *tile_states;
@@ -491,24 +520,23 @@ struct TcBwdParams {
     int64_t b, L, h, d;
     int64_t a_sb, a_sl, a_sh;
     int decay_mode, convention;
-    int n_tiles, n_tiles64, n_dtiles, n_items;
+    int n_tiles, n_dtiles, n_items;
     int64_t head_partial_offset;
 };
 
-constexpr int kBwdStages = 3;
+constexpr int kBwdStages = 2;
 struct BwdSmem {
     static constexpr int mat_a1 = 0;
     static constexpr int mat_u = mat_a1 + kMatBytes;
-    static constexpr int xg = mat_u + kMatBytes;                       // stages of [x tile | dy tile]
-    static constexpr int ostage = xg + kBwdStages * 2 * kTileBytes;    // dx staging, 2 buffers
-    static constexpr int hs = ostage + 2 * kTileBytes;                 // float[kRing][64] saved state entering the tile
-    static constexpr int g = hs + kRing * DT * 4;                      // float[kRing][64] adjoint carry
+    static constexpr int xg = mat_u + kMatBytes;                       // stages of [x tile | dy tile]; dx leaves from the dy half
+    static constexpr int hs = xg + kBwdStages * 2 * kTileBytes;        // float[kRing][128] saved state entering the tile
+    static constexpr int g = hs + kRing * DT * 4;                      // float[kRing][128] adjoint carry
     static constexpr int rowsc = g + kRing * DT * 4;                   // float[kRing][4][128]: Eprev, F, p, a per build
     static constexpr int cs = rowsc + kRing * 4 * QT * 4;              // float[128]
     static constexpr int pw = cs + QT * 4;                             // float[128]
     static constexpr int wt = pw + QT * 4;                             // float[4]
     static constexpr int bars = wt + 16;
-    static constexpr int n_bars = 2 * kBwdStages + 4 + 2 + kRing + 4;
+    static constexpr int n_bars = 3 * kBwdStages + 4 + 2 + kRing;
     static constexpr int tmem_slot = bars + n_bars * 8;
     static constexpr int abort_flag = tmem_slot + 4;
     static constexpr int total = abort_flag + 4;
@@ -536,19 +564,22 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + BwdSmem::abort_flag);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + BwdSmem::tmem_slot);
     auto bar = [&](int i) { return sbase + BwdSmem::bars + i * 8; };
-    constexpr int B_FULL = 0, B_EMPTY = kBwdStages, B_ACC_FULL = 2 * kBwdStages, B_ACC_EMPTY = B_ACC_FULL + 2,
-                  B_MAT_FULL = B_ACC_EMPTY + 2, B_MAT_EMPTY = B_MAT_FULL + 1, B_G = B_MAT_EMPTY + 1,
-                  B_STG_FULL = B_G + kRing, B_STG_EMPTY = B_STG_FULL + 2;
-    constexpr uint32_t kTmemCols = 256;  // 2 stages x (Z | Lam) x 64 columns
+    constexpr int B_FULL = 0, B_EMPTY = kBwdStages, B_STAGED = 2 * kBwdStages, B_ACC_FULL = 3 * kBwdStages,
+                  B_ACC_EMPTY = B_ACC_FULL + 2, B_MAT_FULL = B_ACC_EMPTY + 2, B_MAT_EMPTY = B_MAT_FULL + 1,
+                  B_G = B_MAT_EMPTY + 1;
+    constexpr uint32_t kTmemCols = 512;  // 2 stages x (Z | Lam) x 128 columns
 
     if (tid == 0) {
-        for (int i = 0; i < kBwdStages; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
+        for (int i = 0; i < kBwdStages; ++i) {
+            mbar_init(bar(B_FULL + i), 1);
+            mbar_init(bar(B_EMPTY + i), 1);
+            mbar_init(bar(B_STAGED + i), kEpiWarps);
+        }
         for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiWarps); }
         mbar_init(bar(B_MAT_FULL), 4);
         mbar_init(bar(B_MAT_EMPTY), 1);
-        // carry ready: the two halves of the adjoint row and the two warps that fetch the saved state
-        for (int i = 0; i < kRing; ++i) mbar_init(bar(B_G + i), 4);
-        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_STG_FULL + i), kEpiWarps); mbar_init(bar(B_STG_EMPTY + i), 1); }
+        // carry ready: the two halves of the adjoint row and the four warps that fetch the saved state
+        for (int i = 0; i < kRing; ++i) mbar_init(bar(B_G + i), 6);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tm_x);
@@ -583,8 +614,11 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 11)) break;
                     mbar_expect_tx(bar(B_FULL + s), 2 * kTileBytes);
                     const uint32_t dst = sbase + BwdSmem::xg + s * 2 * kTileBytes;
-                    tma_load_4d(dst, &tm_x, bar(B_FULL + s), dtile * DT, hi, k * QT, bi);
-                    tma_load_4d(dst + kTileBytes, &tm_g, bar(B_FULL + s), dtile * DT, hi, k * QT, bi);
+                    const int c0 = dtile * DT;
+                    tma_load_4d(dst, &tm_x, bar(B_FULL + s), c0, hi, k * QT, bi);
+                    tma_load_4d(dst + kBlockBytes, &tm_x, bar(B_FULL + s), c0 + kBlockCols, hi, k * QT, bi);
+                    tma_load_4d(dst + kTileBytes, &tm_g, bar(B_FULL + s), c0, hi, k * QT, bi);
+                    tma_load_4d(dst + kTileBytes + kBlockBytes, &tm_g, bar(B_FULL + s), c0 + kBlockCols, hi, k * QT, bi);
                 }
             }
         }
@@ -612,7 +646,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 13)) break;
                     if (!mbar_wait(bar(B_ACC_EMPTY + acc), aph ^ 1, abort_flag, 14)) break;
                     tc_fence_after_sync();
-                    const uint64_t xd0 = make_desc_sw128(sbase + BwdSmem::xg + s * 2 * kTileBytes, kTileBytes, 1024);
+                    const uint64_t xd0 = tile_desc(sbase + BwdSmem::xg + s * 2 * kTileBytes);
                     const uint64_t gd0 = xd0 + (kTileBytes >> 4);
                     const uint32_t d_z = tmem_base + acc * 2 * DT, d_l = d_z + DT;
 #pragma unroll
@@ -625,7 +659,6 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         const uint32_t koff = ((kb >> 2) * (QT * 128) + (kb & 3) * 32) >> 4;
                         umma_bf16(d_l, ud0 + koff, gd0 + ((kb * 2048) >> 4), kIdesc, kb > 0 ? 1u : 0u);
                     }
-                    umma_commit(bar(B_EMPTY + s));
                     umma_commit(bar(B_ACC_FULL + acc));
                     if (per_step) umma_commit(bar(B_MAT_EMPTY));
                 }
@@ -633,13 +666,12 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
     } else if (tid < kBuildThread0) {
         // ---------------- epilogue ----------------
-        // thread (q, lane, half): row m = 32 q + lane, channels [32 half, 32 half + 32) of the tile.
+        // thread (q, lane, half): row m = 32 q + lane, channels [64 half, 64 half + 64) of the tile, 32 at a time.
         // The two threads of row 0 are the serial carry chain (the adjoint handed to the tile on the left).
         const int q = warp & 3;
         const int half = (warp - kEpiThread0 / 32) >> 2;
         const int m = q * 32 + lane;
-        const int cb = half * 32;
-        const bool loader = half == 0 && m < DT;  // warps (q = 0, 1; half 0): fetch the saved states
+        const bool loader = half == 0;  // 128 threads: thread m fetches channel m of the saved states
         uint32_t it = 0, mt = 0;
         int cur_head = -1;
         for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
@@ -649,26 +681,26 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const int c0 = dtile * DT;
             const int64_t blk = row * p.n_dtiles + dtile;
             const bool ch_ok = loader && c0 + m < p.d;
-            const float *ts_item = p.tile_states + row * p.n_tiles64 * p.d + c0 + m;
-            // the adjoint partial sums: [blk][half][t] (per-step) or 4 slots per 64-step block (per-head)
-            float *dap_step = p.da_partial + (blk * 2 + half) * (static_cast<int64_t>(p.n_tiles64) * 64);
-            float *dap_head = p.da_partial + p.head_partial_offset + blk * p.n_tiles64 * 4;
+            const float *ts_item = p.tile_states + row * p.n_tiles * p.d + c0 + m;
+            // the adjoint partial sums: [blk][half][t] (per-step) or 8 slots per tile, one per warp (per-head)
+            float *dap_step = p.da_partial + (blk * 2 + half) * (static_cast<int64_t>(p.n_tiles) * QT);
+            float *dap_head = p.da_partial + p.head_partial_offset + blk * p.n_tiles * kEpiWarps;
             float hs_next = 0.f;
             if (loader) {
                 const int slot0 = it & (kRing - 1);
-                hs_sm[slot0 * DT + m] = ch_ok ? ts_item[static_cast<int64_t>(2 * (p.n_tiles - 1)) * p.d] : 0.f;
+                hs_sm[slot0 * DT + m] = ch_ok ? ts_item[static_cast<int64_t>(p.n_tiles - 1) * p.d] : 0.f;
                 g_sm[slot0 * DT + m] = (p.dfinal_state && ch_ok) ? p.dfinal_state[row * p.d + c0 + m] : 0.f;
             }
             bar_sync(1, kEpiThreads);
             if (m == 0) mbar_arrive(bar(B_G + (it & (kRing - 1))));
             if (loader && lane == 0) mbar_arrive(bar(B_G + (it & (kRing - 1))));
             for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
-                const int acc = it & 1, slot = it & (kRing - 1), nslot = (it + 1) & (kRing - 1), buf = it & 1;
+                const int acc = it & 1, slot = it & (kRing - 1), nslot = (it + 1) & (kRing - 1), s = it % kBwdStages;
                 const uint32_t aph = (it >> 1) & 1, gph = (it / kRing) & 1;
                 if (per_step || hi != cur_head) { cur_head = hi; ++mt; }
                 // prefetch the saved state of the next tile to the left while this one is being finished
-                if (loader && k > 0) hs_next = ch_ok ? ts_item[static_cast<int64_t>(2 * (k - 1)) * p.d] : 0.f;
-                mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 15);
+                if (loader && k > 0) hs_next = ch_ok ? ts_item[static_cast<int64_t>(k - 1) * p.d] : 0.f;
+                if (lane == 0) mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 15);
                 __syncwarp();
                 tc_fence_after_sync();
                 const float *rs = rowsc + ((mt - 1) & (kRing - 1)) * 4 * QT;
@@ -682,56 +714,72 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     for (int j = m + 1; j < lim; ++j) f *= a_m;
                     F = f;
                 }
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * 2 * DT + cb;
-                float z[32], lam[32];
-                tmem_ld32(taddr, z);
-                tmem_ld32(taddr + DT, lam);
-                tmem_ld_wait();
-                tc_fence_before_sync();
+                if (lane == 0) mbar_wait(bar(B_G + slot), gph, abort_flag, 16);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + acc));
-
-                mbar_wait(bar(B_G + slot), gph, abort_flag, 16);
-                const float *hin = hs_sm + slot * DT + cb;
-                const float *gin = g_sm + slot * DT + cb;
-#pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    const float4 gv = *reinterpret_cast<const float4 *>(gin + c);
-                    lam[c] = fmaf(F, gv.x, lam[c]);
-                    lam[c + 1] = fmaf(F, gv.y, lam[c + 1]);
-                    lam[c + 2] = fmaf(F, gv.z, lam[c + 2]);
-                    lam[c + 3] = fmaf(F, gv.w, lam[c + 3]);
-                }
-                if (k > 0) {
-                    // publish what the tile on the left needs: row 0 of the adjoint, and its saved state
-                    if (m == 0) {
-                        float *gout = g_sm + nslot * DT + cb;
-#pragma unroll
-                        for (int c = 0; c < 32; c += 4)
-                            *reinterpret_cast<float4 *>(gout + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
-                        mbar_arrive(bar(B_G + nslot));
-                    }
-                    if (loader) {
-                        hs_sm[nslot * DT + m] = hs_next;
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(bar(B_G + nslot));
-                    }
-                } else if (m == 0 && p.dinit_state) {
-                    float *di = p.dinit_state + row * p.d + c0 + cb;
-#pragma unroll
-                    for (int c = 0; c < 32; ++c)
-                        if (c0 + cb + c < p.d) di[c] = a_m * lam[c];
-                }
-                float dacc = 0.f;
-#pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    const float4 hv = *reinterpret_cast<const float4 *>(hin + c);
-                    dacc = fmaf(lam[c], fmaf(Eprev, hv.x, z[c]), dacc);
-                    dacc = fmaf(lam[c + 1], fmaf(Eprev, hv.y, z[c + 1]), dacc);
-                    dacc = fmaf(lam[c + 2], fmaf(Eprev, hv.z, z[c + 2]), dacc);
-                    dacc = fmaf(lam[c + 3], fmaf(Eprev, hv.w, z[c + 3]), dacc);
-                }
                 const int t = k * QT + m;
+                float dacc = 0.f;
+                // ACC_FULL says the MMAs have finished reading the stage: its dy half now takes the dx tile
+                uint8_t *stg = smem + BwdSmem::xg + s * 2 * kTileBytes + kTileBytes + half * kBlockBytes;
+#pragma unroll
+                for (int pass = 0; pass < 2; ++pass) {
+                    const int cb = half * 64 + pass * 32;
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * 2 * DT + cb;
+                    float z[32], lam[32];
+                    __syncwarp();  // single-thread branches of the previous pass have rejoined
+                    tmem_ld32(taddr, z);
+                    tmem_ld32(taddr + DT, lam);
+                    tmem_ld_wait();
+                    if (pass == 1) {
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + acc));
+                    }
+                    const float *hin = hs_sm + slot * DT + cb;
+                    const float *gin = g_sm + slot * DT + cb;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        const float4 gv = *reinterpret_cast<const float4 *>(gin + c);
+                        lam[c] = fmaf(F, gv.x, lam[c]);
+                        lam[c + 1] = fmaf(F, gv.y, lam[c + 1]);
+                        lam[c + 2] = fmaf(F, gv.z, lam[c + 2]);
+                        lam[c + 3] = fmaf(F, gv.w, lam[c + 3]);
+                    }
+                    if (m == 0) {
+                        if (k > 0) {  // row 0 of the adjoint is what the tile on the left receives
+                            float *gout = g_sm + nslot * DT + cb;
+#pragma unroll
+                            for (int c = 0; c < 32; c += 4)
+                                *reinterpret_cast<float4 *>(gout + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
+                            if (pass == 1) mbar_arrive(bar(B_G + nslot));
+                        } else if (p.dinit_state) {
+                            float *di = p.dinit_state + row * p.d + c0 + cb;
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                if (c0 + cb + c < p.d) di[c] = a_m * lam[c];
+                        }
+                    }
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        const float4 hv = *reinterpret_cast<const float4 *>(hin + c);
+                        dacc = fmaf(lam[c], fmaf(Eprev, hv.x, z[c]), dacc);
+                        dacc = fmaf(lam[c + 1], fmaf(Eprev, hv.y, z[c + 1]), dacc);
+                        dacc = fmaf(lam[c + 2], fmaf(Eprev, hv.z, z[c + 2]), dacc);
+                        dacc = fmaf(lam[c + 3], fmaf(Eprev, hv.w, z[c + 3]), dacc);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint4 qv = make_uint4(pack_bf16x2(p_m * lam[8 * j], p_m * lam[8 * j + 1]),
+                                                    pack_bf16x2(p_m * lam[8 * j + 2], p_m * lam[8 * j + 3]),
+                                                    pack_bf16x2(p_m * lam[8 * j + 4], p_m * lam[8 * j + 5]),
+                                                    pack_bf16x2(p_m * lam[8 * j + 6], p_m * lam[8 * j + 7]));
+                        *reinterpret_cast<uint4 *>(stg + sw128_offset(m, pass * 4 + j)) = qv;
+                    }
+                }
+                if (loader && k > 0) {  // the saved state the tile on the left will need
+                    hs_sm[nslot * DT + m] = hs_next;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(B_G + nslot));
+                }
                 if (conv) dacc *= a_m;
                 if (t >= L) dacc = 0.f;
                 if (per_step) {
@@ -740,22 +788,11 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     float wsum = dacc;
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
-                    const int k64 = 2 * k + (q >> 1);
-                    if (lane == 0 && k64 < p.n_tiles64) dap_head[k64 * 4 + (q & 1) * 2 + half] = wsum;
-                }
-                mbar_wait(bar(B_STG_EMPTY + buf), aph ^ 1, abort_flag, 17);
-                uint8_t *stg = smem + BwdSmem::ostage + buf * kTileBytes;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint4 qv = make_uint4(pack_bf16x2(p_m * lam[8 * j], p_m * lam[8 * j + 1]),
-                                                pack_bf16x2(p_m * lam[8 * j + 2], p_m * lam[8 * j + 3]),
-                                                pack_bf16x2(p_m * lam[8 * j + 4], p_m * lam[8 * j + 5]),
-                                                pack_bf16x2(p_m * lam[8 * j + 6], p_m * lam[8 * j + 7]));
-                    *reinterpret_cast<uint4 *>(stg + sw128_offset(m, half * 4 + j)) = qv;
+                    if (lane == 0) dap_head[k * kEpiWarps + q * 2 + half] = wsum;
                 }
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_STG_FULL + buf));
+                if (lane == 0) mbar_arrive(bar(B_STAGED + s));
             }
         }
     } else if (tid < kStoreThread) {
@@ -777,7 +814,8 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const float cs_r = cs_sm[r];
             const float Eprev = exp2f(cs_r - l2);                       // prod_{j<r} a_j
             const float Fr = exp2f(cs_sm[QT - 1] - cs_r + log2_decay(v_edge));
-            mbar_wait(bar(B_MAT_EMPTY), (mt & 1) ^ 1, abort_flag, 18);
+            if (lane == 0) mbar_wait(bar(B_MAT_EMPTY), (mt & 1) ^ 1, abort_flag, 18);
+            __syncwarp();
             store_chunks<false>(r, smem + BwdSmem::mat_a1, ca);
             store_chunks<true>(r, smem + BwdSmem::mat_u, cu);
             float *rs = rowsc + (mt & (kRing - 1)) * 4 * QT;
@@ -822,13 +860,16 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 const int dtile = static_cast<int>(item % p.n_dtiles);
                 const int64_t row = item / p.n_dtiles;
                 const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
+                const bool two = dtile * DT + kBlockCols < p.d;
                 for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
-                    const int buf = it & 1;
-                    if (!mbar_wait(bar(B_STG_FULL + buf), (it >> 1) & 1, abort_flag, 19)) break;
-                    tma_store_4d(&tm_o, sbase + BwdSmem::ostage + buf * kTileBytes, dtile * DT, hi, k * QT, bi);
+                    const int s = it % kBwdStages;
+                    if (!mbar_wait(bar(B_STAGED + s), (it / kBwdStages) & 1, abort_flag, 19)) break;
+                    const uint32_t src = sbase + BwdSmem::xg + s * 2 * kTileBytes + kTileBytes;
+                    tma_store_4d(&tm_o, src, dtile * DT, hi, k * QT, bi);
+                    if (two) tma_store_4d(&tm_o, src + kBlockBytes, dtile * DT + kBlockCols, hi, k * QT, bi);
                     tma_store_commit();
                     tma_store_wait_read<0>();
-                    mbar_arrive(bar(B_STG_EMPTY + buf));
+                    mbar_arrive(bar(B_EMPTY + s));
                 }
             }
             tma_store_wait_all();
@@ -874,7 +915,7 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// bf16 tensor [b, L, h, d] with element strides (sb, sl, sh), box = [64 channels, 1, 128 steps, 1],
+// bf16 tensor [b, L, h, d] with element strides (sb, sl, sh), box = [64 channels, 1, 128 steps, 1] (half a tile),
 // 128-byte swizzle; out-of-range parts of a box read as zero and are not written.
 int make_tmap(CUtensorMap *tm, const void *base, int64_t b, int64_t L, int64_t h, int64_t d, int64_t sb,
               int64_t sl, int64_t sh) {
@@ -888,7 +929,7 @@ int make_tmap(CUtensorMap *tm, const void *base, int64_t b, int64_t L, int64_t h
                                 static_cast<cuuint64_t>(b)};
     const cuuint64_t strides[3] = {static_cast<cuuint64_t>(sh) * 2, static_cast<cuuint64_t>(sl) * 2,
                                    static_cast<cuuint64_t>(sb) * 2};
-    const cuuint32_t box[4] = {tc::DT, 1, tc::QT, 1};
+    const cuuint32_t box[4] = {tc::kBlockCols, 1, tc::QT, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -933,7 +974,6 @@ int launch_fused_fwd_tc(const FusedParams &fp, cudaStream_t stream) {
     p.a_sb = fp.a_sb; p.a_sl = fp.a_sl; p.a_sh = fp.a_sh;
     p.decay_mode = fp.decay_mode; p.convention = fp.convention; p.chunk = fp.chunk;
     p.n_tiles = static_cast<int>((fp.L + tc::QT - 1) / tc::QT);
-    p.n_tiles64 = fp.n_tiles;
     p.n_dtiles = static_cast<int>((fp.d + tc::DT - 1) / tc::DT);
     p.n_items = static_cast<int>(fp.b * fp.h * p.n_dtiles);
     p.n_chunks = fp.n_chunks;
@@ -965,7 +1005,6 @@ int launch_fused_bwd_tc(const FusedParams &fp, cudaStream_t stream) {
     p.a_sb = fp.a_sb; p.a_sl = fp.a_sl; p.a_sh = fp.a_sh;
     p.decay_mode = fp.decay_mode; p.convention = fp.convention;
     p.n_tiles = static_cast<int>((fp.L + tc::QT - 1) / tc::QT);
-    p.n_tiles64 = fp.n_tiles;
     p.n_dtiles = static_cast<int>((fp.d + tc::DT - 1) / tc::DT);
     p.n_items = static_cast<int>(fp.b * fp.h * p.n_dtiles);
     p.head_partial_offset = kHeadPartialOffset(fp.b * fp.h);
