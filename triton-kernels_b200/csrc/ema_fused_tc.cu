@@ -510,7 +510,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 // A1[m,k] = p_k prod_{j=k+1..m-1} a_j (k < m), A1[m,m] = -1 | 0;  U[m,k] = prod_{j=m+1..k} a_j (k >= m);
 // Eprev_m = prod_{j<m} a_j;  F_m = prod_{j=m+1..128} a_j (a_128 = first decay of the next tile, 1 past L).
 // Then dx_m = p_m Lam_m, ddecay_m = sum_c Lam_mc Z_mc (times a_m for the log-decay convention), and row 0
-// of Lam is the adjoint handed to the previous tile.  dx leaves from the stage the dy tile arrived in.
+// of Lam is the adjoint handed to the previous tile.
 struct TcBwdParams {
     const float *decay;
     const float *tile_states;
@@ -525,18 +525,29 @@ struct TcBwdParams {
 };
 
 constexpr int kBwdStages = 2;
+constexpr int kRowRing = 3;   // per-row scalar tables: a build's table is read early in the tile that uses it
+// The two matrices are triangular: the upper-right 64x64 quadrant of A1 and the lower-left one of U are zero.
+// Stored by 64-wide K blocks (rows of 128 bytes), the zero quadrants are one shared 8 KB region Z:
+//   [A1 K-block 0, rows 0-127][U K-block 0, rows 0-63][Z][A1 K-block 1, rows 64-127][U K-block 1, rows 0-127]
+// so that U K-block 0 = (U rows 0-63, Z) and A1 K-block 1 = (Z, A1 rows 64-127) are each contiguous.
 struct BwdSmem {
-    static constexpr int mat_a1 = 0;
-    static constexpr int mat_u = mat_a1 + kMatBytes;
-    static constexpr int xg = mat_u + kMatBytes;                       // stages of [x tile | dy tile]; dx leaves from the dy half
-    static constexpr int hs = xg + kBwdStages * 2 * kTileBytes;        // float[kRing][128] saved state entering the tile
+    static constexpr int m_a1k0 = 0;
+    static constexpr int m_u00 = m_a1k0 + kBlockBytes;
+    static constexpr int m_z = m_u00 + kBlockBytes / 2;
+    static constexpr int m_a111 = m_z + kBlockBytes / 2;
+    static constexpr int m_uk1 = m_a111 + kBlockBytes / 2;
+    static constexpr int mat_bytes = m_uk1 + kBlockBytes;              // 56 KB
+    static constexpr int xg = mat_bytes;                               // stages of [x tile | dy tile]
+    static constexpr int ostage = xg + kBwdStages * 2 * kTileBytes;    // dx staging: one tile, a 64-channel block per half
+    static constexpr int hs = ostage + kTileBytes;                     // float[kRing][128] saved state entering the tile
     static constexpr int g = hs + kRing * DT * 4;                      // float[kRing][128] adjoint carry
-    static constexpr int rowsc = g + kRing * DT * 4;                   // float[kRing][4][128]: Eprev, F, p, a per build
-    static constexpr int cs = rowsc + kRing * 4 * QT * 4;              // float[128]
+    static constexpr int rowsc = g + kRing * DT * 4;                   // float[kRowRing][3][128]: Eprev, F, a per build
+    static constexpr int cs = rowsc + kRowRing * 3 * QT * 4;           // float[128]
     static constexpr int pw = cs + QT * 4;                             // float[128]
     static constexpr int wt = pw + QT * 4;                             // float[4]
     static constexpr int bars = wt + 16;
-    static constexpr int n_bars = 3 * kBwdStages + 4 + 2 + kRing;
+    // stage full/empty, staging full/empty per half, acc full/empty, matrix full/empty, carry ready
+    static constexpr int n_bars = 2 * kBwdStages + 4 + 4 + 2 + kRing;
     static constexpr int tmem_slot = bars + n_bars * 8;
     static constexpr int abort_flag = tmem_slot + 4;
     static constexpr int total = abort_flag + 4;
@@ -564,17 +575,14 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + BwdSmem::abort_flag);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + BwdSmem::tmem_slot);
     auto bar = [&](int i) { return sbase + BwdSmem::bars + i * 8; };
-    constexpr int B_FULL = 0, B_EMPTY = kBwdStages, B_STAGED = 2 * kBwdStages, B_ACC_FULL = 3 * kBwdStages,
-                  B_ACC_EMPTY = B_ACC_FULL + 2, B_MAT_FULL = B_ACC_EMPTY + 2, B_MAT_EMPTY = B_MAT_FULL + 1,
-                  B_G = B_MAT_EMPTY + 1;
+    constexpr int B_FULL = 0, B_EMPTY = kBwdStages, B_STG_FULL = 2 * kBwdStages, B_STG_EMPTY = B_STG_FULL + 2,
+                  B_ACC_FULL = B_STG_EMPTY + 2, B_ACC_EMPTY = B_ACC_FULL + 2, B_MAT_FULL = B_ACC_EMPTY + 2,
+                  B_MAT_EMPTY = B_MAT_FULL + 1, B_G = B_MAT_EMPTY + 1;
     constexpr uint32_t kTmemCols = 512;  // 2 stages x (Z | Lam) x 128 columns
 
     if (tid == 0) {
-        for (int i = 0; i < kBwdStages; ++i) {
-            mbar_init(bar(B_FULL + i), 1);
-            mbar_init(bar(B_EMPTY + i), 1);
-            mbar_init(bar(B_STAGED + i), kEpiWarps);
-        }
+        for (int i = 0; i < kBwdStages; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(bar(B_STG_FULL + i), kEpiWarps / 2); mbar_init(bar(B_STG_EMPTY + i), 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiWarps); }
         mbar_init(bar(B_MAT_FULL), 4);
         mbar_init(bar(B_MAT_EMPTY), 1);
@@ -586,8 +594,8 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         prefetch_tmap(&tm_g);
         prefetch_tmap(&tm_o);
     }
-    for (int i = tid; i < 2 * kMatBytes / 16; i += kThreads)
-        reinterpret_cast<uint4 *>(smem + BwdSmem::mat_a1)[i] = make_uint4(0u, 0u, 0u, 0u);
+    for (int i = tid; i < BwdSmem::mat_bytes / 16; i += kThreads)
+        reinterpret_cast<uint4 *>(smem + BwdSmem::m_a1k0)[i] = make_uint4(0u, 0u, 0u, 0u);
     if (warp == 1) {
         tmem_alloc(sbase + BwdSmem::tmem_slot, kTmemCols);
         tmem_relinquish();
@@ -627,8 +635,11 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         if (lane == 0) {
             uint32_t it = 0, mt = 0;
             int cur_head = -1;
-            const uint64_t a1d0 = make_desc_sw128(sbase + BwdSmem::mat_a1, 16, 1024);
-            const uint64_t ud0 = make_desc_sw128(sbase + BwdSmem::mat_u, 16, 1024);
+            // K block 0 / 1 of each matrix (see BwdSmem): descriptor bases
+            const uint64_t a1d[2] = {make_desc_sw128(sbase + BwdSmem::m_a1k0, 16, 1024),
+                                     make_desc_sw128(sbase + BwdSmem::m_z, 16, 1024)};
+            const uint64_t ud[2] = {make_desc_sw128(sbase + BwdSmem::m_u00, 16, 1024),
+                                    make_desc_sw128(sbase + BwdSmem::m_uk1, 16, 1024)};
             for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
                 const int hi = static_cast<int>((item / p.n_dtiles) % p.h);
                 for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
@@ -650,15 +661,12 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     const uint64_t gd0 = xd0 + (kTileBytes >> 4);
                     const uint32_t d_z = tmem_base + acc * 2 * DT, d_l = d_z + DT;
 #pragma unroll
-                    for (int kb = 0; kb < QT / 16; ++kb) {
-                        const uint32_t koff = ((kb >> 2) * (QT * 128) + (kb & 3) * 32) >> 4;
-                        umma_bf16(d_z, a1d0 + koff, xd0 + ((kb * 2048) >> 4), kIdesc, kb > 0 ? 1u : 0u);
-                    }
+                    for (int kb = 0; kb < QT / 16; ++kb)
+                        umma_bf16(d_z, a1d[kb >> 2] + (((kb & 3) * 32) >> 4), xd0 + ((kb * 2048) >> 4), kIdesc, kb > 0 ? 1u : 0u);
 #pragma unroll
-                    for (int kb = 0; kb < QT / 16; ++kb) {
-                        const uint32_t koff = ((kb >> 2) * (QT * 128) + (kb & 3) * 32) >> 4;
-                        umma_bf16(d_l, ud0 + koff, gd0 + ((kb * 2048) >> 4), kIdesc, kb > 0 ? 1u : 0u);
-                    }
+                    for (int kb = 0; kb < QT / 16; ++kb)
+                        umma_bf16(d_l, ud[kb >> 2] + (((kb & 3) * 32) >> 4), gd0 + ((kb * 2048) >> 4), kIdesc, kb > 0 ? 1u : 0u);
+                    umma_commit(bar(B_EMPTY + s));   // the stage is free as soon as the MMAs have read it
                     umma_commit(bar(B_ACC_FULL + acc));
                     if (per_step) umma_commit(bar(B_MAT_EMPTY));
                 }
@@ -695,7 +703,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             if (m == 0) mbar_arrive(bar(B_G + (it & (kRing - 1))));
             if (loader && lane == 0) mbar_arrive(bar(B_G + (it & (kRing - 1))));
             for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
-                const int acc = it & 1, slot = it & (kRing - 1), nslot = (it + 1) & (kRing - 1), s = it % kBwdStages;
+                const int acc = it & 1, slot = it & (kRing - 1), nslot = (it + 1) & (kRing - 1);
                 const uint32_t aph = (it >> 1) & 1, gph = (it / kRing) & 1;
                 if (per_step || hi != cur_head) { cur_head = hi; ++mt; }
                 // prefetch the saved state of the next tile to the left while this one is being finished
@@ -703,8 +711,9 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 if (lane == 0) mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 15);
                 __syncwarp();
                 tc_fence_after_sync();
-                const float *rs = rowsc + ((mt - 1) & (kRing - 1)) * 4 * QT;
-                const float Eprev = rs[m], a_m = rs[3 * QT + m], p_m = rs[2 * QT + m];
+                const float *rs = rowsc + ((mt - 1) % kRowRing) * 3 * QT;
+                const float Eprev = rs[m], a_m = rs[2 * QT + m];
+                const float p_m = conv ? 1.f : 1.f - a_m;
                 // F: a time-invariant decay uses one Toeplitz table; the rightmost tile of the sequence stops at
                 // step L-1, where the adjoint entering from the right applies undamped
                 float F = rs[QT + m];
@@ -718,8 +727,10 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 __syncwarp();
                 const int t = k * QT + m;
                 float dacc = 0.f;
-                // ACC_FULL says the MMAs have finished reading the stage: its dy half now takes the dx tile
-                uint8_t *stg = smem + BwdSmem::xg + s * 2 * kTileBytes + kTileBytes + half * kBlockBytes;
+                // dx staging: this half's 64-channel block, free once the store of the previous tile has read it
+                uint8_t *stg = smem + BwdSmem::ostage + half * kBlockBytes;
+                if (lane == 0) mbar_wait(bar(B_STG_EMPTY + half), (it & 1) ^ 1, abort_flag, 17);
+                __syncwarp();
 #pragma unroll
                 for (int pass = 0; pass < 2; ++pass) {
                     const int cb = half * 64 + pass * 32;
@@ -792,7 +803,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 }
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(B_STAGED + s));
+                if (lane == 0) mbar_arrive(bar(B_STG_FULL + half));
             }
         }
     } else if (tid < kStoreThread) {
@@ -816,13 +827,22 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const float Fr = exp2f(cs_sm[QT - 1] - cs_r + log2_decay(v_edge));
             if (lane == 0) mbar_wait(bar(B_MAT_EMPTY), (mt & 1) ^ 1, abort_flag, 18);
             __syncwarp();
-            store_chunks<false>(r, smem + BwdSmem::mat_a1, ca);
-            store_chunks<true>(r, smem + BwdSmem::mat_u, cu);
-            float *rs = rowsc + (mt & (kRing - 1)) * 4 * QT;
+            // A1: K block 0 holds every row; K block 1 only rows 64-127 (stored from row 64 on)
+            for_my_chunks<false>(r, [&](int n, int m, int c) {
+                uint8_t *dst = c < 8 ? smem + BwdSmem::m_a1k0 + sw128_offset(m, c)
+                                     : smem + BwdSmem::m_a111 + sw128_offset(m - 64, c - 8);
+                *reinterpret_cast<uint4 *>(dst) = ca.v[n];
+            });
+            // U: K block 0 only rows 0-63; K block 1 every row
+            for_my_chunks<true>(r, [&](int n, int m, int c) {
+                uint8_t *dst = c < 8 ? smem + BwdSmem::m_u00 + sw128_offset(m, c)
+                                     : smem + BwdSmem::m_uk1 + sw128_offset(m, c - 8);
+                *reinterpret_cast<uint4 *>(dst) = cu.v[n];
+            });
+            float *rs = rowsc + (mt % kRowRing) * 3 * QT;
             rs[r] = Eprev;
             rs[QT + r] = Fr;
-            rs[2 * QT + r] = pw;
-            rs[3 * QT + r] = conv ? exp2f(l2) : v;
+            rs[2 * QT + r] = conv ? exp2f(l2) : v;
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_MAT_FULL));
@@ -860,16 +880,19 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 const int dtile = static_cast<int>(item % p.n_dtiles);
                 const int64_t row = item / p.n_dtiles;
                 const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
-                const bool two = dtile * DT + kBlockCols < p.d;
+                const bool two = dtile * DT + kBlockCols < p.d;   // the second 64-channel block exists
                 for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
-                    const int s = it % kBwdStages;
-                    if (!mbar_wait(bar(B_STAGED + s), (it / kBwdStages) & 1, abort_flag, 19)) break;
-                    const uint32_t src = sbase + BwdSmem::xg + s * 2 * kTileBytes + kTileBytes;
+                    const uint32_t src = sbase + BwdSmem::ostage;
+                    if (!mbar_wait(bar(B_STG_FULL + 0), it & 1, abort_flag, 19)) break;
                     tma_store_4d(&tm_o, src, dtile * DT, hi, k * QT, bi);
+                    tma_store_commit();
+                    if (!mbar_wait(bar(B_STG_FULL + 1), it & 1, abort_flag, 20)) break;
                     if (two) tma_store_4d(&tm_o, src + kBlockBytes, dtile * DT + kBlockCols, hi, k * QT, bi);
                     tma_store_commit();
+                    tma_store_wait_read<1>();          // block 0 has been read: hand it back to its four warps
+                    mbar_arrive(bar(B_STG_EMPTY + 0));
                     tma_store_wait_read<0>();
-                    mbar_arrive(bar(B_EMPTY + s));
+                    mbar_arrive(bar(B_STG_EMPTY + 1));
                 }
             }
             tma_store_wait_all();
