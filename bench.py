@@ -89,7 +89,8 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm),
+                "window": "about 1.2 s of identical back-to-back steps ending with the timed steps"}
 
 
 def algorithmic_bytes(b, L, h, d, s=2):
@@ -193,10 +194,19 @@ def run_gpu(args):
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
+    # The timed region lasts tens of milliseconds, less than one nvidia-smi sample.  So that the clock
+    # record describes the same load, identical steps run untimed for about a second right before it
+    # (at least 5 sampler periods); the samples cover that run-in and the timed steps.
+    t_begin = time.time()
+    if not args.no_spinup:
+        t_spin = time.time()
+        while time.time() - t_spin < 1.2:
+            for _ in range(50):
+                step()
+            torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    t_begin = time.time()
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
     start.record()
@@ -295,9 +305,11 @@ def run_gpu(args):
                 "step": {"achieved": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9,
                          "frac": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9 / peak}}
     traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(traffic_file):
+    if os.path.exists(traffic_file):   # dram__bytes_read.sum + dram__bytes_write.sum from the committed ncu capture
         with open(traffic_file) as f:
-            roofline["traffic"] = json.load(f).get("ema_bwd_bytes_per_launch")
+            tr = json.load(f)
+        roofline["traffic"] = tr.get("ema_bwd_bytes_per_launch")
+        roofline["fwd"]["traffic"] = tr.get("ema_fwd_bytes_per_launch")
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu_baseline:
@@ -343,6 +355,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
+    ap.add_argument("--no-spinup", action="store_true", help="skip the untimed run-in used for clock sampling (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 10:
