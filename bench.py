@@ -171,18 +171,42 @@ def run_gpu(args):
     a = torch.sigmoid(2 + 4 * torch.rand((h,), generator=torch.Generator(device=dev).manual_seed(99), device=dev))
     y = torch.empty_like(x)
     dx = torch.empty_like(x)
-    da = torch.empty_like(a)
+    # Two buffers for the per-head decay gradient: with N > 1 its all-reduce (the only collective of the
+    # row-sharded path, 4*h bytes) runs on NCCL's stream while the next step computes; a step waits for the
+    # reduce issued two steps earlier before it overwrites that buffer.
+    da_bufs = [torch.empty_like(a), torch.empty_like(a)]
+    pending = [None, None]
+    n_steps_done = 0
     ts, nt = ops.n_tiles_of(x, a)
     tile_states = torch.empty((b * h, nt, d), dtype=torch.float32, device=dev)
     ws = None
 
+    def reduce_da():
+        nonlocal n_steps_done
+        slot = n_steps_done % 2
+        n_steps_done += 1
+        if world > 1:
+            pending[slot] = dist.all_reduce(da_bufs[slot], async_op=True)
+
+    def da_slot():
+        slot = n_steps_done % 2
+        if pending[slot] is not None:
+            pending[slot].wait()   # stream-level wait for the reduce that last used this buffer
+            pending[slot] = None
+        return da_bufs[slot]
+
+    def drain():
+        for slot in range(2):
+            if pending[slot] is not None:
+                pending[slot].wait()
+                pending[slot] = None
+
     def step():
         nonlocal ws
         ops.ema_fwd(x, a, out=y, tile_states=tile_states)
-        r = ops.ema_bwd(x, a, dy, tile_states, dx=dx, ddecay=da, workspace=ws)
+        r = ops.ema_bwd(x, a, dy, tile_states, dx=dx, ddecay=da_slot(), workspace=ws)
         ws = r["workspace"]
-        if world > 1:
-            dist.all_reduce(da)
+        reduce_da()
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -199,11 +223,18 @@ def run_gpu(args):
     # (at least 5 sampler periods); the samples cover that run-in and the timed steps.
     t_begin = time.time()
     if not args.no_spinup:
-        t_spin = time.time()
-        while time.time() - t_spin < 1.2:
-            for _ in range(50):
-                step()
-            torch.cuda.synchronize()
+        # a fixed count on every rank (each step carries a collective when N > 1): ~1.2 s at the measured step time
+        t0 = time.time()
+        for _ in range(20):
+            step()
+        torch.cuda.synchronize()
+        per_step = max((time.time() - t0) / 20, 1e-5)
+        n_spin = torch.tensor([int(1.2 / per_step)], device=dev)
+        if world > 1:
+            dist.broadcast(n_spin, 0)
+        for _ in range(int(n_spin.item())):
+            step()
+        torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -214,10 +245,10 @@ def run_gpu(args):
         ev[i][0].record()
         ops.ema_fwd(x, a, out=y, tile_states=tile_states)
         ev[i][1].record()
-        ops.ema_bwd(x, a, dy, tile_states, dx=dx, ddecay=da, workspace=ws)
+        ops.ema_bwd(x, a, dy, tile_states, dx=dx, ddecay=da_slot(), workspace=ws)
         ev[i][2].record()
-        if world > 1:
-            dist.all_reduce(da)
+        reduce_da()
+    drain()   # the last reduces finish inside the timed region
     stop.record()
     torch.cuda.synchronize()
     if world > 1:

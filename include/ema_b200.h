@@ -88,6 +88,9 @@ int ema_b200_device_status(int clear);
  * 1 = CUDA-core path only.  fp32 problems always take the CUDA-core path (exactness).  Meant for A/B
  * measurements and tests; the environment variable EMA_B200_PATH=fma sets the same switch at load. */
 int ema_b200_set_path(int path);
+/* Kernel family the last ema_b200_fwd / ema_b200_bwd call on this thread launched: 1 = tensor cores,
+ * 0 = CUDA cores, -1 = none yet.  Lets a test assert that the tensor-core path really ran. */
+int ema_b200_last_path(void);
 
 /* Number of time steps one internal tile covers for this problem.  The forward writes one saved
  * state per tile and the backward consumes them, so both report the same value for the same

@@ -39,6 +39,7 @@ int pick_vec(const ema_b200_problem *p, const void *x, const void *out, const vo
 // Kernel family for bf16 problems: 0 = tensor cores where the layout allows (default), 1 = CUDA cores
 // only.  Set by ema_b200_set_path or, once, by the environment variable EMA_B200_PATH=fma.
 int g_path = -1;
+thread_local int g_last_path = -1;  // kernel family of the last fused launch on this thread: 1 tensor cores, 0 CUDA cores
 bool tc_enabled() {
     if (g_path < 0) {
         const char *e = std::getenv("EMA_B200_PATH");
@@ -87,6 +88,8 @@ extern "C" const char *ema_b200_error_string(int code) {
 
 extern "C" int ema_b200_device_status(int clear) { return read_tc_status(clear); }
 
+extern "C" int ema_b200_last_path(void) { return g_last_path; }
+
 extern "C" int ema_b200_set_path(int path) {
     if (path != 0 && path != 1) return EMA_ERR_BADARG;
     g_path = path;
@@ -108,9 +111,7 @@ extern "C" size_t ema_b200_bwd_workspace_bytes(const ema_b200_problem *p) {
     if (check_problem(p) != EMA_OK) return 0;
     // sized for the narrowest channel tile (vec = 1) so that it never depends on pointer alignment
     const int64_t n_tiles = (p->L + kFmaTile - 1) / kFmaTile;
-    int64_t n_dtiles = (p->d + kFmaCT - 1) / kFmaCT;
-    const int64_t tc_slices = 2 * ((p->d + 127) / 128);  // the tensor-core kernel's slices per row
-    if (tc_slices > n_dtiles) n_dtiles = tc_slices;
+    const int64_t n_dtiles = (p->d + kFmaCT - 1) / kFmaCT;
     const int64_t rows = p->b * p->h;
     const int64_t per_step = rows * n_dtiles * n_tiles * kFmaTile;
     const int64_t per_head = kHeadPartialOffset(rows) + rows * n_dtiles * n_tiles * (kFmaThreads / 32);
@@ -158,8 +159,10 @@ extern "C" int ema_b200_fwd(const ema_b200_problem *p, const void *x, const floa
         tc_tensor_ok(x, p->d, p->x_sb, p->x_sl, p->x_sh, p->b, p->L, p->h) &&
         tc_tensor_ok(y, p->d, p->y_sb, p->y_sl, p->y_sh, p->b, p->L, p->h) && aligned(tile_states, 16)) {
         rc = launch_fused_fwd_tc(fp, st);
+        if (rc == EMA_OK) g_last_path = 1;
         if (rc != EMA_ERR_UNSUPPORTED) return rc;  // a tensor map the driver refuses falls through to the FMA path
     }
+    g_last_path = 0;
     return launch_fused_fwd_fma(fp, p->dtype, vec, st);
 }
 
@@ -212,13 +215,8 @@ extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const floa
         rc = launch_fused_bwd_tc(fp, st);
         if (rc && rc != EMA_ERR_UNSUPPORTED) return rc;
         done = rc == EMA_OK;
-        // partial-sum slices of the tensor-core kernel: per 128-channel tile, two halves (per-step decay) or one
-        // block of four per 64 steps (per-head decay)
-        if (done) {
-            const int tc_dtiles = static_cast<int>((p->d + 127) / 128);
-            fp.n_dtiles = p->decay_mode == EMA_DECAY_PER_STEP ? 2 * tc_dtiles : tc_dtiles;
-        }
     }
+    g_last_path = done ? 1 : 0;
     if (!done) {
         rc = launch_fused_bwd_fma(fp, p->dtype, vec, st);
         if (rc) return rc;

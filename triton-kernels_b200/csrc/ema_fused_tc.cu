@@ -521,6 +521,7 @@ struct TcBwdParams {
     int64_t a_sb, a_sl, a_sh;
     int decay_mode, convention;
     int n_tiles, n_dtiles, n_items;
+    int n_dt64;       // 64-channel slices per row in the partial-sum buffer
     int64_t head_partial_offset;
 };
 
@@ -687,12 +688,15 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const int64_t row = item / p.n_dtiles;
             const int hi = static_cast<int>(row % p.h);
             const int c0 = dtile * DT;
-            const int64_t blk = row * p.n_dtiles + dtile;
             const bool ch_ok = loader && c0 + m < p.d;
             const float *ts_item = p.tile_states + row * p.n_tiles * p.d + c0 + m;
-            // the adjoint partial sums: [blk][half][t] (per-step) or 8 slots per tile, one per warp (per-head)
-            float *dap_step = p.da_partial + (blk * 2 + half) * (static_cast<int64_t>(p.n_tiles) * QT);
-            float *dap_head = p.da_partial + p.head_partial_offset + blk * p.n_tiles * kEpiWarps;
+            // Partial sums of the decay gradient, in the layout of the CUDA-core kernel (so that a suffix re-scan by
+            // that kernel can overwrite some tiles of a pass made by this one): one slice per 64 channels,
+            // [row][slice][t] for a per-step decay, [row][slice][tile][8] for a per-head decay.
+            const int slice = 2 * dtile + half;
+            const bool slice_ok = slice < p.n_dt64;   // the second half of the last tile may hold no channels
+            float *dap_step = p.da_partial + (row * p.n_dt64 + slice) * (static_cast<int64_t>(p.n_tiles) * QT);
+            float *dap_head = p.da_partial + p.head_partial_offset + (row * p.n_dt64 + slice) * p.n_tiles * 8;
             float hs_next = 0.f;
             if (loader) {
                 const int slot0 = it & (kRing - 1);
@@ -794,12 +798,15 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 if (conv) dacc *= a_m;
                 if (t >= L) dacc = 0.f;
                 if (per_step) {
-                    if (t < L) dap_step[t] = dacc;
+                    if (t < L && slice_ok) dap_step[t] = dacc;
                 } else {
                     float wsum = dacc;
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
-                    if (lane == 0) dap_head[k * kEpiWarps + q * 2 + half] = wsum;
+                    if (lane == 0 && slice_ok) {   // four warps per slice fill its eight slots
+                        dap_head[k * 8 + q * 2] = wsum;
+                        dap_head[k * 8 + q * 2 + 1] = 0.f;
+                    }
                 }
                 fence_proxy_async();
                 __syncwarp();
@@ -944,6 +951,10 @@ int make_tmap(CUtensorMap *tm, const void *base, int64_t b, int64_t L, int64_t h
               int64_t sl, int64_t sh) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return EMA_ERR_CUDA;
+    // cuTensorMapEncodeTiled is a driver call and wants a context current on this thread.  A thread that has
+    // made no runtime call yet (e.g. an autograd worker on device 0) has none: bind the device's primary context.
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaSetDevice(dev) != cudaSuccess) return EMA_ERR_CUDA;
     // a dimension of extent 1 may carry any stride; give it a legal one
     if (h == 1) sh = d;
     if (L == 1) sl = h * d;
@@ -1030,6 +1041,7 @@ int launch_fused_bwd_tc(const FusedParams &fp, cudaStream_t stream) {
     p.n_tiles = static_cast<int>((fp.L + tc::QT - 1) / tc::QT);
     p.n_dtiles = static_cast<int>((fp.d + tc::DT - 1) / tc::DT);
     p.n_items = static_cast<int>(fp.b * fp.h * p.n_dtiles);
+    p.n_dt64 = static_cast<int>((fp.d + 63) / 64);
     p.head_partial_offset = kHeadPartialOffset(fp.b * fp.h);
     const int sms = sm_count();
     const int rounds = (p.n_items + sms - 1) / sms;

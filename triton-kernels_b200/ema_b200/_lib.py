@@ -53,6 +53,7 @@ def lib():
         "ema_b200_error_string": (ctypes.c_char_p, [ci]),
         "ema_b200_device_status": (ci, [ci]),
         "ema_b200_set_path": (ci, [ci]),
+        "ema_b200_last_path": (ci, []),
         "ema_b200_tile_steps": (ci, [pp]),
         "ema_b200_tile_states_bytes": (sz, [pp]),
         "ema_b200_bwd_workspace_bytes": (sz, [pp]),
