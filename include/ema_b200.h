@@ -35,7 +35,8 @@ enum {
     EMA_ERR_UNSUPPORTED = -3, /* valid request the library has no kernel for                  */
     EMA_ERR_CUDA = -4,        /* a CUDA call failed; see ema_b200_last_cuda_error()           */
     EMA_ERR_TIMEOUT = -5,     /* a bounded device-side wait ran out                           */
-    EMA_ERR_WORKSPACE = -6    /* workspace pointer null or smaller than _workspace_bytes says */
+    EMA_ERR_WORKSPACE = -6,   /* workspace pointer null or smaller than _workspace_bytes says */
+    EMA_ERR_SCRATCH_LIMIT = -7 /* problem needs more than ema_b200_static_scratch_limit() bytes */
 };
 
 enum { EMA_F32 = 0, EMA_BF16 = 1 };
@@ -136,6 +137,32 @@ int ema_b200_bwd(const ema_b200_problem *p, const void *x, const float *decay, c
                  const float *tile_states, void *dx, float *ddecay, const float *dfinal_state,
                  float *dinit_state, float stop_below, void *workspace, size_t workspace_bytes,
                  void *stream);
+
+/* ---- backward without a workspace ---------------------------------------------------------
+ * (No counterpart in the reference: its backward allocates its temporaries with torch.empty.)
+ *
+ * ema_b200_bwd_static_scratch() is ema_b200_bwd() for callers that can neither hand over a workspace
+ * nor allocate one at the time of the call: hosts that gave all device memory to their own arena at
+ * start-up, latency-critical loops in which cudaMalloc/cudaFree would stall every stream of the
+ * process, and code that runs while the framework's allocator must not be entered.  The partial sums
+ * of the decay gradient go to a fixed array in device memory that belongs to the library's image
+ * (reserved per device when the image is loaded there); the call itself allocates and frees nothing.
+ *
+ *  - Limit: ema_b200_bwd_workspace_bytes(p) must not exceed ema_b200_static_scratch_limit()
+ *    (8 MiB); otherwise EMA_ERR_SCRATCH_LIMIT is returned and nothing is launched.  Use
+ *    ema_b200_bwd() with a caller-owned workspace for larger problems.
+ *  - First call on a device: looks up the array's device address (and, like any first launch, makes
+ *    the CUDA runtime load the kernels).  Make that first call at start-up, outside any stream
+ *    capture; later calls only launch kernels on `stream`.
+ *  - One array per device: two calls on the same device whose kernels may overlap (different
+ *    streams, or several host threads) race on it and give wrong ddecay.  Order them on one stream or
+ *    with events.  Calls on different devices are independent.
+ *  - The array needs no clearing: each call writes every partial sum before reading it.
+ *  - No dfinal_state / dinit_state / stop_below: the sequence-parallel fix-up passes use
+ *    ema_b200_bwd().  Results equal those of ema_b200_bwd() on the same inputs.                  */
+size_t ema_b200_static_scratch_limit(void);
+int ema_b200_bwd_static_scratch(const ema_b200_problem *p, const void *x, const float *decay, const void *dy,
+                                const float *tile_states, void *dx, float *ddecay, void *stream);
 
 /* ---- stage kernels on the reference's folded layouts --------------------------------------
  * X, dout, out, dx: [B, L, T] contiguous, element type `dtype`;  A: [B, L] fp32 with element

@@ -82,6 +82,9 @@ extern "C" const char *ema_b200_error_string(int code) {
         case EMA_ERR_CUDA: return "a CUDA call failed (see ema_b200_last_cuda_error)";
         case EMA_ERR_TIMEOUT: return "a bounded device-side wait ran out";
         case EMA_ERR_WORKSPACE: return "workspace missing or too small";
+        case EMA_ERR_SCRATCH_LIMIT:
+            return "problem needs more scratch than the library's built-in array holds (8 MiB): "
+                   "use ema_b200_bwd with a caller-owned workspace";
         default: return "unknown error code";
     }
 }

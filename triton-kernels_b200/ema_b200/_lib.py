@@ -59,6 +59,8 @@ def lib():
         "ema_b200_bwd_workspace_bytes": (sz, [pp]),
         "ema_b200_fwd": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp]),
         "ema_b200_bwd": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp, sz, vp]),
+        "ema_b200_static_scratch_limit": (sz, []),
+        "ema_b200_bwd_static_scratch": (ci, [pp, vp, vp, vp, vp, vp, vp, vp]),
         "ema_b200_chunk_cumsum": (ci, [vp, i64, i64, vp, i64, i64, ci, vp]),
         "ema_b200_chunk_state": (ci, [vp, vp, vp, ci, i64, i64, i64, ci, vp]),
         "ema_b200_state_passing_fwd": (ci, [vp, vp, i64, i64, vp, vp, i64, i64, i64, vp]),

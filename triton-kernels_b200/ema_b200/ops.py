@@ -144,6 +144,37 @@ def ema_bwd(x, decay, dy, tile_states, *, prescaled_log=False, dfinal_state=None
     return res
 
 
+def ema_bwd_static_scratch(x, decay, dy, tile_states, dx, ddecay, *, prescaled_log=False):
+    """Backward scan into caller-provided `dx` and `ddecay`, with no allocation of any kind.
+
+    The partial sums of the decay gradient go to a fixed array inside the library (one per device,
+    `static_scratch_limit()` bytes); problems that need more raise EmaB200Error.  For callers that must
+    not enter torch's allocator or cudaMalloc at the time of the call.  Every tensor must already have
+    the layout the library wants (unit stride on d, contiguous decay): nothing is copied here.  Calls
+    on one device must not overlap (same stream, or ordered by events): they share the array.  Make
+    the first call on a device at start-up, outside any stream capture: it does the one-time set-up.
+    """
+    if dy.shape != x.shape or dy.dtype != x.dtype or dx.shape != x.shape or dx.dtype != x.dtype:
+        raise ValueError("dy and dx must match x in shape and dtype")
+    if any(t.stride(-1) != 1 and t.shape[-1] > 1 for t in (x, dy, dx)) or not decay.is_contiguous():
+        raise ValueError("x, dy, dx need unit stride on d and decay must be contiguous")
+    if decay.dtype != torch.float32 or ddecay.dtype != torch.float32 or ddecay.shape != decay.shape:
+        raise ValueError("decay and ddecay must be fp32 and of one shape")
+    dev = require_cuda(x, decay, dy, tile_states, dx, ddecay)
+    conv = CONV_PRESCALED_LOG if prescaled_log else CONV_NORTH_STAR
+    p = _problem(x, decay, dx, dy=dy, convention=conv)
+    with torch.cuda.device(dev):
+        rc = lib().ema_b200_bwd_static_scratch(ctypes.byref(p), ptr(x), ptr(decay), ptr(dy), ptr(tile_states),
+                                               ptr(dx), ptr(ddecay), stream_ptr(dev))
+    check("ema_b200_bwd_static_scratch", rc)
+    return dx, ddecay
+
+
+def static_scratch_limit():
+    """Bytes of the library's built-in scratch array (the limit of ema_bwd_static_scratch)."""
+    return int(lib().ema_b200_static_scratch_limit())
+
+
 class EmaFunction(torch.autograd.Function):
     """y_t = a_t y_{t-1} + (1 - a_t) x_t with gradients for x and a."""
 
