@@ -60,46 +60,64 @@ __device__ __forceinline__ float ex2_approx(float x) {
 //   LOWER, shift 0:  M[m,k] = p_k 2^(cs[m]   - cs[k]),  k <= m            forward G
 //   LOWER, shift 1:  M[m,k] = p_k 2^(cs[m-1] - cs[k]),  k <= m-1;  M[m,m] = diag      backward A1
 //   UPPER:           M[m,k] =     2^(cs[k]   - cs[m]),  k >= m                        backward U
-// Every element is independent (one ex2 each), so the 8256 elements of a triangle are dealt out evenly:
-// builder thread t takes every second 8-element chunk of the row pair (t % 64, 127 - t % 64), which
-// always holds 17 chunks.  Values are produced into registers first and stored once the matrix buffer
-// has been released by the MMAs that were reading it.
+// A chunk is 8 consecutive k of one row (16 bytes of bf16).  The chunk that holds the diagonal costs one ex2
+// per element.  Every other chunk is a row scalar times a per-column table: the exponent is split at the end
+// (LOWER) or the start (UPPER) of the chunk, both parts <= 0, so nothing overflows however small a decay is:
+//   LOWER: 2^(cs[m'] - cs[k]) = 2^(cs[m'] - cs[8j+7]) * 2^(cs[8j+7] - cs[k]),   m' = m - shift >= 8j+7
+//   UPPER: 2^(cs[k]  - cs[m]) = 2^(cs[8j-1] - cs[m])  * 2^(cs[k] - cs[8j-1]),   m <= 8j-1
+// wlo[k] = p_k 2^(cs[8j+7] - cs[k]) and rup[k] = 2^(cs[k] - cs[8j-1]) (j = k / 8) are tables in shared memory.
+// Work split over the 128 builder threads: thread t makes the diagonal chunk of row t and every second one of
+// the 15 other chunks of the row pair (t % 64, 127 - t % 64).  Values are produced into registers first and
+// stored once the matrix buffer has been released by the MMAs that were reading it.
 // ---------------------------------------------------------------------------------------------
-constexpr int kMaxChunks = 9;
+constexpr int kOffSlots = 8;               // register slots 0-7: off-diagonal chunks; slot 8: the diagonal chunk
+constexpr int kMaxChunks = kOffSlots + 1;
 struct RowChunks {
     uint4 v[kMaxChunks];
 };
 
-// Calls f(register slot, row, chunk) for this thread's chunks, in a fixed order.
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+    return make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+}
+__device__ __forceinline__ void load8(const float *tab, int c, float (&o)[8]) {   // tab is 16-byte aligned
+    const float4 a = *reinterpret_cast<const float4 *>(tab + c * 8), b = *reinterpret_cast<const float4 *>(tab + c * 8 + 4);
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+
+// Calls f(register slot, row, chunk) for this thread's off-diagonal chunks, in a fixed order.
 template <bool UPPER, typename F>
-__device__ __forceinline__ void for_my_chunks(int t, F f) {
+__device__ __forceinline__ void for_off_chunks(int t, F f) {
     const int pr = t & 63, sel = t >> 6;
-    const int row_long = UPPER ? pr : 127 - pr;   // the row of the pair with more chunks
+    const int row_long = UPPER ? pr : 127 - pr;   // the row of the pair with more off-diagonal chunks
     const int row_short = 127 - row_long;
-    const int n_long = UPPER ? 16 - (row_long >> 3) : (row_long >> 3) + 1;
+    const int n_long = UPPER ? 15 - (row_long >> 3) : (row_long >> 3);
 #pragma unroll
-    for (int s = 0; s < kMaxChunks; ++s) {   // s is a compile-time register index; i the position in the 17-chunk list
+    for (int s = 0; s < kOffSlots; ++s) {   // s is a compile-time register index; i the position in the 15-chunk list
         const int i = 2 * s + sel;
-        if (i >= 17) continue;
+        if (i >= 15) continue;
         const bool in_long = i < n_long;
         const int row = in_long ? row_long : row_short;
         const int j = in_long ? i : i - n_long;                       // index inside the row's chunk list
-        const int chunk = UPPER ? (row >> 3) + j : j;
+        const int chunk = UPPER ? (row >> 3) + 1 + j : j;
         f(s, row, chunk);
     }
 }
+// The same, plus the diagonal chunk of row t (slot 8): every chunk this thread stores.
+template <bool UPPER, typename F>
+__device__ __forceinline__ void for_my_chunks(int t, F f) {
+    for_off_chunks<UPPER>(t, f);
+    f(kOffSlots, t, t >> 3);
+}
 
-// cs_sm and p_sm are 16-byte aligned; a chunk is 8 consecutive k, i.e. two float4 of each table.
 template <int SHIFT>
-__device__ __forceinline__ void compute_lower(int t, const float *cs_sm, const float *p_sm, float diag, RowChunks &out) {
-    for_my_chunks<false>(t, [&](int n, int m, int c) {
-        const float cm = (m - SHIFT >= 0) ? cs_sm[m - SHIFT] : 0.f;
-        const int top = m - SHIFT;
-        const float4 ca = *reinterpret_cast<const float4 *>(cs_sm + c * 8), cb = *reinterpret_cast<const float4 *>(cs_sm + c * 8 + 4);
-        const float4 pa = *reinterpret_cast<const float4 *>(p_sm + c * 8), pb = *reinterpret_cast<const float4 *>(p_sm + c * 8 + 4);
-        const float cs8[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
-        const float p8[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
-        float v[8];
+__device__ __forceinline__ void compute_lower(int t, const float *cs_sm, const float *p_sm, const float *wlo_sm,
+                                              float diag, RowChunks &out) {
+    {   // diagonal chunk of row t
+        const int m = t, c = t >> 3, top = m - SHIFT;
+        const float cm = top >= 0 ? cs_sm[top] : 0.f;
+        float cs8[8], p8[8], v[8];
+        load8(cs_sm, c, cs8);
+        load8(p_sm, c, p8);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const int k = c * 8 + e;
@@ -107,24 +125,38 @@ __device__ __forceinline__ void compute_lower(int t, const float *cs_sm, const f
             const float g = p8[e] * ex2_approx(fminf(cm - cs8[e], 0.f));
             v[e] = (k <= top) ? g : ((SHIFT == 1 && k == m) ? diag : 0.f);
         }
-        out.v[n] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                              pack_bf16x2(v[6], v[7]));
+        out.v[kOffSlots] = pack8(v);
+    }
+    for_off_chunks<false>(t, [&](int n, int m, int c) {
+        const float s = ex2_approx(cs_sm[m - SHIFT] - cs_sm[c * 8 + 7]);   // m - SHIFT >= 8c + 7 here
+        float w[8], v[8];
+        load8(wlo_sm, c, w);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = w[e] * s;
+        out.v[n] = pack8(v);
     });
 }
-__device__ __forceinline__ void compute_upper(int t, const float *cs_sm, RowChunks &out) {
-    for_my_chunks<true>(t, [&](int n, int m, int c) {
+__device__ __forceinline__ void compute_upper(int t, const float *cs_sm, const float *rup_sm, RowChunks &out) {
+    {   // diagonal chunk of row t
+        const int m = t, c = t >> 3;
         const float cm = cs_sm[m];
-        const float4 ca = *reinterpret_cast<const float4 *>(cs_sm + c * 8), cb = *reinterpret_cast<const float4 *>(cs_sm + c * 8 + 4);
-        const float cs8[8] = {ca.x, ca.y, ca.z, ca.w, cb.x, cb.y, cb.z, cb.w};
-        float v[8];
+        float cs8[8], v[8];
+        load8(cs_sm, c, cs8);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
             const int k = c * 8 + e;
             const float g = ex2_approx(fminf(cs8[e] - cm, 0.f));
             v[e] = (k >= m) ? g : 0.f;
         }
-        out.v[n] = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                              pack_bf16x2(v[6], v[7]));
+        out.v[kOffSlots] = pack8(v);
+    }
+    for_off_chunks<true>(t, [&](int n, int m, int c) {
+        const float s = ex2_approx(cs_sm[c * 8 - 1] - cs_sm[m]);          // m <= 8c - 1 here
+        float w[8], v[8];
+        load8(rup_sm, c, w);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = w[e] * s;
+        out.v[n] = pack8(v);
     });
 }
 template <bool UPPER>
@@ -136,13 +168,19 @@ __device__ __forceinline__ void store_chunks(int t, uint8_t *mat, const RowChunk
 
 // Inclusive scan of one value per builder thread (128 threads, 4 warps) through shared memory.
 // Leaves cs_sm[r] = sum_{i<=r} v_i.  Two named-barrier syncs; the first also fences the previous use.
-__device__ __forceinline__ void builder_scan(float v, int r, float *cs_sm, float *warp_tot) {
+// to_end = cs[8j+7] - cs[r] and from_start = cs[r] - cs[8j-1] for r's group of eight, j = r / 8.
+__device__ __forceinline__ void builder_scan(float v, int r, float *cs_sm, float *warp_tot, float &to_end,
+                                             float &from_start) {
     const int lane = r & 31, w = r >> 5;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
         const float n = __shfl_up_sync(0xffffffffu, v, o);
         if (lane >= o) v += n;
     }
+    const float v_end = __shfl_sync(0xffffffffu, v, lane | 7);
+    const float v_before = __shfl_sync(0xffffffffu, v, (lane & ~7) - 1 < 0 ? 0 : (lane & ~7) - 1);
+    to_end = v_end - v;
+    from_start = lane < 8 ? v : v - v_before;
     bar_sync(2, 128);  // everybody has finished reading the previous tile's tables
     if (lane == 31) warp_tot[w] = v;
     bar_sync(2, 128);
@@ -188,7 +226,8 @@ struct FwdSmem {
     static constexpr int e = h + kRing * DT * 4;               // float[kRing][128] E_m per build
     static constexpr int cs = e + kRing * QT * 4;              // float[128] cumulative log2 decay
     static constexpr int pw = cs + QT * 4;                     // float[128] input weights
-    static constexpr int wt = pw + QT * 4;                     // float[4] scan scratch
+    static constexpr int wlo = pw + QT * 4;                    // float[128] column table of the off-diagonal chunks
+    static constexpr int wt = wlo + QT * 4;                    // float[4] scan scratch
     static constexpr int bars = wt + 16;
     // stage full/empty/staged, acc full/empty, matrix full/empty, carry ready
     static constexpr int n_bars = 3 * kFwdStages + 4 + 2 * kFwdMatBufs + kRing;
@@ -202,7 +241,7 @@ static_assert(kFwdSmemBytes <= 227 * 1024, "forward shared memory exceeds the pe
 __global__ void __launch_bounds__(kThreads, 1)
 ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                   const TcParams p) {
-    extern __shared__ uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const uint32_t sbase = smem_u32(smem);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -214,6 +253,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     float *e_sm = reinterpret_cast<float *>(smem + FwdSmem::e);
     float *cs_sm = reinterpret_cast<float *>(smem + FwdSmem::cs);
     float *p_sm = reinterpret_cast<float *>(smem + FwdSmem::pw);
+    float *wlo_sm = reinterpret_cast<float *>(smem + FwdSmem::wlo);
     float *wt_sm = reinterpret_cast<float *>(smem + FwdSmem::wt);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + FwdSmem::abort_flag);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + FwdSmem::tmem_slot);
@@ -416,11 +456,13 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         // one build: scan log2 a, produce the matrix into registers, then store it when the buffer is free
         auto build = [&](float l2, float pw) {
             const int mb = mt % kFwdMatBufs;
-            builder_scan(l2, r, cs_sm, wt_sm);
+            float to_end, from_start;
+            builder_scan(l2, r, cs_sm, wt_sm, to_end, from_start);
             p_sm[r] = pw;
+            wlo_sm[r] = pw * ex2_approx(to_end);
             bar_sync(2, 128);
             RowChunks g;
-            compute_lower<0>(r, cs_sm, p_sm, 0.f, g);
+            compute_lower<0>(r, cs_sm, p_sm, wlo_sm, 0.f, g);
             const float E = exp2f(cs_sm[r]);
             if (lane == 0) mbar_wait(bar(B_MAT_EMPTY + mb), ((mt / kFwdMatBufs) & 1) ^ 1, abort_flag, 8);
             __syncwarp();
@@ -545,7 +587,9 @@ struct BwdSmem {
     static constexpr int rowsc = g + kRing * DT * 4;                   // float[kRowRing][3][128]: Eprev, F, a per build
     static constexpr int cs = rowsc + kRowRing * 3 * QT * 4;           // float[128]
     static constexpr int pw = cs + QT * 4;                             // float[128]
-    static constexpr int wt = pw + QT * 4;                             // float[4]
+    static constexpr int wlo = pw + QT * 4;                            // float[128] column table, lower matrix
+    static constexpr int rup = wlo + QT * 4;                           // float[128] column table, upper matrix
+    static constexpr int wt = rup + QT * 4;                            // float[4]
     static constexpr int bars = wt + 16;
     // stage full/empty, staging full/empty per half, acc full/empty, matrix full/empty, carry ready
     static constexpr int n_bars = 2 * kBwdStages + 4 + 4 + 2 + kRing;
@@ -553,15 +597,22 @@ struct BwdSmem {
     static constexpr int abort_flag = tmem_slot + 4;
     static constexpr int total = abort_flag + 4;
 };
-constexpr int kBwdSmemBytes = BwdSmem::total + 1024;
+constexpr int kBwdSmemBytes = BwdSmem::total;   // no alignment slack: see the kernel
 static_assert(kBwdSmemBytes <= 227 * 1024, "backward shared memory exceeds the per-CTA limit");
 
 __global__ void __launch_bounds__(kThreads, 1)
 ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_g,
                   const __grid_constant__ CUtensorMap tm_o, const TcBwdParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // The 128-byte-swizzled TMA boxes and MMA descriptors need a 1024-byte-aligned base.  This kernel uses all of
+    // the shared memory a CTA may have, so there is no room for aligning by hand: the declaration asks for the
+    // alignment, and a base that lacks it ends the kernel before anything is set up (status 0x2ff).
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = smem_raw;
     const uint32_t sbase = smem_u32(smem);
+    if (sbase & 1023u) {
+        if (threadIdx.x == 0) atomicCAS(&g_tc_status, 0, 0x2ff);
+        return;
+    }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool per_step = p.decay_mode == EMA_DECAY_PER_STEP;
     const int conv = p.convention;
@@ -572,6 +623,8 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     float *rowsc = reinterpret_cast<float *>(smem + BwdSmem::rowsc);
     float *cs_sm = reinterpret_cast<float *>(smem + BwdSmem::cs);
     float *p_sm = reinterpret_cast<float *>(smem + BwdSmem::pw);
+    float *wlo_sm = reinterpret_cast<float *>(smem + BwdSmem::wlo);
+    float *rup_sm = reinterpret_cast<float *>(smem + BwdSmem::rup);
     float *wt_sm = reinterpret_cast<float *>(smem + BwdSmem::wt);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + BwdSmem::abort_flag);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + BwdSmem::tmem_slot);
@@ -822,13 +875,16 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         // v: raw decay value of step r of the tile; v_edge: of the step right after the tile (identity past L)
         auto build = [&](float v, float v_edge) {
             const float l2 = log2_decay(v);
-            builder_scan(l2, r, cs_sm, wt_sm);
+            float to_end, from_start;
+            builder_scan(l2, r, cs_sm, wt_sm, to_end, from_start);
             const float pw = conv ? 1.f : 1.f - v;
             p_sm[r] = pw;
+            wlo_sm[r] = pw * ex2_approx(to_end);
+            rup_sm[r] = ex2_approx(from_start);
             bar_sync(2, 128);
             RowChunks ca, cu;
-            compute_lower<1>(r, cs_sm, p_sm, diag, ca);
-            compute_upper(r, cs_sm, cu);
+            compute_lower<1>(r, cs_sm, p_sm, wlo_sm, diag, ca);
+            compute_upper(r, cs_sm, rup_sm, cu);
             const float cs_r = cs_sm[r];
             const float Eprev = exp2f(cs_r - l2);                       // prod_{j<r} a_j
             const float Fr = exp2f(cs_sm[QT - 1] - cs_r + log2_decay(v_edge));
