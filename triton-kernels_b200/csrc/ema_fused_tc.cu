@@ -14,12 +14,15 @@
 // move the tile.
 //
 // One persistent CTA per SM walks its work items (scan row, 128-channel tile) and, inside an item, the
-// tiles in sequence order.  15 warps, each with one job:
-//   warp 0      TMA producer (x tiles, and dy tiles in the backward) into a ring of stages
-//   warp 1      MMA issuer; owns the TMEM allocation
-//   warps 2-9   epilogue: TMEM lane quadrant (warp % 4) x one half of the 128 channels
-//   warps 10-13 build the decay matrices (once per head for a time-invariant decay, per tile otherwise)
-//   warp 14     issues the TMA stores of finished tiles and hands the stages back to the producer
+// tiles in sequence order.  20 warps in five warpgroups, each warp with one job:
+//   warp 0       TMA producer (x tiles, and dy tiles in the backward) into a ring of stages
+//   warp 1       MMA issuer; owns the TMEM allocation
+//   warp 2       issues the TMA stores of finished tiles and hands the stages back to the producer
+//   warp 3       idle (fills the first warpgroup)
+//   warps 4-11   epilogue: TMEM lane quadrant (warp % 4) x one half of the 128 channels
+//   warps 12-19  build the decay matrices (once per head for a time-invariant decay, per tile otherwise)
+// Registers follow the work (setmaxnreg): the first warpgroup and the builders give theirs up, the epilogue
+// warpgroups take them.
 // The warps meet only through mbarriers: stage full/empty, accumulator full/empty, matrix full/empty,
 // carry ready (a ring of 4 so that the warp on the serial carry chain can run ahead of the others), and
 // stage staged.  Every wait is bounded (ema_tc_common.cuh): after a timeout the roles run their loops to
@@ -36,12 +39,16 @@ constexpr int kBlockCols = 64;             // channels per 128-byte-swizzled blo
 constexpr int kBlockBytes = QT * 128;      // [128 steps x 64 channels] bf16
 constexpr int kTileBytes = 2 * kBlockBytes;
 constexpr int kMatBytes = QT * QT * 2;
-constexpr int kThreads = 480;              // 15 warps
-constexpr int kEpiThread0 = 64;            // warps 2-9
+constexpr int kThreads = 640;              // 20 warps
+constexpr int kStoreThread = 64;           // warp 2, lane 0
+constexpr int kEpiThread0 = 128;           // warps 4-11
 constexpr int kEpiThreads = 256;
 constexpr int kEpiWarps = kEpiThreads / 32;
-constexpr int kBuildThread0 = 320;         // warps 10-13
-constexpr int kStoreThread = 448;          // warp 14, lane 0
+constexpr int kBuildThread0 = 384;         // warps 12-19
+constexpr int kBuildThreads = 256;
+constexpr int kBuildWarps = kBuildThreads / 32;
+// registers per thread after the role split; 128*48 + 256*136 + 256*80 = 640*96, the allocation at launch
+constexpr int kRegsLight = 48, kRegsEpilogue = 136, kRegsBuilder = 80;
 constexpr int kRing = 4;                   // depth of the carry ring and of the per-row scalar tables
 constexpr uint32_t kIdesc = make_idesc_bf16(QT, DT, 0, 1);
 
@@ -49,6 +56,10 @@ constexpr uint32_t kIdesc = make_idesc_bf16(QT, DT, 0, 1);
 __device__ __forceinline__ void bar_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+template <int N>
+__device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -66,23 +77,33 @@ __device__ __forceinline__ float ex2_approx(float x) {
 //   LOWER: 2^(cs[m'] - cs[k]) = 2^(cs[m'] - cs[8j+7]) * 2^(cs[8j+7] - cs[k]),   m' = m - shift >= 8j+7
 //   UPPER: 2^(cs[k]  - cs[m]) = 2^(cs[8j-1] - cs[m])  * 2^(cs[k] - cs[8j-1]),   m <= 8j-1
 // wlo[k] = p_k 2^(cs[8j+7] - cs[k]) and rup[k] = 2^(cs[k] - cs[8j-1]) (j = k / 8) are tables in shared memory.
-// Work split over the 128 builder threads: thread t makes the diagonal chunk of row t and every second one of
-// the 15 other chunks of the row pair (t % 64, 127 - t % 64).  Values are produced into registers first and
-// stored once the matrix buffer has been released by the MMAs that were reading it.
+// Work split over the 256 builder threads: thread t makes one half (4 elements) of the diagonal chunk of row
+// t % 128 and every fourth one of the 15 other chunks of the row pair (t % 64, 127 - t % 64).  Which chunks a
+// thread owns, and where they are read from and written to, never changes: those offsets are worked out once
+// per kernel (OffGeom, DiagGeom), so that a build is little more than loads, multiplies, packs and stores.
+// Values are produced into registers first and stored once the matrix buffer has been released by the MMAs
+// that were reading it.
 // ---------------------------------------------------------------------------------------------
-constexpr int kOffSlots = 8;               // register slots 0-7: off-diagonal chunks; slot 8: the diagonal chunk
-constexpr int kMaxChunks = kOffSlots + 1;
+constexpr int kOffSlots = 4;
 struct RowChunks {
-    uint4 v[kMaxChunks];
+    uint4 v[kOffSlots];   // off-diagonal chunks
+    uint2 dg;             // this thread's half of a diagonal chunk
 };
-
-__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
-    return make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
-}
-__device__ __forceinline__ void load8(const float *tab, int c, float (&o)[8]) {   // tab is 16-byte aligned
-    const float4 a = *reinterpret_cast<const float4 *>(tab + c * 8), b = *reinterpret_cast<const float4 *>(tab + c * 8 + 4);
-    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
-}
+// Off-diagonal chunks of one matrix, per register slot.  All offsets in bytes.
+struct OffGeom {
+    uint32_t a[kOffSlots];    // into the cs table: the row's entry, cs[m - shift] (LOWER) or cs[m] (UPPER)
+    uint32_t c[kOffSlots];    // into a 128-float table: first column of the chunk (8 * chunk floats)
+    uint32_t st[kOffSlots];   // destination of the chunk, relative to the start of the matrix storage
+    bool last_valid;          // the last slot is empty for a quarter of the threads
+};
+// This thread's half of the diagonal chunk of row m = t % 128.
+struct DiagGeom {
+    uint32_t k;      // byte offset of its 4 columns in a 128-float table
+    uint32_t top;    // byte offset of cs[m - shift] (LOWER; 0 with has_top false when m - shift < 0) or cs[m] (UPPER)
+    uint32_t st;     // destination, relative to the start of the matrix storage
+    int lim;         // element e of the half is inside the triangle iff e <= lim (LOWER) or e >= lim (UPPER)
+    bool has_top;
+};
 
 // Calls f(register slot, row, chunk) for this thread's off-diagonal chunks, in a fixed order.
 template <bool UPPER, typename F>
@@ -93,7 +114,7 @@ __device__ __forceinline__ void for_off_chunks(int t, F f) {
     const int n_long = UPPER ? 15 - (row_long >> 3) : (row_long >> 3);
 #pragma unroll
     for (int s = 0; s < kOffSlots; ++s) {   // s is a compile-time register index; i the position in the 15-chunk list
-        const int i = 2 * s + sel;
+        const int i = 4 * s + sel;
         if (i >= 15) continue;
         const bool in_long = i < n_long;
         const int row = in_long ? row_long : row_short;
@@ -102,93 +123,109 @@ __device__ __forceinline__ void for_off_chunks(int t, F f) {
         f(s, row, chunk);
     }
 }
-// The same, plus the diagonal chunk of row t (slot 8): every chunk this thread stores.
-template <bool UPPER, typename F>
-__device__ __forceinline__ void for_my_chunks(int t, F f) {
-    for_off_chunks<UPPER>(t, f);
-    f(kOffSlots, t, t >> 3);
+// store_off(row, chunk) -> byte offset of a chunk in the matrix storage
+template <bool UPPER, int SHIFT, typename F>
+__device__ __forceinline__ void make_geom(int t, OffGeom &og, DiagGeom &dg, F store_off) {
+#pragma unroll
+    for (int s = 0; s < kOffSlots; ++s) og.a[s] = og.c[s] = og.st[s] = 0;
+    og.last_valid = 4 * (kOffSlots - 1) + (t >> 6) < 15;
+    for_off_chunks<UPPER>(t, [&](int s, int m, int c) {
+        og.a[s] = 4u * static_cast<uint32_t>(UPPER ? m : m - SHIFT);
+        og.c[s] = 32u * static_cast<uint32_t>(c);
+        og.st[s] = store_off(m, c);
+    });
+    const int m = t & 127, hb = t >> 7, k0 = (m >> 3) * 8 + 4 * hb;
+    dg.k = 4u * static_cast<uint32_t>(k0);
+    dg.has_top = UPPER || m - SHIFT >= 0;
+    dg.top = dg.has_top ? 4u * static_cast<uint32_t>(UPPER ? m : m - SHIFT) : 0u;
+    dg.st = store_off(m, m >> 3) + 8u * static_cast<uint32_t>(hb);
+    dg.lim = UPPER ? m - k0 : m - SHIFT - k0;
 }
 
-template <int SHIFT>
-__device__ __forceinline__ void compute_lower(int t, const float *cs_sm, const float *p_sm, const float *wlo_sm,
-                                              float diag, RowChunks &out) {
-    {   // diagonal chunk of row t
-        const int m = t, c = t >> 3, top = m - SHIFT;
-        const float cm = top >= 0 ? cs_sm[top] : 0.f;
-        float cs8[8], p8[8], v[8];
-        load8(cs_sm, c, cs8);
-        load8(p_sm, c, p8);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const int k = c * 8 + e;
-            // past the diagonal the exponent is positive: clamp it so that the discarded value stays finite
-            const float g = p8[e] * ex2_approx(fminf(cm - cs8[e], 0.f));
-            v[e] = (k <= top) ? g : ((SHIFT == 1 && k == m) ? diag : 0.f);
-        }
-        out.v[kOffSlots] = pack8(v);
-    }
-    for_off_chunks<false>(t, [&](int n, int m, int c) {
-        const float s = ex2_approx(cs_sm[m - SHIFT] - cs_sm[c * 8 + 7]);   // m - SHIFT >= 8c + 7 here
-        float w[8], v[8];
-        load8(wlo_sm, c, w);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = w[e] * s;
-        out.v[n] = pack8(v);
-    });
+__device__ __forceinline__ float ld_f32(const uint8_t *base, uint32_t off) {
+    return *reinterpret_cast<const float *>(base + off);
 }
-__device__ __forceinline__ void compute_upper(int t, const float *cs_sm, const float *rup_sm, RowChunks &out) {
-    {   // diagonal chunk of row t
-        const int m = t, c = t >> 3;
-        const float cm = cs_sm[m];
-        float cs8[8], v[8];
-        load8(cs_sm, c, cs8);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-            const int k = c * 8 + e;
-            const float g = ex2_approx(fminf(cs8[e] - cm, 0.f));
-            v[e] = (k >= m) ? g : 0.f;
-        }
-        out.v[kOffSlots] = pack8(v);
-    }
-    for_off_chunks<true>(t, [&](int n, int m, int c) {
-        const float s = ex2_approx(cs_sm[c * 8 - 1] - cs_sm[m]);          // m <= 8c - 1 here
-        float w[8], v[8];
-        load8(rup_sm, c, w);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) v[e] = w[e] * s;
-        out.v[n] = pack8(v);
-    });
+__device__ __forceinline__ float4 ld_f32x4(const uint8_t *base, uint32_t off) {
+    return *reinterpret_cast<const float4 *>(base + off);
 }
+
+// off-diagonal chunks: row scalar x column table
 template <bool UPPER>
-__device__ __forceinline__ void store_chunks(int t, uint8_t *mat, const RowChunks &in) {
-    for_my_chunks<UPPER>(t, [&](int n, int m, int c) {
-        *reinterpret_cast<uint4 *>(mat + (c >> 3) * (QT * 128) + sw128_offset(m, c & 7)) = in.v[n];
-    });
+__device__ __forceinline__ void compute_off(const OffGeom &g, const uint8_t *cs_b, const uint8_t *tab_b, RowChunks &out) {
+#pragma unroll
+    for (int s = 0; s < kOffSlots; ++s) {
+        if (s == kOffSlots - 1 && !g.last_valid) continue;
+        const float ca = ld_f32(cs_b, g.a[s]);
+        const float cb = ld_f32(cs_b, UPPER ? g.c[s] - 4u : g.c[s] + 28u);   // cs[8c - 1] | cs[8c + 7]
+        const float sc = ex2_approx(UPPER ? cb - ca : ca - cb);     // <= 0 either way
+        const float4 w0 = ld_f32x4(tab_b, g.c[s]), w1 = ld_f32x4(tab_b, g.c[s] + 16);
+        out.v[s] = make_uint4(pack_bf16x2(w0.x * sc, w0.y * sc), pack_bf16x2(w0.z * sc, w0.w * sc),
+                              pack_bf16x2(w1.x * sc, w1.y * sc), pack_bf16x2(w1.z * sc, w1.w * sc));
+    }
+}
+// diagonal half chunks: one ex2 per element; `diag` is the value on the diagonal itself (SHIFT = 1 only)
+template <int SHIFT>
+__device__ __forceinline__ void compute_diag_lower(const DiagGeom &g, const uint8_t *cs_b, const uint8_t *p_b, float diag,
+                                                   RowChunks &out) {
+    const float cm = g.has_top ? ld_f32(cs_b, g.top) : 0.f;
+    const float4 c4 = ld_f32x4(cs_b, g.k), p4 = ld_f32x4(p_b, g.k);
+    const float cs4[4] = {c4.x, c4.y, c4.z, c4.w}, pw4[4] = {p4.x, p4.y, p4.z, p4.w};
+    float v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        // past the diagonal the exponent is positive: clamp it so that the discarded value stays finite
+        const float gv = pw4[e] * ex2_approx(fminf(cm - cs4[e], 0.f));
+        v[e] = (e <= g.lim) ? gv : ((SHIFT == 1 && e == g.lim + 1) ? diag : 0.f);
+    }
+    out.dg = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+}
+__device__ __forceinline__ void compute_diag_upper(const DiagGeom &g, const uint8_t *cs_b, RowChunks &out) {
+    const float cm = ld_f32(cs_b, g.top);
+    const float4 c4 = ld_f32x4(cs_b, g.k);
+    const float cs4[4] = {c4.x, c4.y, c4.z, c4.w};
+    float v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v[e] = (e >= g.lim) ? ex2_approx(fminf(cs4[e] - cm, 0.f)) : 0.f;
+    out.dg = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+}
+__device__ __forceinline__ void store_matrix(const OffGeom &og, const DiagGeom &dg, uint8_t *mat, const RowChunks &in) {
+#pragma unroll
+    for (int s = 0; s < kOffSlots; ++s) {
+        if (s == kOffSlots - 1 && !og.last_valid) continue;
+        *reinterpret_cast<uint4 *>(mat + og.st[s]) = in.v[s];
+    }
+    *reinterpret_cast<uint2 *>(mat + dg.st) = in.dg;
 }
 
-// Inclusive scan of one value per builder thread (128 threads, 4 warps) through shared memory.
-// Leaves cs_sm[r] = sum_{i<=r} v_i.  Two named-barrier syncs; the first also fences the previous use.
+// Inclusive scan of one value per row (builder threads 0-127, 4 warps) through shared memory; all 256 builder
+// threads call it.  Leaves cs_sm[r] = sum_{i<=r} v_i, visible to the first 128 threads only: the caller's next
+// 256-thread barrier publishes it.  The first barrier also fences the previous use of the tables.
 // to_end = cs[8j+7] - cs[r] and from_start = cs[r] - cs[8j-1] for r's group of eight, j = r / 8.
-__device__ __forceinline__ void builder_scan(float v, int r, float *cs_sm, float *warp_tot, float &to_end,
+__device__ __forceinline__ void builder_scan(float v, int t, float *cs_sm, float *warp_tot, float &to_end,
                                              float &from_start) {
-    const int lane = r & 31, w = r >> 5;
+    const int lane = t & 31, w = t >> 5;
+    const bool scanner = t < 128;
+    if (scanner) {
 #pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-        const float n = __shfl_up_sync(0xffffffffu, v, o);
-        if (lane >= o) v += n;
+        for (int o = 1; o < 32; o <<= 1) {
+            const float n = __shfl_up_sync(0xffffffffu, v, o);
+            if (lane >= o) v += n;
+        }
+        const float v_end = __shfl_sync(0xffffffffu, v, lane | 7);
+        const float v_before = __shfl_sync(0xffffffffu, v, lane < 8 ? 0 : (lane & ~7) - 1);
+        to_end = v_end - v;
+        from_start = lane < 8 ? v : v - v_before;
     }
-    const float v_end = __shfl_sync(0xffffffffu, v, lane | 7);
-    const float v_before = __shfl_sync(0xffffffffu, v, (lane & ~7) - 1 < 0 ? 0 : (lane & ~7) - 1);
-    to_end = v_end - v;
-    from_start = lane < 8 ? v : v - v_before;
-    bar_sync(2, 128);  // everybody has finished reading the previous tile's tables
-    if (lane == 31) warp_tot[w] = v;
-    bar_sync(2, 128);
-    float off = 0.f;
+    bar_sync(2, kBuildThreads);  // everybody has finished reading the previous tile's tables
+    if (scanner) {
+        if (lane == 31) warp_tot[w] = v;
+        bar_sync(3, 128);
+        float off = 0.f;
 #pragma unroll
-    for (int i = 0; i < 3; ++i)
-        if (i < w) off += warp_tot[i];
-    cs_sm[r] = v + off;
+        for (int i = 0; i < 3; ++i)
+            if (i < w) off += warp_tot[i];
+        cs_sm[t] = v + off;
+    }
 }
 
 // dst[0..min(32, n_valid)) = y; deliberately not inlined (see the forward epilogue)
@@ -270,7 +307,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             mbar_init(bar(B_STAGED + i), kEpiWarps);
         }
         for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiWarps); }
-        for (int i = 0; i < kFwdMatBufs; ++i) { mbar_init(bar(B_MAT_FULL + i), 4); mbar_init(bar(B_MAT_EMPTY + i), 1); }
+        for (int i = 0; i < kFwdMatBufs; ++i) { mbar_init(bar(B_MAT_FULL + i), kBuildWarps); mbar_init(bar(B_MAT_EMPTY + i), 1); }
         for (int i = 0; i < kRing; ++i) mbar_init(bar(B_H + i), 2);           // one arrival per channel half
         *abort_flag = 0;
         fence_barrier_init();
@@ -293,66 +330,92 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     // log2 of the multiplicative decay of one step
     auto log2_decay = [&](float v) { return conv ? v * 1.4426950408889634f : log2f(v); };
 
-    if (warp == 0) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            uint32_t it = 0;
-            for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                const int dtile = static_cast<int>(item % p.n_dtiles);
-                const int64_t row = item / p.n_dtiles;
-                const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
-                for (int k = 0; k < p.n_tiles; ++k, ++it) {
-                    const int s = it % kFwdStages;
-                    const uint32_t ph = (it / kFwdStages) & 1;
-                    if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 1)) break;
-                    mbar_expect_tx(bar(B_FULL + s), kTileBytes);
-                    const uint32_t dst = sbase + FwdSmem::x + s * kTileBytes;
-                    tma_load_4d(dst, &tm_x, bar(B_FULL + s), dtile * DT, hi, k * QT, bi);
-                    tma_load_4d(dst + kBlockBytes, &tm_x, bar(B_FULL + s), dtile * DT + kBlockCols, hi, k * QT, bi);
+    if (warp < 4) {
+        reg_dec<kRegsLight>();
+        if (warp == 0) {
+            // ---------------- TMA producer ----------------
+            if (lane == 0) {
+                uint32_t it = 0;
+                for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
+                    const int dtile = static_cast<int>(item % p.n_dtiles);
+                    const int64_t row = item / p.n_dtiles;
+                    const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
+                    for (int k = 0; k < p.n_tiles; ++k, ++it) {
+                        const int s = it % kFwdStages;
+                        const uint32_t ph = (it / kFwdStages) & 1;
+                        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 1)) break;
+                        mbar_expect_tx(bar(B_FULL + s), kTileBytes);
+                        const uint32_t dst = sbase + FwdSmem::x + s * kTileBytes;
+                        tma_load_4d(dst, &tm_x, bar(B_FULL + s), dtile * DT, hi, k * QT, bi);
+                        tma_load_4d(dst + kBlockBytes, &tm_x, bar(B_FULL + s), dtile * DT + kBlockCols, hi, k * QT, bi);
+                    }
                 }
             }
-        }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            // A matrix is built per tile (per-step decay) or whenever the head changes (time-invariant
-            // decay); the MMA issuer, the epilogue and the builders evaluate the same predicate, so they
-            // agree on the build counter mt without talking to each other.
-            uint32_t it = 0, mt = 0;
-            int cur_head = -1, mb_cur = 0;
-            for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                const int hi = static_cast<int>((item / p.n_dtiles) % p.h);
-                for (int k = 0; k < p.n_tiles; ++k, ++it) {
-                    const int s = it % kFwdStages;
-                    const uint32_t ph = (it / kFwdStages) & 1;
-                    const int acc = it & 1;
-                    const uint32_t aph = (it >> 1) & 1;
-                    if (per_step || hi != cur_head) {
-                        // every MMA that read the previous head's matrix has been issued: release its buffer
-                        if (!per_step && mt > 0) umma_commit(bar(B_MAT_EMPTY + ((mt - 1) % kFwdMatBufs)));
-                        mb_cur = mt % kFwdMatBufs;
-                        if (!mbar_wait(bar(B_MAT_FULL + mb_cur), (mt / kFwdMatBufs) & 1, abort_flag, 2)) break;
-                        cur_head = hi;
-                        ++mt;
+        } else if (warp == 1) {
+            // ---------------- MMA issuer ----------------
+            if (lane == 0) {
+                // A matrix is built per tile (per-step decay) or whenever the head changes (time-invariant
+                // decay); the MMA issuer, the epilogue and the builders evaluate the same predicate, so they
+                // agree on the build counter mt without talking to each other.
+                uint32_t it = 0, mt = 0;
+                int cur_head = -1, mb_cur = 0;
+                for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
+                    const int hi = static_cast<int>((item / p.n_dtiles) % p.h);
+                    for (int k = 0; k < p.n_tiles; ++k, ++it) {
+                        const int s = it % kFwdStages;
+                        const uint32_t ph = (it / kFwdStages) & 1;
+                        const int acc = it & 1;
+                        const uint32_t aph = (it >> 1) & 1;
+                        if (per_step || hi != cur_head) {
+                            // every MMA that read the previous head's matrix has been issued: release its buffer
+                            if (!per_step && mt > 0) umma_commit(bar(B_MAT_EMPTY + ((mt - 1) % kFwdMatBufs)));
+                            mb_cur = mt % kFwdMatBufs;
+                            if (!mbar_wait(bar(B_MAT_FULL + mb_cur), (mt / kFwdMatBufs) & 1, abort_flag, 2)) break;
+                            cur_head = hi;
+                            ++mt;
+                        }
+                        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 3)) break;
+                        if (!mbar_wait(bar(B_ACC_EMPTY + acc), aph ^ 1, abort_flag, 4)) break;
+                        tc_fence_after_sync();
+                        const uint64_t ad0 = make_desc_sw128(sbase + FwdSmem::mat + mb_cur * kMatBytes, 16, 1024);
+                        const uint64_t bd0 = tile_desc(sbase + FwdSmem::x + s * kTileBytes);
+    #pragma unroll
+                        for (int kb = 0; kb < QT / 16; ++kb) {
+                            // descriptor start addresses are in 16-byte units: next K step inside / across 64-wide K blocks
+                            const uint64_t ad = ad0 + (((kb >> 2) * (QT * 128) + (kb & 3) * 32) >> 4);
+                            const uint64_t bd = bd0 + ((kb * 2048) >> 4);
+                            umma_bf16(tmem_base + acc * DT, ad, bd, kIdesc, kb > 0 ? 1u : 0u);
+                        }
+                        umma_commit(bar(B_ACC_FULL + acc));
+                        if (per_step) umma_commit(bar(B_MAT_EMPTY + mb_cur));
                     }
-                    if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 3)) break;
-                    if (!mbar_wait(bar(B_ACC_EMPTY + acc), aph ^ 1, abort_flag, 4)) break;
-                    tc_fence_after_sync();
-                    const uint64_t ad0 = make_desc_sw128(sbase + FwdSmem::mat + mb_cur * kMatBytes, 16, 1024);
-                    const uint64_t bd0 = tile_desc(sbase + FwdSmem::x + s * kTileBytes);
-#pragma unroll
-                    for (int kb = 0; kb < QT / 16; ++kb) {
-                        // descriptor start addresses are in 16-byte units: next K step inside / across 64-wide K blocks
-                        const uint64_t ad = ad0 + (((kb >> 2) * (QT * 128) + (kb & 3) * 32) >> 4);
-                        const uint64_t bd = bd0 + ((kb * 2048) >> 4);
-                        umma_bf16(tmem_base + acc * DT, ad, bd, kIdesc, kb > 0 ? 1u : 0u);
-                    }
-                    umma_commit(bar(B_ACC_FULL + acc));
-                    if (per_step) umma_commit(bar(B_MAT_EMPTY + mb_cur));
                 }
+            }
+        } else {
+            // ---------------- TMA store issuer ----------------
+            if (tid == kStoreThread) {
+                uint32_t it = 0;
+                for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
+                    const int dtile = static_cast<int>(item % p.n_dtiles);
+                    const int64_t row = item / p.n_dtiles;
+                    const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
+                    const bool two = dtile * DT + kBlockCols < p.d;   // the second 64-channel block exists
+                    for (int k = 0; k < p.n_tiles; ++k, ++it) {
+                        const int s = it % kFwdStages;
+                        if (!mbar_wait(bar(B_STAGED + s), (it / kFwdStages) & 1, abort_flag, 9)) break;
+                        const uint32_t src = sbase + FwdSmem::x + s * kTileBytes;
+                        tma_store_4d(&tm_y, src, dtile * DT, hi, k * QT, bi);
+                        if (two) tma_store_4d(&tm_y, src + kBlockBytes, dtile * DT + kBlockCols, hi, k * QT, bi);
+                        tma_store_commit();
+                        tma_store_wait_read<0>();          // the stage has been read: hand it back to the producer
+                        mbar_arrive(bar(B_EMPTY + s));
+                    }
+                }
+                tma_store_wait_all();
             }
         }
     } else if (tid < kBuildThread0) {
+        reg_inc<kRegsEpilogue>();
         // ---------------- epilogue ----------------
         // Thread (q, lane, half) owns row m = 32 q + lane and channels [64 half, 64 half + 64) of the tile,
         // handled 32 at a time.  The two threads of row 127 are the serial carry chain: they publish the
@@ -448,26 +511,40 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 if (lane == 0) mbar_arrive(bar(B_STAGED + s));
             }
         }
-    } else if (tid < kStoreThread) {
+    } else {
+        reg_dec<kRegsBuilder>();
         // ---------------- matrix builders ----------------
-        const int r = tid - kBuildThread0;
+        const int bt = tid - kBuildThread0;   // 0-255; threads 0-127 also own row r = bt of the per-row tables
+        const int r = bt & 127;
+        const bool row_owner = bt < 128;
         uint32_t mt = 0;
         int cur_head = -1;
+        OffGeom og;
+        DiagGeom dgm;
+        // a forward matrix is two 64-wide K blocks of [128 rows x 128 B], one after the other
+        make_geom<false, 0>(bt, og, dgm, [](int m, int c) {
+            return static_cast<uint32_t>((c >> 3) * (QT * 128)) + sw128_offset(m, c & 7);
+        });
+        const uint8_t *cs_b = smem + FwdSmem::cs, *p_b = smem + FwdSmem::pw, *wlo_b = smem + FwdSmem::wlo;
         // one build: scan log2 a, produce the matrix into registers, then store it when the buffer is free
+        // (l2 and pw are read from the row owners only)
         auto build = [&](float l2, float pw) {
             const int mb = mt % kFwdMatBufs;
-            float to_end, from_start;
-            builder_scan(l2, r, cs_sm, wt_sm, to_end, from_start);
-            p_sm[r] = pw;
-            wlo_sm[r] = pw * ex2_approx(to_end);
-            bar_sync(2, 128);
+            float to_end = 0.f, from_start = 0.f;
+            builder_scan(l2, bt, cs_sm, wt_sm, to_end, from_start);
+            if (row_owner) {
+                p_sm[r] = pw;
+                wlo_sm[r] = pw * ex2_approx(to_end);
+            }
+            bar_sync(2, kBuildThreads);
             RowChunks g;
-            compute_lower<0>(r, cs_sm, p_sm, wlo_sm, 0.f, g);
-            const float E = exp2f(cs_sm[r]);
+            compute_diag_lower<0>(dgm, cs_b, p_b, 0.f, g);
+            compute_off<false>(og, cs_b, wlo_b, g);
+            const float E = ex2_approx(cs_sm[r]);
             if (lane == 0) mbar_wait(bar(B_MAT_EMPTY + mb), ((mt / kFwdMatBufs) & 1) ^ 1, abort_flag, 8);
             __syncwarp();
-            store_chunks<false>(r, smem + FwdSmem::mat + mb * kMatBytes, g);
-            e_sm[(mt & (kRing - 1)) * QT + r] = E;
+            store_matrix(og, dgm, smem + FwdSmem::mat + mb * kMatBytes, g);
+            if (row_owner) e_sm[(mt & (kRing - 1)) * QT + r] = E;
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_MAT_FULL + mb));
@@ -484,46 +561,25 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     cur_head = static_cast<int>(hi);
                     build(log2_decay(v), conv ? 1.f : 1.f - v);
                 }
-                if (p.log_decay_sum && r == 0 && dtile == 0)
+                if (p.log_decay_sum && bt == 0 && dtile == 0)
                     p.log_decay_sum[row] = static_cast<float>(L) * (conv ? v : logf(v));
                 continue;
             }
             // per-step decay: the raw value of step r of the next tile is fetched one tile ahead
             float logsum = 0.f;
-            float v_next = (r < L) ? arow[static_cast<int64_t>(r) * p.a_sl] : (conv ? 0.f : 1.f);
+            const float ident = conv ? 0.f : 1.f;   // raw value of an identity step (past L)
+            float v_next = (row_owner && r < L) ? arow[static_cast<int64_t>(r) * p.a_sl] : ident;
             for (int k = 0; k < p.n_tiles; ++k) {
                 const float v = v_next;
                 if (k + 1 < p.n_tiles) {
                     const int t = (k + 1) * QT + r;
-                    v_next = t < L ? arow[static_cast<int64_t>(t) * p.a_sl] : (conv ? 0.f : 1.f);
+                    v_next = (row_owner && t < L) ? arow[static_cast<int64_t>(t) * p.a_sl] : ident;
                 }
                 build(log2_decay(v), conv ? 1.f : 1.f - v);
                 // cs_sm[127] now holds log2 of the product of this tile's decays
-                if (p.log_decay_sum && r == 0) logsum += cs_sm[QT - 1] * 0.6931471805599453f;
+                if (p.log_decay_sum && bt == 0) logsum += cs_sm[QT - 1] * 0.6931471805599453f;
             }
-            if (p.log_decay_sum && r == 0 && dtile == 0) p.log_decay_sum[row] = logsum;
-        }
-    } else {
-        // ---------------- TMA store issuer ----------------
-        if (tid == kStoreThread) {
-            uint32_t it = 0;
-            for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                const int dtile = static_cast<int>(item % p.n_dtiles);
-                const int64_t row = item / p.n_dtiles;
-                const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
-                const bool two = dtile * DT + kBlockCols < p.d;   // the second 64-channel block exists
-                for (int k = 0; k < p.n_tiles; ++k, ++it) {
-                    const int s = it % kFwdStages;
-                    if (!mbar_wait(bar(B_STAGED + s), (it / kFwdStages) & 1, abort_flag, 9)) break;
-                    const uint32_t src = sbase + FwdSmem::x + s * kTileBytes;
-                    tma_store_4d(&tm_y, src, dtile * DT, hi, k * QT, bi);
-                    if (two) tma_store_4d(&tm_y, src + kBlockBytes, dtile * DT + kBlockCols, hi, k * QT, bi);
-                    tma_store_commit();
-                    tma_store_wait_read<0>();          // the stage has been read: hand it back to the producer
-                    mbar_arrive(bar(B_EMPTY + s));
-                }
-            }
-            tma_store_wait_all();
+            if (p.log_decay_sum && bt == 0 && dtile == 0) p.log_decay_sum[row] = logsum;
         }
     }
 
@@ -638,7 +694,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         for (int i = 0; i < kBwdStages; ++i) { mbar_init(bar(B_FULL + i), 1); mbar_init(bar(B_EMPTY + i), 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(bar(B_STG_FULL + i), kEpiWarps / 2); mbar_init(bar(B_STG_EMPTY + i), 1); }
         for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiWarps); }
-        mbar_init(bar(B_MAT_FULL), 4);
+        mbar_init(bar(B_MAT_FULL), kBuildWarps);
         mbar_init(bar(B_MAT_EMPTY), 1);
         // carry ready: the two halves of the adjoint row and the four warps that fetch the saved state
         for (int i = 0; i < kRing; ++i) mbar_init(bar(B_G + i), 6);
@@ -662,71 +718,100 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     const int64_t n_items = p.n_items;
     auto log2_decay = [&](float v) { return conv ? v * 1.4426950408889634f : log2f(v); };
 
-    if (warp == 0) {
-        // ---------------- TMA producer ----------------
-        if (lane == 0) {
-            uint32_t it = 0;
-            for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                const int dtile = static_cast<int>(item % p.n_dtiles);
-                const int64_t row = item / p.n_dtiles;
-                const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
-                for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
-                    const int s = it % kBwdStages;
-                    const uint32_t ph = (it / kBwdStages) & 1;
-                    if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 11)) break;
-                    mbar_expect_tx(bar(B_FULL + s), 2 * kTileBytes);
-                    const uint32_t dst = sbase + BwdSmem::xg + s * 2 * kTileBytes;
-                    const int c0 = dtile * DT;
-                    tma_load_4d(dst, &tm_x, bar(B_FULL + s), c0, hi, k * QT, bi);
-                    tma_load_4d(dst + kBlockBytes, &tm_x, bar(B_FULL + s), c0 + kBlockCols, hi, k * QT, bi);
-                    tma_load_4d(dst + kTileBytes, &tm_g, bar(B_FULL + s), c0, hi, k * QT, bi);
-                    tma_load_4d(dst + kTileBytes + kBlockBytes, &tm_g, bar(B_FULL + s), c0 + kBlockCols, hi, k * QT, bi);
+    if (warp < 4) {
+        reg_dec<kRegsLight>();
+        if (warp == 0) {
+            // ---------------- TMA producer ----------------
+            if (lane == 0) {
+                uint32_t it = 0;
+                for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
+                    const int dtile = static_cast<int>(item % p.n_dtiles);
+                    const int64_t row = item / p.n_dtiles;
+                    const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
+                    for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
+                        const int s = it % kBwdStages;
+                        const uint32_t ph = (it / kBwdStages) & 1;
+                        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 11)) break;
+                        mbar_expect_tx(bar(B_FULL + s), 2 * kTileBytes);
+                        const uint32_t dst = sbase + BwdSmem::xg + s * 2 * kTileBytes;
+                        const int c0 = dtile * DT;
+                        tma_load_4d(dst, &tm_x, bar(B_FULL + s), c0, hi, k * QT, bi);
+                        tma_load_4d(dst + kBlockBytes, &tm_x, bar(B_FULL + s), c0 + kBlockCols, hi, k * QT, bi);
+                        tma_load_4d(dst + kTileBytes, &tm_g, bar(B_FULL + s), c0, hi, k * QT, bi);
+                        tma_load_4d(dst + kTileBytes + kBlockBytes, &tm_g, bar(B_FULL + s), c0 + kBlockCols, hi, k * QT, bi);
+                    }
                 }
             }
-        }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
-        if (lane == 0) {
-            uint32_t it = 0, mt = 0;
-            int cur_head = -1;
-            // K block 0 / 1 of each matrix (see BwdSmem): descriptor bases
-            const uint64_t a1d[2] = {make_desc_sw128(sbase + BwdSmem::m_a1k0, 16, 1024),
-                                     make_desc_sw128(sbase + BwdSmem::m_z, 16, 1024)};
-            const uint64_t ud[2] = {make_desc_sw128(sbase + BwdSmem::m_u00, 16, 1024),
-                                    make_desc_sw128(sbase + BwdSmem::m_uk1, 16, 1024)};
-            for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                const int hi = static_cast<int>((item / p.n_dtiles) % p.h);
-                for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
-                    const int s = it % kBwdStages;
-                    const uint32_t ph = (it / kBwdStages) & 1;
-                    const int acc = it & 1;
-                    const uint32_t aph = (it >> 1) & 1;
-                    if (per_step || hi != cur_head) {
-                        // single matrix buffer: hand it back to the builders once the MMAs issued so far are done
-                        if (!per_step && mt > 0) umma_commit(bar(B_MAT_EMPTY));
-                        if (!mbar_wait(bar(B_MAT_FULL), mt & 1, abort_flag, 12)) break;
-                        cur_head = hi;
-                        ++mt;
+        } else if (warp == 1) {
+            // ---------------- MMA issuer ----------------
+            if (lane == 0) {
+                uint32_t it = 0, mt = 0;
+                int cur_head = -1;
+                // K block 0 / 1 of each matrix (see BwdSmem): descriptor bases
+                const uint64_t a1d[2] = {make_desc_sw128(sbase + BwdSmem::m_a1k0, 16, 1024),
+                                         make_desc_sw128(sbase + BwdSmem::m_z, 16, 1024)};
+                const uint64_t ud[2] = {make_desc_sw128(sbase + BwdSmem::m_u00, 16, 1024),
+                                        make_desc_sw128(sbase + BwdSmem::m_uk1, 16, 1024)};
+                for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
+                    const int hi = static_cast<int>((item / p.n_dtiles) % p.h);
+                    for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
+                        const int s = it % kBwdStages;
+                        const uint32_t ph = (it / kBwdStages) & 1;
+                        const int acc = it & 1;
+                        const uint32_t aph = (it >> 1) & 1;
+                        if (per_step || hi != cur_head) {
+                            // single matrix buffer: hand it back to the builders once the MMAs issued so far are done
+                            if (!per_step && mt > 0) umma_commit(bar(B_MAT_EMPTY));
+                            if (!mbar_wait(bar(B_MAT_FULL), mt & 1, abort_flag, 12)) break;
+                            cur_head = hi;
+                            ++mt;
+                        }
+                        if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 13)) break;
+                        if (!mbar_wait(bar(B_ACC_EMPTY + acc), aph ^ 1, abort_flag, 14)) break;
+                        tc_fence_after_sync();
+                        const uint64_t xd0 = tile_desc(sbase + BwdSmem::xg + s * 2 * kTileBytes);
+                        const uint64_t gd0 = xd0 + (kTileBytes >> 4);
+                        const uint32_t d_z = tmem_base + acc * 2 * DT, d_l = d_z + DT;
+    #pragma unroll
+                        for (int kb = 0; kb < QT / 16; ++kb)
+                            umma_bf16(d_z, a1d[kb >> 2] + (((kb & 3) * 32) >> 4), xd0 + ((kb * 2048) >> 4), kIdesc, kb > 0 ? 1u : 0u);
+    #pragma unroll
+                        for (int kb = 0; kb < QT / 16; ++kb)
+                            umma_bf16(d_l, ud[kb >> 2] + (((kb & 3) * 32) >> 4), gd0 + ((kb * 2048) >> 4), kIdesc, kb > 0 ? 1u : 0u);
+                        umma_commit(bar(B_EMPTY + s));   // the stage is free as soon as the MMAs have read it
+                        umma_commit(bar(B_ACC_FULL + acc));
+                        if (per_step) umma_commit(bar(B_MAT_EMPTY));
                     }
-                    if (!mbar_wait(bar(B_FULL + s), ph, abort_flag, 13)) break;
-                    if (!mbar_wait(bar(B_ACC_EMPTY + acc), aph ^ 1, abort_flag, 14)) break;
-                    tc_fence_after_sync();
-                    const uint64_t xd0 = tile_desc(sbase + BwdSmem::xg + s * 2 * kTileBytes);
-                    const uint64_t gd0 = xd0 + (kTileBytes >> 4);
-                    const uint32_t d_z = tmem_base + acc * 2 * DT, d_l = d_z + DT;
-#pragma unroll
-                    for (int kb = 0; kb < QT / 16; ++kb)
-                        umma_bf16(d_z, a1d[kb >> 2] + (((kb & 3) * 32) >> 4), xd0 + ((kb * 2048) >> 4), kIdesc, kb > 0 ? 1u : 0u);
-#pragma unroll
-                    for (int kb = 0; kb < QT / 16; ++kb)
-                        umma_bf16(d_l, ud[kb >> 2] + (((kb & 3) * 32) >> 4), gd0 + ((kb * 2048) >> 4), kIdesc, kb > 0 ? 1u : 0u);
-                    umma_commit(bar(B_EMPTY + s));   // the stage is free as soon as the MMAs have read it
-                    umma_commit(bar(B_ACC_FULL + acc));
-                    if (per_step) umma_commit(bar(B_MAT_EMPTY));
                 }
+            }
+        } else {
+            // ---------------- TMA store issuer ----------------
+            if (tid == kStoreThread) {
+                uint32_t it = 0;
+                for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
+                    const int dtile = static_cast<int>(item % p.n_dtiles);
+                    const int64_t row = item / p.n_dtiles;
+                    const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
+                    const bool two = dtile * DT + kBlockCols < p.d;   // the second 64-channel block exists
+                    for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
+                        const uint32_t src = sbase + BwdSmem::ostage;
+                        if (!mbar_wait(bar(B_STG_FULL + 0), it & 1, abort_flag, 19)) break;
+                        tma_store_4d(&tm_o, src, dtile * DT, hi, k * QT, bi);
+                        tma_store_commit();
+                        if (!mbar_wait(bar(B_STG_FULL + 1), it & 1, abort_flag, 20)) break;
+                        if (two) tma_store_4d(&tm_o, src + kBlockBytes, dtile * DT + kBlockCols, hi, k * QT, bi);
+                        tma_store_commit();
+                        tma_store_wait_read<1>();          // block 0 has been read: hand it back to its four warps
+                        mbar_arrive(bar(B_STG_EMPTY + 0));
+                        tma_store_wait_read<0>();
+                        mbar_arrive(bar(B_STG_EMPTY + 1));
+                    }
+                }
+                tma_store_wait_all();
             }
         }
     } else if (tid < kBuildThread0) {
+        reg_inc<kRegsEpilogue>();
         // ---------------- epilogue ----------------
         // thread (q, lane, half): row m = 32 q + lane, channels [64 half, 64 half + 64) of the tile, 32 at a time.
         // The two threads of row 0 are the serial carry chain (the adjoint handed to the tile on the left).
@@ -866,46 +951,58 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 if (lane == 0) mbar_arrive(bar(B_STG_FULL + half));
             }
         }
-    } else if (tid < kStoreThread) {
+    } else {
+        reg_dec<kRegsBuilder>();
         // ---------------- matrix builders ----------------
-        const int r = tid - kBuildThread0;
+        const int bt = tid - kBuildThread0;   // 0-255; threads 0-127 also own row r = bt of the per-row tables
+        const int r = bt & 127;
+        const bool row_owner = bt < 128;
         uint32_t mt = 0;
         int cur_head = -1;
         const float diag = conv ? 0.f : -1.f;
-        // v: raw decay value of step r of the tile; v_edge: of the step right after the tile (identity past L)
+        OffGeom oga, ogu;
+        DiagGeom dga, dgu;
+        // A1: K block 0 holds every row; K block 1 only rows 64-127 (stored from row 64 on)
+        make_geom<false, 1>(bt, oga, dga, [](int m, int c) {
+            return c < 8 ? BwdSmem::m_a1k0 + sw128_offset(m, c) : BwdSmem::m_a111 + sw128_offset(m - 64, c - 8);
+        });
+        // U: K block 0 only rows 0-63; K block 1 every row
+        make_geom<true, 0>(bt, ogu, dgu, [](int m, int c) {
+            return c < 8 ? BwdSmem::m_u00 + sw128_offset(m, c) : BwdSmem::m_uk1 + sw128_offset(m, c - 8);
+        });
+        const uint8_t *cs_b = smem + BwdSmem::cs, *p_b = smem + BwdSmem::pw, *wlo_b = smem + BwdSmem::wlo,
+                      *rup_b = smem + BwdSmem::rup;
+        // v: raw decay value of step r of the tile; v_edge: of the step right after the tile (identity past L);
+        // both are read from the row owners only
         auto build = [&](float v, float v_edge) {
             const float l2 = log2_decay(v);
-            float to_end, from_start;
-            builder_scan(l2, r, cs_sm, wt_sm, to_end, from_start);
-            const float pw = conv ? 1.f : 1.f - v;
-            p_sm[r] = pw;
-            wlo_sm[r] = pw * ex2_approx(to_end);
-            rup_sm[r] = ex2_approx(from_start);
-            bar_sync(2, 128);
+            float to_end = 0.f, from_start = 0.f;
+            builder_scan(l2, bt, cs_sm, wt_sm, to_end, from_start);
+            if (row_owner) {
+                const float pw = conv ? 1.f : 1.f - v;
+                p_sm[r] = pw;
+                wlo_sm[r] = pw * ex2_approx(to_end);
+                rup_sm[r] = ex2_approx(from_start);
+            }
+            bar_sync(2, kBuildThreads);
             RowChunks ca, cu;
-            compute_lower<1>(r, cs_sm, p_sm, wlo_sm, diag, ca);
-            compute_upper(r, cs_sm, rup_sm, cu);
+            compute_diag_lower<1>(dga, cs_b, p_b, diag, ca);
+            compute_off<false>(oga, cs_b, wlo_b, ca);
+            compute_diag_upper(dgu, cs_b, cu);
+            compute_off<true>(ogu, cs_b, rup_b, cu);
             const float cs_r = cs_sm[r];
-            const float Eprev = exp2f(cs_r - l2);                       // prod_{j<r} a_j
-            const float Fr = exp2f(cs_sm[QT - 1] - cs_r + log2_decay(v_edge));
+            const float Eprev = ex2_approx(cs_r - l2);                       // prod_{j<r} a_j
+            const float Fr = ex2_approx(cs_sm[QT - 1] - cs_r + log2_decay(v_edge));
             if (lane == 0) mbar_wait(bar(B_MAT_EMPTY), (mt & 1) ^ 1, abort_flag, 18);
             __syncwarp();
-            // A1: K block 0 holds every row; K block 1 only rows 64-127 (stored from row 64 on)
-            for_my_chunks<false>(r, [&](int n, int m, int c) {
-                uint8_t *dst = c < 8 ? smem + BwdSmem::m_a1k0 + sw128_offset(m, c)
-                                     : smem + BwdSmem::m_a111 + sw128_offset(m - 64, c - 8);
-                *reinterpret_cast<uint4 *>(dst) = ca.v[n];
-            });
-            // U: K block 0 only rows 0-63; K block 1 every row
-            for_my_chunks<true>(r, [&](int n, int m, int c) {
-                uint8_t *dst = c < 8 ? smem + BwdSmem::m_u00 + sw128_offset(m, c)
-                                     : smem + BwdSmem::m_uk1 + sw128_offset(m, c - 8);
-                *reinterpret_cast<uint4 *>(dst) = cu.v[n];
-            });
-            float *rs = rowsc + (mt % kRowRing) * 3 * QT;
-            rs[r] = Eprev;
-            rs[QT + r] = Fr;
-            rs[2 * QT + r] = conv ? exp2f(l2) : v;
+            store_matrix(oga, dga, smem, ca);
+            store_matrix(ogu, dgu, smem, cu);
+            if (row_owner) {
+                float *rs = rowsc + (mt % kRowRing) * 3 * QT;
+                rs[r] = Eprev;
+                rs[QT + r] = Fr;
+                rs[2 * QT + r] = conv ? ex2_approx(l2) : v;
+            }
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_MAT_FULL));
@@ -923,7 +1020,9 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 }
                 continue;
             }
-            auto load_v = [&](int t) { return (t >= 0 && t < L) ? arow[static_cast<int64_t>(t) * p.a_sl] : ident; };
+            auto load_v = [&](int t) {
+                return (row_owner && t >= 0 && t < L) ? arow[static_cast<int64_t>(t) * p.a_sl] : ident;
+            };
             float v_next = load_v((p.n_tiles - 1) * QT + r);
             float edge_next = ident;  // step n_tiles*128 is past the end
             for (int k = p.n_tiles - 1; k >= 0; --k) {
@@ -934,31 +1033,6 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 }
                 build(v, edge);
             }
-        }
-    } else {
-        // ---------------- TMA store issuer ----------------
-        if (tid == kStoreThread) {
-            uint32_t it = 0;
-            for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                const int dtile = static_cast<int>(item % p.n_dtiles);
-                const int64_t row = item / p.n_dtiles;
-                const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
-                const bool two = dtile * DT + kBlockCols < p.d;   // the second 64-channel block exists
-                for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
-                    const uint32_t src = sbase + BwdSmem::ostage;
-                    if (!mbar_wait(bar(B_STG_FULL + 0), it & 1, abort_flag, 19)) break;
-                    tma_store_4d(&tm_o, src, dtile * DT, hi, k * QT, bi);
-                    tma_store_commit();
-                    if (!mbar_wait(bar(B_STG_FULL + 1), it & 1, abort_flag, 20)) break;
-                    if (two) tma_store_4d(&tm_o, src + kBlockBytes, dtile * DT + kBlockCols, hi, k * QT, bi);
-                    tma_store_commit();
-                    tma_store_wait_read<1>();          // block 0 has been read: hand it back to its four warps
-                    mbar_arrive(bar(B_STG_EMPTY + 0));
-                    tma_store_wait_read<0>();
-                    mbar_arrive(bar(B_STG_EMPTY + 1));
-                }
-            }
-            tma_store_wait_all();
         }
     }
 

@@ -8,9 +8,12 @@ library or a CUDA device is missing.
     y = ema(x, a)              # x[b,L,h,d], a[b,L,h] or a[h];  y_t = a_t y_{t-1} + (1-a_t) x_t
     y.backward(dy)             # dx, da
 
+Host-resident tensors: `HostPipeline` / `ema_fwd_bwd_host` (host.py) stream batch slices through the GPU.
+
 The reference project's own entry points (same names, same signatures) live in the sibling
 package `kernels`.
 """
 from ._lib import EmaB200Error, lib, lib_path  # noqa: F401
 from .ops import (ema, ema_fwd, ema_bwd, ema_scan_folded_fwd, ema_scan_folded_bwd,  # noqa: F401
                   EmaFunction)
+from .host import HostPipeline, ema_fwd_bwd_host  # noqa: F401

@@ -1,0 +1,127 @@
+"""EMA forward + backward for tensors that live in host memory.
+
+The scan rows of different batch entries are independent, so a host-resident problem is cut into batch
+slices that flow through three CUDA streams: host-to-device copies of x and dy, the fused forward and
+backward kernels, device-to-host copies of y and dx.  PCIe carries both directions at once, so a step
+costs about max(bytes in, bytes out) / link bandwidth instead of their sum, and the kernels hide behind
+the copies.  Device memory holds `depth` slices of each tensor, whatever the batch size.
+
+    pipe = HostPipeline(x_host.shape, x_host.dtype, per_head=True, device="cuda:0")
+    pipe.run(x_host, a_host, dy_host, y_host, dx_host, da_host)      # host tensors, ideally pinned
+
+`run` orders everything after the caller's current stream and, unless told otherwise, returns once the last
+copy has landed in the output tensors.
+"""
+import ctypes
+
+import torch
+
+from . import ops
+from ._lib import lib
+
+
+class HostPipeline:
+    def __init__(self, shape, dtype, per_head, device="cuda", slices=8, depth=3, prescaled_log=False):
+        b, L, h, d = shape
+        if b < 1:
+            raise ValueError("batch must not be empty")
+        self.shape, self.dtype, self.per_head = (b, L, h, d), dtype, per_head
+        self.prescaled_log = prescaled_log
+        self.device = torch.device(device)
+        slices = max(1, min(slices, b))
+        self.bounds = [(i * b) // slices for i in range(slices + 1)]        # batch rows of slice i: bounds[i]:bounds[i+1]
+        bs = max(self.bounds[i + 1] - self.bounds[i] for i in range(slices))
+        self.depth = depth = max(1, min(depth, slices))
+        dev = self.device
+        mk = lambda: [torch.empty((bs, L, h, d), dtype=dtype, device=dev) for _ in range(depth)]
+        self.x, self.dy, self.y, self.dx = mk(), mk(), mk(), mk()
+        probe_a = torch.empty((h,) if per_head else (bs, L, h), dtype=torch.float32, device=dev)
+        _, nt = ops.n_tiles_of(self.x[0], probe_a)
+        self.tile_states = [torch.empty((bs * h, nt, d), dtype=torch.float32, device=dev) for _ in range(depth)]
+        # the backward's workspace, sized for the largest slice
+        prob = ops._problem(self.x[0], probe_a, self.dx[0], dy=self.dy[0],
+                            convention=ops.CONV_PRESCALED_LOG if prescaled_log else ops.CONV_NORTH_STAR)
+        ws_floats = (lib().ema_b200_bwd_workspace_bytes(ctypes.byref(prob)) + 3) // 4
+        self.workspace = [torch.empty((ws_floats,), dtype=torch.float32, device=dev) for _ in range(depth)]
+        self.a = torch.empty((h,) if per_head else (b, L, h), dtype=torch.float32, device=dev)
+        # per-head decay: one partial gradient per slice, summed in slice order at the end (deterministic)
+        self.da = torch.empty((slices, h) if per_head else (b, L, h), dtype=torch.float32, device=dev)
+        self.da_sum = torch.empty((h,), dtype=torch.float32, device=dev) if per_head else None
+        self.s_in, self.s_comp, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
+        ev = lambda: [torch.cuda.Event() for _ in range(depth)]
+        self.ev_in, self.ev_comp, self.ev_out = ev(), ev(), ev()
+        self.n_launches = 0   # library kernel launches of the last run
+
+    def run(self, x, a, dy, y, dx, da, sync=True):
+        """x, dy -> y, dx (host tensors shaped like the problem); a -> da (host, fp32).
+
+        With sync=False the call only queues the work; the caller's current stream waits for it, and the outputs
+        are valid once that stream has been synchronised."""
+        b, L, h, d = self.shape
+        for t in (x, dy, y, dx):
+            if tuple(t.shape) != (b, L, h, d) or t.dtype != self.dtype or t.is_cuda:
+                raise ValueError("x, dy, y, dx must be host tensors of the pipeline's shape and dtype")
+        if tuple(a.shape) != tuple(self.a.shape) or tuple(da.shape) != tuple(self.a.shape):
+            raise ValueError("a and da must have the decay's shape")
+        n = len(self.bounds) - 1
+        cur = torch.cuda.current_stream(self.device)
+        start = torch.cuda.Event()
+        start.record(cur)
+        for s in (self.s_in, self.s_comp, self.s_out):
+            s.wait_event(start)
+        with torch.cuda.stream(self.s_in):
+            self.a.copy_(a, non_blocking=True)
+            ev_a = torch.cuda.Event()
+            ev_a.record(self.s_in)
+        self.s_comp.wait_event(ev_a)
+        launches = 0
+        for i in range(n):
+            lo, hi = self.bounds[i], self.bounds[i + 1]
+            k, slot = hi - lo, i % self.depth
+            xs, dys, ys, dxs = self.x[slot][:k], self.dy[slot][:k], self.y[slot][:k], self.dx[slot][:k]
+            with torch.cuda.stream(self.s_in):
+                if i >= self.depth:
+                    self.s_in.wait_event(self.ev_comp[slot])     # the kernels of slice i - depth have read x, dy
+                xs.copy_(x[lo:hi], non_blocking=True)
+                dys.copy_(dy[lo:hi], non_blocking=True)
+                self.ev_in[slot].record(self.s_in)
+            with torch.cuda.stream(self.s_comp):
+                self.s_comp.wait_event(self.ev_in[slot])
+                if i >= self.depth:
+                    self.s_comp.wait_event(self.ev_out[slot])    # y, dx of slice i - depth have left
+                a_i = self.a if self.per_head else self.a[lo:hi]
+                da_i = self.da[i] if self.per_head else self.da[lo:hi]
+                ts = self.tile_states[slot][: k * h]
+                ops.ema_fwd(xs, a_i, out=ys, tile_states=ts, prescaled_log=self.prescaled_log)
+                ops.ema_bwd(xs, a_i, dys, ts, dx=dxs, ddecay=da_i, workspace=self.workspace[slot],
+                            prescaled_log=self.prescaled_log)
+                launches += 4 if self.per_head else 3
+                self.ev_comp[slot].record(self.s_comp)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(self.ev_comp[slot])
+                y[lo:hi].copy_(ys, non_blocking=True)
+                dx[lo:hi].copy_(dxs, non_blocking=True)
+                self.ev_out[slot].record(self.s_out)
+        with torch.cuda.stream(self.s_comp):
+            if self.per_head:
+                torch.sum(self.da, dim=0, out=self.da_sum)
+                da.copy_(self.da_sum, non_blocking=True)
+            else:
+                da.copy_(self.da, non_blocking=True)
+        for s in (self.s_comp, self.s_out):
+            cur.wait_stream(s)
+        self.n_launches = launches
+        if sync:
+            cur.synchronize()
+        return y, dx, da
+
+
+def ema_fwd_bwd_host(x, a, dy, y=None, dx=None, da=None, device="cuda", slices=8, depth=3, prescaled_log=False):
+    """One-shot form: builds a pipeline for this problem, runs it, synchronises, returns (y, dx, da) on the host."""
+    pin = torch.cuda.is_available()
+    y = torch.empty_like(x, pin_memory=pin) if y is None else y
+    dx = torch.empty_like(x, pin_memory=pin) if dx is None else dx
+    da = torch.empty_like(a, pin_memory=pin) if da is None else da
+    pipe = HostPipeline(tuple(x.shape), x.dtype, per_head=a.dim() == 1, device=device, slices=slices, depth=depth,
+                        prescaled_log=prescaled_log)
+    return pipe.run(x, a, dy, y, dx, da)
