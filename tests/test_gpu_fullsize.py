@@ -1,0 +1,105 @@
+"""Parity at the full sizes of the benchmark configurations.
+
+The sequential oracle cannot run a whole 2-billion-element problem in seconds, but the scan rows (b, h) are
+independent: a few full-length rows, all channels, are checked against the oracle, and the rest of the tensor
+through properties that do not depend on the size:
+  * the decay gradient of a time-invariant decay equals the sum over (b, t) of the per-step gradient of the
+    same decay broadcast to [b, L, h] (two different kernel paths, one reduction each);
+  * every output is finite and no bounded device-side wait ran out.
+Synthetic inputs: x, dy ~ N(0,1) in bf16, a = sigmoid(U(lo, hi)), fixed seeds.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import BF16_REL
+from oracle import ema_oracle as eo
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(seed, b, L, h, d, per_head, lo, hi):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn((b, L, h, d), generator=g, device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn((b, L, h, d), generator=g, device="cuda", dtype=torch.bfloat16)
+    shape = (h,) if per_head else (b, L, h)
+    a = torch.sigmoid(lo + (hi - lo) * torch.rand(shape, generator=g, device="cuda", dtype=torch.float32))
+    return x, a, dy
+
+
+def _check_rows(rows, x, a, dy, y, dx, da_steps):
+    """rows: list of (bi, hi).  da_steps: per-step decay gradient [b, L, h] or None."""
+    for bi, hi in rows:
+        xs = x[bi, :, hi].float().cpu().numpy()[None, :, None, :]
+        dys = dy[bi, :, hi].float().cpu().numpy()[None, :, None, :]
+        L = xs.shape[1]
+        a_row = (a[hi].expand(L) if a.dim() == 1 else a[bi, :, hi]).float().cpu().numpy().reshape(1, L, 1).copy()
+        y_ref = eo.fwd(xs, a_row, acc64=True)
+        dx_ref, da_ref = eo.bwd(xs, a_row, dys, acc64=True)
+        for got, ref, what in ((y[bi, :, hi], y_ref, "y"), (dx[bi, :, hi], dx_ref, "dx")):
+            g = got.float().cpu().numpy()
+            err = np.abs(g - ref[0, :, 0, :]).max() / np.abs(ref).max()
+            assert err <= BF16_REL, f"{what} row {(bi, hi)}: normalised max err {err:.3e}"
+        if da_steps is not None:
+            g = da_steps[bi, :, hi].float().cpu().numpy()
+            err = np.abs(g - da_ref[0, :, 0]).max() / np.abs(da_ref).max()
+            assert err <= BF16_REL, f"da row {(bi, hi)}: normalised max err {err:.3e}"
+
+
+def _run(x, a, dy):
+    from ema_b200 import ops
+    fwd = ops.ema_fwd(x, a, want_tile_states=True)
+    bwd = ops.ema_bwd(x, a, dy, fwd["tile_states"])
+    torch.cuda.synchronize()
+    return fwd["y"], bwd["dx"], bwd["ddecay"]
+
+
+def test_headline_config_time_invariant_decay(ema_lib):
+    # x, dy bf16 [16, 8192, 2, 1024], a fp32 [2], forward + backward
+    b, L, h, d = 16, 8192, 2, 1024
+    x, a, dy = _inputs(1236, b, L, h, d, True, 2.0, 6.0)
+    y, dx, da = _run(x, a, dy)
+    assert ema_lib.ema_b200_last_path() == 1
+    # the same decay as a per-step tensor: per-step gradients, checked row-wise, whose sum must give da[h]
+    a_steps = a.view(1, 1, h).expand(b, L, h).contiguous()
+    y2, dx2, da_steps = _run(x, a_steps, dy)
+    assert torch.equal(y, y2) or (y.float() - y2.float()).abs().max() <= BF16_REL * y.float().abs().max()
+    total = da_steps.double().sum(dim=(0, 1)).cpu().numpy()
+    got = da.double().cpu().numpy()
+    assert np.abs(got - total).max() <= BF16_REL * np.abs(total).max(), (got, total)
+    _check_rows([(0, 0), (7, 1), (15, 1)], x, a, dy, y, dx, da_steps)
+    for t in (y, dx, da):
+        assert bool(torch.isfinite(t).all())
+    assert ema_lib.ema_b200_device_status(0) == 0
+
+
+def test_time_varying_decay_config(ema_lib):
+    # x bf16 [16, 8192, 2, 1024], a fp32 [16, 8192, 2]: the forward-only configuration, backward checked too
+    b, L, h, d = 16, 8192, 2, 1024
+    x, a, dy = _inputs(1235, b, L, h, d, False, 2.0, 6.0)
+    y, dx, da = _run(x, a, dy)
+    assert ema_lib.ema_b200_last_path() == 1
+    _check_rows([(0, 1), (9, 0), (15, 1)], x, a, dy, y, dx, da)
+    for t in (y, dx, da):
+        assert bool(torch.isfinite(t).all())
+    assert ema_lib.ema_b200_device_status(0) == 0
+
+
+def test_long_sequence_config(ema_lib):
+    # x, dy bf16 [4, 65536, 8, 1024] (4 GiB each), a fp32 [4, 65536, 8] = sigmoid(U(3, 8))
+    b, L, h, d = 4, 65536, 8, 1024
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 * 2**30:
+        pytest.skip("needs about 25 GiB of device memory")
+    x, a, dy = _inputs(1237, b, L, h, d, False, 3.0, 8.0)
+    y, dx, da = _run(x, a, dy)
+    assert ema_lib.ema_b200_last_path() == 1
+    _check_rows([(0, 0), (3, 7)], x, a, dy, y, dx, da)
+    # finite everywhere, checked slice by slice to keep temporaries small
+    for t in (y, dx):
+        for bi in range(b):
+            assert bool(torch.isfinite(t[bi]).all())
+    assert bool(torch.isfinite(da).all())
+    assert ema_lib.ema_b200_device_status(0) == 0
+    del x, dy, y, dx
+    torch.cuda.empty_cache()
