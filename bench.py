@@ -3,6 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W]            # this library
     python bench.py --impl reference [--steps K] [--warmup W]      # the reference's CPU path
+    python bench.py --workload c2|c4 [--no-e2e]                    # the other single-GPU configurations
 
 One "step" is one forward (y, saved tile states) plus one backward (dx, da) over one batch of
 synthetic input with the shapes of the headline workload: x, dy bf16 [16, 8192, 2, 1024] ~ N(0,1),
@@ -26,8 +27,16 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "triton-kernels_b200"))
 sys.path.insert(0, ROOT)
 
-WORKLOAD = dict(name="ema_fwd_bwd_b16_L8192_h2_d1024_bf16_perhead_decay_chunk256",
-                b=16, L=8192, h=2, d=1024, chunk=256)
+# The headline workload (default) and the other single-GPU configurations of the benchmark suite.
+WORKLOADS = {
+    "c3": dict(name="ema_fwd_bwd_b16_L8192_h2_d1024_bf16_perhead_decay_chunk256",
+               b=16, L=8192, h=2, d=1024, chunk=256, per_head=True, fwd_only=False, lo=2.0, hi=6.0),
+    "c2": dict(name="ema_fwd_b16_L8192_h2_d1024_bf16_perstep_decay_chunk128",
+               b=16, L=8192, h=2, d=1024, chunk=128, per_head=False, fwd_only=True, lo=2.0, hi=6.0),
+    "c4": dict(name="ema_fwd_bwd_b4_L65536_h8_d1024_bf16_perstep_decay_chunk512",
+               b=4, L=65536, h=8, d=1024, chunk=512, per_head=False, fwd_only=False, lo=3.0, hi=8.0),
+}
+WORKLOAD = WORKLOADS["c3"]
 METRIC = "ema_fwd_bwd_tokens_per_s"
 UNIT = "tokens/s"
 
@@ -93,10 +102,11 @@ class ClockSampler:
                 "window": "about 1.2 s of identical back-to-back steps ending with the timed steps"}
 
 
-def algorithmic_bytes(b, L, h, d, s=2):
+def algorithmic_bytes(b, L, h, d, s=2, per_head=True):
     n = b * L * h * d
-    fwd = n * 2 * s + 4 * h                   # x read, y written, a[h] read
-    bwd = n * 3 * s + 4 * h + 4 * h           # x, dy read, dx written, a read, da written
+    na = 4 * h if per_head else 4 * b * L * h
+    fwd = n * 2 * s + na                      # x read, y written, decay read
+    bwd = n * 3 * s + na + na                 # x, dy read, dx written, decay read, its gradient written
     return fwd, bwd
 
 
@@ -163,12 +173,15 @@ def run_gpu(args):
     import ema_b200
     from ema_b200 import ops
 
-    W = WORKLOAD
+    W = WORKLOADS[args.workload]
     b, L, h, d = W["b"], W["L"], W["h"], W["d"]
+    per_head, fwd_only = W["per_head"], W["fwd_only"]
     g = torch.Generator(device=dev).manual_seed(1236 + rank)
     x = torch.randn((b, L, h, d), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
     dy = torch.randn((b, L, h, d), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
-    a = torch.sigmoid(2 + 4 * torch.rand((h,), generator=torch.Generator(device=dev).manual_seed(99), device=dev))
+    a_shape = (h,) if per_head else (b, L, h)
+    a = torch.sigmoid(W["lo"] + (W["hi"] - W["lo"]) *
+                      torch.rand(a_shape, generator=torch.Generator(device=dev).manual_seed(99), device=dev))
     y = torch.empty_like(x)
     dx = torch.empty_like(x)
     # Two buffers for the per-head decay gradient: with N > 1 its all-reduce (the only collective of the
@@ -185,7 +198,7 @@ def run_gpu(args):
         nonlocal n_steps_done
         slot = n_steps_done % 2
         n_steps_done += 1
-        if world > 1:
+        if world > 1 and per_head:
             pending[slot] = dist.all_reduce(da_bufs[slot], async_op=True)
 
     def da_slot():
@@ -204,6 +217,8 @@ def run_gpu(args):
     def step():
         nonlocal ws
         ops.ema_fwd(x, a, out=y, tile_states=tile_states)
+        if fwd_only:
+            return
         r = ops.ema_bwd(x, a, dy, tile_states, dx=dx, ddecay=da_slot(), workspace=ws)
         ws = r["workspace"]
         reduce_da()
@@ -245,9 +260,11 @@ def run_gpu(args):
         ev[i][0].record()
         ops.ema_fwd(x, a, out=y, tile_states=tile_states)
         ev[i][1].record()
-        ops.ema_bwd(x, a, dy, tile_states, dx=dx, ddecay=da_slot(), workspace=ws)
+        if not fwd_only:
+            ops.ema_bwd(x, a, dy, tile_states, dx=dx, ddecay=da_slot(), workspace=ws)
         ev[i][2].record()
-        reduce_da()
+        if not fwd_only:
+            reduce_da()
     drain()   # the last reduces finish inside the timed region
     stop.record()
     torch.cuda.synchronize()
@@ -272,12 +289,14 @@ def run_gpu(args):
     try:
         if args.no_e2e:
             raise RuntimeError("skipped (--no-e2e)")
+        if fwd_only:
+            raise RuntimeError("skipped: the host pipeline runs forward + backward, this workload is forward only")
         hx, hdy = x.cpu().pin_memory(), dy.cpu().pin_memory()
         ha = a.cpu().pin_memory()
         hy, hdx = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
         hda = torch.empty_like(ha).pin_memory()
         # the library's host-buffer entry: batch slices stream through H2D copy, kernels and D2H copy concurrently
-        pipe = ema_b200.HostPipeline((b, L, h, d), torch.bfloat16, per_head=True, device=dev, slices=8, depth=3)
+        pipe = ema_b200.HostPipeline((b, L, h, d), torch.bfloat16, per_head=per_head, device=dev, slices=8, depth=3)
 
         def e2e_step():
             pipe.run(hx, ha, hdy, hy, hdx, hda, sync=False)
@@ -302,7 +321,7 @@ def run_gpu(args):
             e2e_ms = float(t.item())
         nbytes = x.numel() * 2
         e2e = {"value": tokens / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": 2 * nbytes + 4 * h, "d2h_bytes_per_step": 2 * nbytes + 4 * h,
+               "h2d_bytes_per_step": 2 * nbytes + 4 * a.numel(), "d2h_bytes_per_step": 2 * nbytes + 4 * a.numel(),
                "api": "ema_b200.HostPipeline.run: pinned host x, dy, a -> y, dx, da; 8 batch slices, "
                       "H2D / kernels / D2H on three streams",
                "gpu_launches_per_step": pipe.n_launches}
@@ -316,26 +335,33 @@ def run_gpu(args):
         return
 
     peak, peak_kind = measured_peaks()
-    fwd_b, bwd_b = algorithmic_bytes(b, L, h, d)
-    bwd_gbs = bwd_b / (bwd_ms * 1e-3) / 1e9
+    fwd_b, bwd_b = algorithmic_bytes(b, L, h, d, per_head=per_head)
     fwd_gbs = fwd_b / (fwd_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "ema_bwd (reverse scan: reads x, dy, writes dx; plus its small da reduction)",
-                "achieved": bwd_gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                "frac": bwd_gbs / peak, "traffic": None,
-                "algorithmic_bytes_per_launch": bwd_b, "ms_per_launch": bwd_ms,
-                "fwd": {"achieved": fwd_gbs, "frac": fwd_gbs / peak, "algorithmic_bytes_per_launch": fwd_b,
-                        "ms_per_launch": fwd_ms},
-                "step": {"achieved": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9,
-                         "frac": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9 / peak}}
+    fwd_obj = {"achieved": fwd_gbs, "frac": fwd_gbs / peak, "algorithmic_bytes_per_launch": fwd_b,
+               "ms_per_launch": fwd_ms}
+    if fwd_only:
+        roofline = {"bound": "hbm", "kernel": "ema_fwd (scan: reads x, writes y and the saved tile states)",
+                    "achieved": fwd_gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": fwd_gbs / peak,
+                    "traffic": None, "algorithmic_bytes_per_launch": fwd_b, "ms_per_launch": fwd_ms}
+    else:
+        bwd_gbs = bwd_b / (bwd_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm",
+                    "kernel": "ema_bwd (reverse scan: reads x, dy, writes dx; plus its small da reduction)",
+                    "achieved": bwd_gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                    "frac": bwd_gbs / peak, "traffic": None,
+                    "algorithmic_bytes_per_launch": bwd_b, "ms_per_launch": bwd_ms, "fwd": fwd_obj,
+                    "step": {"achieved": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9,
+                             "frac": (fwd_b + bwd_b) / (ms_per_step * 1e-3) / 1e9 / peak}}
     traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(traffic_file):   # dram__bytes_read.sum + dram__bytes_write.sum from the committed ncu capture
+    if args.workload == "c3" and os.path.exists(traffic_file):
+        # dram__bytes_read.sum + dram__bytes_write.sum from the committed ncu capture of this workload
         with open(traffic_file) as f:
             tr = json.load(f)
         roofline["traffic"] = tr.get("ema_bwd_bytes_per_launch")
         roofline["fwd"]["traffic"] = tr.get("ema_fwd_bytes_per_launch")
 
     cpu_baseline = None
-    if world == 1 and not args.no_cpu_baseline:
+    if world == 1 and not args.no_cpu_baseline and args.workload == "c3":
         sb, sL = 1, 4096
         val, sec, threads = cpu_reference_sample(sb, sL, h, d, steps=1, warmup=0)
         cpu_baseline = {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
@@ -356,14 +382,16 @@ def run_gpu(args):
             cpu_baseline["c_oracle_error"] = str(exc)[:120]
 
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
+        "metric": "ema_fwd_tokens_per_s" if fwd_only else METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 in/out, f32 accumulate", "data": "synthetic",
         "config": {"workload": W["name"], "b_per_gpu": b, "L": L, "h": h, "d": d, "chunk": W["chunk"],
                    "tile_steps": ts, "sharding": "batch rows per rank, no data-path collective",
-                   "l2": "inputs (2 GiB per step) exceed the 126 MB L2; no flush needed"},
+                   "decay": "per head [h]" if per_head else "per step [b, L, h]",
+                   "l2": f"inputs ({x.numel() * 2 * (1 if fwd_only else 2) / 2**30:.1f} GiB per step) exceed the 126 MB L2; "
+                         "no flush needed"},
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-        "gpu_launches": 4 * K, "clocks": clocks,
+        "gpu_launches": (1 if fwd_only else 4 if per_head else 3) * K, "clocks": clocks,
     }
     print(json.dumps(line))
     if world > 1:
@@ -376,6 +404,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS),
+                    help="c3 = the headline configuration (default); c2, c4 = the other single-GPU configurations")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-spinup", action="store_true", help="skip the untimed run-in used for clock sampling (profiling runs)")
