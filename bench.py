@@ -4,6 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W]            # this library
     python bench.py --impl reference [--steps K] [--warmup W]      # the reference's CPU path
     python bench.py --workload c2|c4 [--no-e2e]                    # the other single-GPU configurations
+    torchrun ... bench.py --gpus N --workload c5                    # sequence parallel, one 65536-step segment per rank
 
 One "step" is one forward (y, saved tile states) plus one backward (dx, da) over one batch of
 synthetic input with the shapes of the headline workload: x, dy bf16 [16, 8192, 2, 1024] ~ N(0,1),
@@ -35,6 +36,10 @@ WORKLOADS = {
                b=16, L=8192, h=2, d=1024, chunk=128, per_head=False, fwd_only=True, lo=2.0, hi=6.0),
     "c4": dict(name="ema_fwd_bwd_b4_L65536_h8_d1024_bf16_perstep_decay_chunk512",
                b=4, L=65536, h=8, d=1024, chunk=512, per_head=False, fwd_only=False, lo=3.0, hi=8.0),
+    # sequence parallel: every rank holds one contiguous 65536-step segment of b8 h4 d1024 sequences of length
+    # 65536 * N (N = 8 gives the suite's 524288-step configuration); carries are exchanged over NCCL
+    "c5": dict(name="ema_fwd_bwd_seqparallel_b8_Lseg65536_h4_d1024_bf16_perstep_decay_chunk256",
+               b=8, L=65536, h=4, d=1024, chunk=256, per_head=False, fwd_only=False, lo=2.0, hi=6.0, seq_parallel=True),
 }
 WORKLOAD = WORKLOADS["c3"]
 METRIC = "ema_fwd_bwd_tokens_per_s"
@@ -169,6 +174,9 @@ def run_gpu(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    elif WORKLOADS[args.workload].get("seq_parallel"):
+        # the sequence-parallel entry point needs a process group even when it has a single member
+        dist.init_process_group("nccl", store=dist.HashStore(), rank=0, world_size=1, device_id=dev)
 
     import ema_b200
     from ema_b200 import ops
@@ -176,6 +184,7 @@ def run_gpu(args):
     W = WORKLOADS[args.workload]
     b, L, h, d = W["b"], W["L"], W["h"], W["d"]
     per_head, fwd_only = W["per_head"], W["fwd_only"]
+    seq_parallel = bool(W.get("seq_parallel"))
     g = torch.Generator(device=dev).manual_seed(1236 + rank)
     x = torch.randn((b, L, h, d), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
     dy = torch.randn((b, L, h, d), generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
@@ -214,8 +223,17 @@ def run_gpu(args):
                 pending[slot].wait()
                 pending[slot] = None
 
+    def sp_forward():
+        from ema_b200 import dist as ema_dist
+        xr, ar = x.detach().requires_grad_(True), a.detach().requires_grad_(True)
+        return xr, ar, ema_dist.ema_sequence_parallel(xr, ar)
+
     def step():
         nonlocal ws
+        if seq_parallel:
+            _, _, out = sp_forward()
+            out.backward(dy)
+            return
         ops.ema_fwd(x, a, out=y, tile_states=tile_states)
         if fwd_only:
             return
@@ -258,6 +276,13 @@ def run_gpu(args):
     start.record()
     for i in range(K):
         ev[i][0].record()
+        if seq_parallel:
+            _, _, out = sp_forward()
+            ev[i][1].record()
+            out.backward(dy)
+            ev[i][2].record()
+            del out
+            continue
         ops.ema_fwd(x, a, out=y, tile_states=tile_states)
         ev[i][1].record()
         if not fwd_only:
@@ -291,6 +316,8 @@ def run_gpu(args):
             raise RuntimeError("skipped (--no-e2e)")
         if fwd_only:
             raise RuntimeError("skipped: the host pipeline runs forward + backward, this workload is forward only")
+        if seq_parallel:
+            raise RuntimeError("skipped: the host pipeline shards batch rows, this workload shards the sequence")
         hx, hdy = x.cpu().pin_memory(), dy.cpu().pin_memory()
         ha = a.cpu().pin_memory()
         hy, hdx = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
@@ -386,15 +413,18 @@ def run_gpu(args):
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 in/out, f32 accumulate", "data": "synthetic",
         "config": {"workload": W["name"], "b_per_gpu": b, "L": L, "h": h, "d": d, "chunk": W["chunk"],
-                   "tile_steps": ts, "sharding": "batch rows per rank, no data-path collective",
+                   "tile_steps": ts,
+                   "sharding": ("contiguous sequence segment per rank; all-gather of per-row carries, prefix / suffix "
+                                "re-scan") if seq_parallel else "batch rows per rank, no data-path collective",
                    "decay": "per head [h]" if per_head else "per step [b, L, h]",
                    "l2": f"inputs ({x.numel() * 2 * (1 if fwd_only else 2) / 2**30:.1f} GiB per step) exceed the 126 MB L2; "
                          "no flush needed"},
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
-        "gpu_launches": (1 if fwd_only else 4 if per_head else 3) * K, "clocks": clocks,
+        "gpu_launches": (1 if fwd_only else 4 if per_head else 3) * K * (2 if seq_parallel and world > 1 else 1),
+        "clocks": clocks,
     }
     print(json.dumps(line))
-    if world > 1:
+    if dist.is_initialized():
         dist.destroy_process_group()
 
 
@@ -405,7 +435,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS),
-                    help="c3 = the headline configuration (default); c2, c4 = the other single-GPU configurations")
+                    help="c3 = the headline configuration (default); c2, c4 = the other single-GPU configurations; "
+                         "c5 = sequence parallel over the ranks")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-spinup", action="store_true", help="skip the untimed run-in used for clock sampling (profiling runs)")
