@@ -89,6 +89,10 @@ int ema_b200_device_status(int clear);
  * 1 = CUDA-core path only.  fp32 problems always take the CUDA-core path (exactness).  Meant for A/B
  * measurements and tests; the environment variable EMA_B200_PATH=fma sets the same switch at load. */
 int ema_b200_set_path(int path);
+/* Whether the bf16 kernels may cut a work item across thread blocks when the items do not divide evenly among
+ * the SMs (1, the default; the environment variable EMA_B200_SPLIT=0 turns it off at load).  Returns the
+ * previous setting.  Results do not depend on it; meant for A/B measurements and tests. */
+int ema_b200_set_split(int on);
 /* Kernel family the last ema_b200_fwd / ema_b200_bwd call on this thread launched: 1 = tensor cores,
  * 0 = CUDA cores, -1 = none yet.  Lets a test assert that the tensor-core path really ran. */
 int ema_b200_last_path(void);
@@ -120,10 +124,18 @@ size_t ema_b200_bwd_workspace_bytes(const ema_b200_problem *p);
  *   log_decay_sum optional [b, h] fp32: sum of log a over the steps that were processed
  *   stop_below    0 to scan all L steps.  > 0: stop after the first tile at whose end the
  *                 product of decays since step 0 is below this value - used to re-scan only the
- *                 prefix an incoming carry can still influence (sequence-parallel fix-up). */
+ *                 prefix an incoming carry can still influence (sequence-parallel fix-up).
+ *   workspace     optional scratch of ema_b200_fwd_workspace_bytes(p) bytes, 16-byte aligned.  With
+ *                 it, and when the work items (scan row x 128 channels) do not divide evenly among
+ *                 the SMs, the bf16 kernels cut items across thread blocks and pass the carries
+ *                 through this scratch, so that every SM has work; without it each item stays on
+ *                 one thread block.  The results are the same either way.  Two calls that may
+ *                 overlap in time must not share a scratch. */
+size_t ema_b200_fwd_workspace_bytes(const ema_b200_problem *p);
 int ema_b200_fwd(const ema_b200_problem *p, const void *x, const float *decay, void *y,
-                 float *chunk_states, float *tile_states, const float *init_state,
-                 float *final_state, float *log_decay_sum, float stop_below, void *stream);
+                 float *chunk_states, float *tile_states, const float *init_state, float *final_state,
+                 float *log_decay_sum, float stop_below, void *workspace, size_t workspace_bytes,
+                 void *stream);
 
 /* Backward scan: reads x, dy and the saved tile states once, writes dx and d(decay).
  * Replaces the nine launches and the torch glue of _ema_chunk_scan_combined_bwd

@@ -62,7 +62,7 @@ def test_host_only_queries(ema_lib):
 def test_bad_problem_is_rejected_before_launch(ema_lib, kw, code):
     p = _problem(**kw)
     one = ctypes.c_void_p(256)
-    rc = ema_lib.ema_b200_fwd(ctypes.byref(p), one, one, one, None, None, None, None, None, ctypes.c_float(0), None)
+    rc = ema_lib.ema_b200_fwd(ctypes.byref(p), one, one, one, None, None, None, None, None, ctypes.c_float(0), None, 0, None)
     assert rc == code
 
 
@@ -70,18 +70,18 @@ def test_null_and_misaligned_pointers(ema_lib):
     p = _problem()
     ok = ctypes.c_void_p(256)
     f0 = ctypes.c_float(0)
-    assert ema_lib.ema_b200_fwd(None, ok, ok, ok, None, None, None, None, None, f0, None) == -1
-    assert ema_lib.ema_b200_fwd(ctypes.byref(p), None, ok, ok, None, None, None, None, None, f0, None) == -1
-    assert ema_lib.ema_b200_fwd(ctypes.byref(p), ok, None, ok, None, None, None, None, None, f0, None) == -1
+    assert ema_lib.ema_b200_fwd(None, ok, ok, ok, None, None, None, None, None, f0, None, 0, None) == -1
+    assert ema_lib.ema_b200_fwd(ctypes.byref(p), None, ok, ok, None, None, None, None, None, f0, None, 0, None) == -1
+    assert ema_lib.ema_b200_fwd(ctypes.byref(p), ok, None, ok, None, None, None, None, None, f0, None, 0, None) == -1
     # no output requested at all
-    assert ema_lib.ema_b200_fwd(ctypes.byref(p), ok, ok, None, None, None, None, None, None, f0, None) == -1
+    assert ema_lib.ema_b200_fwd(ctypes.byref(p), ok, ok, None, None, None, None, None, None, f0, None, 0, None) == -1
     # fp32 data at an odd address
-    assert ema_lib.ema_b200_fwd(ctypes.byref(p), ctypes.c_void_p(258), ok, ok, None, None, None, None, None, f0, None) == -2
+    assert ema_lib.ema_b200_fwd(ctypes.byref(p), ctypes.c_void_p(258), ok, ok, None, None, None, None, None, f0, None, 0, None) == -2
     # chunk states without a chunk size
     p0 = _problem(chunk=0)
-    assert ema_lib.ema_b200_fwd(ctypes.byref(p0), ok, ok, ok, ok, None, None, None, None, f0, None) == -1
+    assert ema_lib.ema_b200_fwd(ctypes.byref(p0), ok, ok, ok, ok, None, None, None, None, f0, None, 0, None) == -1
     # negative stop threshold
-    assert ema_lib.ema_b200_fwd(ctypes.byref(p), ok, ok, ok, None, None, None, None, None, ctypes.c_float(-1), None) == -1
+    assert ema_lib.ema_b200_fwd(ctypes.byref(p), ok, ok, ok, None, None, None, None, None, ctypes.c_float(-1), None, 0, None) == -1
     # backward: missing workspace, workspace too small
     assert ema_lib.ema_b200_bwd(ctypes.byref(p), ok, ok, ok, ok, ok, ok, None, None, f0, None, 0, None) == -6
     assert ema_lib.ema_b200_bwd(ctypes.byref(p), ok, ok, ok, ok, ok, ok, None, None, f0, ok, 16, None) == -6

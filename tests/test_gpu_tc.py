@@ -139,3 +139,43 @@ def test_tc_backward_equals_fma_path(per_head, prescaled, _lib):
     for key, rel in (("dx", 1.6e-2), ("ddecay", 5e-3), ("dinit_state", 5e-3)):
         assert_close_bf16(gt[key], gf[key].float().cpu().numpy(), key, rel=rel)
     assert _lib.ema_b200_device_status(1) == 0
+
+
+SPLIT_SHAPES = [
+    (10, 640, 2, 1024),    # 160 items of 5 tiles on 148 SMs
+    (19, 300, 1, 1024),    # 152 items of 3 tiles, ragged last tile
+    (3, 2000, 7, 1000),    # 168 items of 16 tiles, d not a multiple of 128
+]
+
+
+@pytest.mark.parametrize("shape", SPLIT_SHAPES)
+@pytest.mark.parametrize("per_head", [False, True])
+def test_items_cut_across_thread_blocks_give_identical_results(shape, per_head, _lib):
+    """When the work items do not divide evenly among the SMs the kernels cut some of them across thread blocks
+    and hand the carries through global memory: same arithmetic per tile, so bit-identical outputs."""
+    if torch.cuda.get_device_properties(0).multi_processor_count != 148:
+        pytest.skip("shapes chosen for 148 SMs")
+    E = _E()
+    b, L, h, d = shape
+    x, a, dy, np_in = make_inputs(77, b, L, h, d, per_head=per_head, dtype=torch.bfloat16)
+    init = torch.randn(b, h, d, device="cuda")
+    dfin = torch.randn(b, h, d, device="cuda")
+    res = []
+    for split in (1, 0):
+        _lib.ema_b200_set_split(split)
+        f = E.ops.ema_fwd(x, a, init_state=init, want_tile_states=True, want_final=True, chunk=128, want_chunk_states=True)
+        g = E.ops.ema_bwd(x, a, dy, f["tile_states"], dfinal_state=dfin, want_dinit=True)
+        torch.cuda.synchronize()
+        assert _lib.ema_b200_last_path() == 1
+        res.append((f["y"], f["final_state"], f["chunk_states"], f["tile_states"], g["dx"], g["ddecay"], g["dinit_state"]))
+    _lib.ema_b200_set_split(1)
+    for got, ref, what in zip(res[0], res[1], ("y", "final", "chunk_states", "tile_states", "dx", "da", "dinit")):
+        assert torch.equal(got, ref), what
+    assert _lib.ema_b200_device_status(0) == 0
+    # and the plain problem (no initial state) against the oracle
+    f = E.ops.ema_fwd(x, a, want_tile_states=True)
+    g = E.ops.ema_bwd(x, a, dy, f["tile_states"])
+    y_ref, dx_ref, da_ref = oracle_fwd_bwd(np_in)
+    assert_close_bf16(f["y"], y_ref, "y")
+    assert_close_bf16(g["dx"], dx_ref, "dx")
+    assert_close_bf16(g["ddecay"], da_ref, "da")

@@ -90,6 +90,7 @@ extern "C" const char *ema_b200_error_string(int code) {
 }
 
 extern "C" int ema_b200_device_status(int clear) { return read_tc_status(clear); }
+extern "C" int ema_b200_set_split(int on) { return tc_set_split(on); }
 
 extern "C" int ema_b200_last_path(void) { return g_last_path; }
 
@@ -110,8 +111,8 @@ extern "C" size_t ema_b200_tile_states_bytes(const ema_b200_problem *p) {
     return static_cast<size_t>(p->b * p->h * n_tiles * p->d) * sizeof(float);
 }
 
-extern "C" size_t ema_b200_bwd_workspace_bytes(const ema_b200_problem *p) {
-    if (check_problem(p) != EMA_OK) return 0;
+// floats of decay-gradient partial sums (the first part of the backward's workspace), rounded to 256 bytes
+static size_t bwd_partial_bytes(const ema_b200_problem *p) {
     // sized for the narrowest channel tile (vec = 1) so that it never depends on pointer alignment
     const int64_t n_tiles = (p->L + kFmaTile - 1) / kFmaTile;
     const int64_t n_dtiles = (p->d + kFmaCT - 1) / kFmaCT;
@@ -119,12 +120,27 @@ extern "C" size_t ema_b200_bwd_workspace_bytes(const ema_b200_problem *p) {
     const int64_t per_step = rows * n_dtiles * n_tiles * kFmaTile;
     const int64_t per_head = kHeadPartialOffset(rows) + rows * n_dtiles * n_tiles * (kFmaThreads / 32);
     const int64_t n = p->decay_mode == EMA_DECAY_PER_STEP ? per_step : per_head;
-    return static_cast<size_t>(n > 0 ? n : 1) * sizeof(float);
+    return (static_cast<size_t>(n > 0 ? n : 1) * sizeof(float) + 255) / 256 * 256;
+}
+
+static size_t sync_bytes(const ema_b200_problem *p) {
+    return p->dtype == EMA_BF16 ? tc_sync_bytes(p->b, p->h, p->d) : 0;
+}
+
+extern "C" size_t ema_b200_bwd_workspace_bytes(const ema_b200_problem *p) {
+    if (check_problem(p) != EMA_OK) return 0;
+    return bwd_partial_bytes(p) + sync_bytes(p);
+}
+
+extern "C" size_t ema_b200_fwd_workspace_bytes(const ema_b200_problem *p) {
+    if (check_problem(p) != EMA_OK) return 0;
+    return sync_bytes(p);
 }
 
 extern "C" int ema_b200_fwd(const ema_b200_problem *p, const void *x, const float *decay, void *y,
                             float *chunk_states, float *tile_states, const float *init_state,
-                            float *final_state, float *log_decay_sum, float stop_below, void *stream) {
+                            float *final_state, float *log_decay_sum, float stop_below, void *workspace,
+                            size_t workspace_bytes, void *stream) {
     int rc = check_problem(p);
     if (rc) return rc;
     if (chunk_states && p->chunk <= 0) return EMA_ERR_BADARG;
@@ -157,6 +173,10 @@ extern "C" int ema_b200_fwd(const ema_b200_problem *p, const void *x, const floa
     fp.init_state = init_state; fp.final_state = final_state;
     fp.log_decay_sum = log_decay_sum;
     fp.stop_below = stop_below;
+    // optional scratch: without it (or with too little) the kernels simply never cut a work item across CTAs
+    const bool ws_ok = workspace && aligned(workspace, 16) && workspace_bytes >= sync_bytes(p);
+    fp.sync_ws = ws_ok ? workspace : nullptr;
+    fp.sync_ws_bytes = ws_ok ? workspace_bytes : 0;
     if (rows * fp.n_dtiles >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;
     if (p->dtype == EMA_BF16 && y && stop_below == 0.f && tc_enabled() &&
         tc_tensor_ok(x, p->d, p->x_sb, p->x_sl, p->x_sh, p->b, p->L, p->h) &&
@@ -208,6 +228,8 @@ extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const floa
     fp.dfinal_state = dfinal_state; fp.dinit_state = dinit_state;
     fp.da_partial = static_cast<float *>(workspace);
     fp.stop_below = stop_below;
+    fp.sync_ws = static_cast<uint8_t *>(workspace) + bwd_partial_bytes(p);
+    fp.sync_ws_bytes = sync_bytes(p);
     if (rows * fp.n_dtiles >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;
     bool done = false;
     if (p->dtype == EMA_BF16 && stop_below == 0.f && tc_enabled() && vec == 4 &&

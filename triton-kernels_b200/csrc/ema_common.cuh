@@ -32,6 +32,9 @@ struct FusedParams {
     int n_tiles, n_dtiles;
     int64_t n_chunks;
     float stop_below;
+    // scratch for carries handed between CTAs of the tensor-core kernels (optional; see tc_sync_bytes)
+    void *sync_ws;
+    size_t sync_ws_bytes;
 };
 
 // ---- raw vector types: VEC elements of T moved by one load/store instruction ----------------
@@ -164,5 +167,8 @@ bool tc_tensor_ok(const void *base, int64_t d, int64_t sb, int64_t sl, int64_t s
 int launch_fused_fwd_tc(const FusedParams &p, cudaStream_t stream);
 int launch_fused_bwd_tc(const FusedParams &p, cudaStream_t stream);
 int read_tc_status(int clear);
+// bytes of scratch that let the tensor-core kernels cut work items across CTAs (0 = never needed)
+size_t tc_sync_bytes(int64_t b, int64_t h, int64_t d);
+int tc_set_split(int on);   // returns the previous setting
 
 }  // namespace ema

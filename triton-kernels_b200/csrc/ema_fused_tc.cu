@@ -27,6 +27,8 @@
 // carry ready (a ring of 4 so that the warp on the serial carry chain can run ahead of the others), and
 // stage staged.  Every wait is bounded (ema_tc_common.cuh): after a timeout the roles run their loops to
 // the end without waiting, the CTA tears down normally and the host sees EMA_ERR_TIMEOUT.
+#include <cstdlib>
+
 #include "ema_common.cuh"
 #include "ema_tc_common.cuh"
 
@@ -249,7 +251,74 @@ struct TcParams {
     int n_tiles;      // 128-step tiles; one saved state per tile and row (layout shared with the CUDA-core path)
     int n_dtiles, n_items;
     int64_t n_chunks;
+    // split schedule (see Sched): carries handed from CTA to CTA, 128 floats and one arrival counter per work item
+    int split;
+    float *carry;
+    unsigned *flags;
 };
+
+// ---------------------------------------------------------------------------------------------
+// Which tiles a CTA works on.  Whole items dealt round-robin (split = 0) leave SMs idle when the item count is
+// not a multiple of the grid (256 items on 148 SMs: 128 CTAs x 2).  With split = 1 the tiles of all items, in
+// item-major order, are cut into one contiguous range per CTA.  A range is at least one item long, so it is a
+// possibly partial first item, whole items, and a possibly partial last item, and every item is cut at most
+// once.  The CTA that owns the first part of a cut item hands the carry to the owner of the second part through
+// global memory (128 floats + an arrival counter per item).  Each CTA works on the piece that somebody waits
+// for FIRST and on the piece that waits for somebody LAST, so that a carry is published a whole range ahead of
+// its use and no wait depends on another wait; the wait itself is bounded like every other wait of the kernel.
+// ---------------------------------------------------------------------------------------------
+struct Piece {
+    int64_t item;
+    int k0, k1;   // tiles [k0, k1) of the item
+};
+struct Sched {
+    int64_t first, stride;
+    int n, n_tiles, head_k0, tail_k1;
+    bool split;
+    __device__ Sched(int n_items, int n_tiles_, bool split_) : n_tiles(n_tiles_), split(split_) {
+        if (!split_) {
+            first = blockIdx.x;
+            stride = gridDim.x;
+            n = n_items > static_cast<int>(blockIdx.x) ? (n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+            head_k0 = 0;
+            tail_k1 = n_tiles_;
+        } else {
+            const int64_t units = static_cast<int64_t>(n_items) * n_tiles_;
+            const int64_t u0 = blockIdx.x * units / gridDim.x, u1 = (blockIdx.x + 1) * units / gridDim.x;
+            first = u0 / n_tiles_;
+            const int64_t last = (u1 - 1) / n_tiles_;
+            stride = 1;
+            n = static_cast<int>(last - first + 1);
+            head_k0 = static_cast<int>(u0 - first * n_tiles_);
+            tail_k1 = static_cast<int>(u1 - last * n_tiles_);
+        }
+    }
+    // idx-th piece in working order.  FORWARD scan: a cut last item starts at tile 0 (somebody waits for it), a cut
+    // first item needs a carry: [last, middle ..., first].  BACKWARD scan: the roles are swapped, ascending order.
+    template <bool FORWARD>
+    __device__ Piece get(int idx) const {
+        int q = idx;
+        if (FORWARD && split && n > 1) q = idx == 0 ? n - 1 : (idx == n - 1 ? 0 : idx);
+        Piece pc;
+        pc.item = first + q * stride;
+        pc.k0 = q == 0 ? head_k0 : 0;
+        pc.k1 = q == n - 1 ? tail_k1 : n_tiles;
+        return pc;
+    }
+};
+// Bounded wait for the two halves of a carry (one arrival per 64-channel half).
+__device__ __forceinline__ bool wait_carry(const unsigned *flag, volatile int *abort_flag, int site) {
+    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+        unsigned v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v >= 2u) return true;
+        if (*abort_flag) return false;
+        __nanosleep(64);
+    }
+    *abort_flag = 1;
+    atomicCAS(&g_tc_status, 0, 0x100 | (site & 0xff));
+    return false;
+}
 
 // ---------------------------------------------------------------------------------------------
 // forward
@@ -326,7 +395,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int64_t n_items = p.n_items;
+    const Sched sched(p.n_items, p.n_tiles, p.split != 0);
     // log2 of the multiplicative decay of one step
     auto log2_decay = [&](float v) { return conv ? v * 1.4426950408889634f : log2f(v); };
 
@@ -336,11 +405,12 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             // ---------------- TMA producer ----------------
             if (lane == 0) {
                 uint32_t it = 0;
-                for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                    const int dtile = static_cast<int>(item % p.n_dtiles);
-                    const int64_t row = item / p.n_dtiles;
+                for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
+                    const Piece pc = sched.get<true>(pi);
+                    const int dtile = static_cast<int>(pc.item % p.n_dtiles);
+                    const int64_t row = pc.item / p.n_dtiles;
                     const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
-                    for (int k = 0; k < p.n_tiles; ++k, ++it) {
+                    for (int k = pc.k0; k < pc.k1; ++k, ++it) {
                         const int s = it % kFwdStages;
                         const uint32_t ph = (it / kFwdStages) & 1;
                         if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 1)) break;
@@ -359,9 +429,10 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 // agree on the build counter mt without talking to each other.
                 uint32_t it = 0, mt = 0;
                 int cur_head = -1, mb_cur = 0;
-                for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                    const int hi = static_cast<int>((item / p.n_dtiles) % p.h);
-                    for (int k = 0; k < p.n_tiles; ++k, ++it) {
+                for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
+                    const Piece pc = sched.get<true>(pi);
+                    const int hi = static_cast<int>((pc.item / p.n_dtiles) % p.h);
+                    for (int k = pc.k0; k < pc.k1; ++k, ++it) {
                         const int s = it % kFwdStages;
                         const uint32_t ph = (it / kFwdStages) & 1;
                         const int acc = it & 1;
@@ -395,12 +466,13 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             // ---------------- TMA store issuer ----------------
             if (tid == kStoreThread) {
                 uint32_t it = 0;
-                for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                    const int dtile = static_cast<int>(item % p.n_dtiles);
-                    const int64_t row = item / p.n_dtiles;
+                for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
+                    const Piece pc = sched.get<true>(pi);
+                    const int dtile = static_cast<int>(pc.item % p.n_dtiles);
+                    const int64_t row = pc.item / p.n_dtiles;
                     const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
                     const bool two = dtile * DT + kBlockCols < p.d;   // the second 64-channel block exists
-                    for (int k = 0; k < p.n_tiles; ++k, ++it) {
+                    for (int k = pc.k0; k < pc.k1; ++k, ++it) {
                         const int s = it % kFwdStages;
                         if (!mbar_wait(bar(B_STAGED + s), (it / kFwdStages) & 1, abort_flag, 9)) break;
                         const uint32_t src = sbase + FwdSmem::x + s * kTileBytes;
@@ -427,21 +499,31 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         const bool loader = half == 0;   // 128 threads that move per-channel vectors: thread m <-> channel m
         uint32_t it = 0, mt = 0;
         int cur_head = -1;
-        for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-            const int dtile = static_cast<int>(item % p.n_dtiles);
-            const int64_t row = item / p.n_dtiles;
+        for (int pi = 0; pi < sched.n; ++pi) {
+            const Piece pc = sched.get<true>(pi);
+            const int dtile = static_cast<int>(pc.item % p.n_dtiles);
+            const int64_t row = pc.item / p.n_dtiles;
             const int hi = static_cast<int>(row % p.h);
             const int c0 = dtile * DT;
             const bool ch_ok = loader && c0 + m < p.d;
             float *ts_item = p.tile_states ? p.tile_states + row * p.n_tiles * p.d + c0 : nullptr;
+            const bool publish = pc.k1 < p.n_tiles;   // the item continues in another CTA: hand it the state
+            float *carry_item = p.carry + pc.item * DT;
             if (loader) {
-                const float v = (p.init_state && ch_ok) ? p.init_state[row * p.d + c0 + m] : 0.f;
+                float v;
+                if (pc.k0 > 0) {   // second part of a cut item: the state comes from the CTA that made the first part
+                    if (lane == 0) wait_carry(p.flags + pc.item, abort_flag, 22);
+                    __syncwarp();
+                    v = __ldcg(carry_item + m);
+                } else {
+                    v = (p.init_state && ch_ok) ? p.init_state[row * p.d + c0 + m] : 0.f;
+                    if (p.chunk_states && ch_ok) p.chunk_states[(row * p.n_chunks) * p.d + c0 + m] = v;
+                }
                 h_sm[(it & (kRing - 1)) * DT + m] = v;
-                if (p.chunk_states && ch_ok) p.chunk_states[(row * p.n_chunks) * p.d + c0 + m] = v;
             }
-            bar_sync(1, kEpiThreads);  // once per item: the previous item is finished everywhere, the state is in place
+            bar_sync(1, kEpiThreads);  // once per piece: the previous one is finished everywhere, the state is in place
             if (m == QT - 1) mbar_arrive(bar(B_H + (it & (kRing - 1))));
-            for (int k = 0; k < p.n_tiles; ++k, ++it) {
+            for (int k = pc.k0; k < pc.k1; ++k, ++it) {
                 const int acc = it & 1, slot = it & (kRing - 1), s = it % kFwdStages;
                 const uint32_t aph = (it >> 1) & 1, hph = (it / kRing) & 1;
                 if (per_step || hi != cur_head) { cur_head = hi; ++mt; }
@@ -476,7 +558,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         y[c + 2] = fmaf(E, hv.z, y[c + 2]);
                         y[c + 3] = fmaf(E, hv.w, y[c + 3]);
                     }
-                    if (m == QT - 1 && k + 1 < p.n_tiles) {  // the last row is the state entering the next tile
+                    if (m == QT - 1 && k + 1 < pc.k1) {  // the last row is the state entering the next tile
                         float *hout = h_sm + ((it + 1) & (kRing - 1)) * DT + cb;
 #pragma unroll
                         for (int c = 0; c < 32; c += 4)
@@ -487,7 +569,8 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     // cost the common path registers
                     const bool at_chunk_end = p.chunk_states && t + 1 < L && (t + 1) % p.chunk == 0;
                     const bool at_last_step = p.final_state && t == L - 1;
-                    if (at_chunk_end || at_last_step) {
+                    const bool at_cut = publish && m == QT - 1 && k + 1 == pc.k1;
+                    if (at_chunk_end || at_last_step || at_cut) {
                         float tmp[32];  // a copy, so that y itself never has its address taken and stays in registers
 #pragma unroll
                         for (int c = 0; c < 32; ++c) tmp[c] = y[c];
@@ -495,6 +578,13 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         if (at_chunk_end)
                             store_row32(p.chunk_states + (row * p.n_chunks + (t + 1) / p.chunk) * p.d + c0 + cb, tmp, n_valid);
                         if (at_last_step) store_row32(p.final_state + row * p.d + c0 + cb, tmp, n_valid);
+                        if (at_cut) {
+                            store_row32(carry_item + cb, tmp, 32);
+                            if (pass == 1) {   // this half of the carry is complete
+                                __threadfence();
+                                atomicAdd(p.flags + pc.item, 1u);
+                            }
+                        }
                     }
                     // bf16 -> the stage, in the TMA's 128-byte swizzle
 #pragma unroll
@@ -550,9 +640,10 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             if (lane == 0) mbar_arrive(bar(B_MAT_FULL + mb));
             ++mt;
         };
-        for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-            const int64_t row = item / p.n_dtiles;
-            const int dtile = static_cast<int>(item % p.n_dtiles);
+        for (int pi = 0; pi < sched.n; ++pi) {
+            const Piece pc = sched.get<true>(pi);
+            const int64_t row = pc.item / p.n_dtiles;
+            const int dtile = static_cast<int>(pc.item % p.n_dtiles);
             const int64_t bi = row / p.h, hi = row % p.h;
             const float *arow = p.decay + (per_step ? bi * p.a_sb + hi * p.a_sh : hi * p.a_sh);
             if (!per_step) {
@@ -568,10 +659,10 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             // per-step decay: the raw value of step r of the next tile is fetched one tile ahead
             float logsum = 0.f;
             const float ident = conv ? 0.f : 1.f;   // raw value of an identity step (past L)
-            float v_next = (row_owner && r < L) ? arow[static_cast<int64_t>(r) * p.a_sl] : ident;
-            for (int k = 0; k < p.n_tiles; ++k) {
+            float v_next = (row_owner && pc.k0 * QT + r < L) ? arow[static_cast<int64_t>(pc.k0 * QT + r) * p.a_sl] : ident;
+            for (int k = pc.k0; k < pc.k1; ++k) {
                 const float v = v_next;
-                if (k + 1 < p.n_tiles) {
+                if (k + 1 < pc.k1) {
                     const int t = (k + 1) * QT + r;
                     v_next = (row_owner && t < L) ? arow[static_cast<int64_t>(t) * p.a_sl] : ident;
                 }
@@ -621,6 +712,10 @@ struct TcBwdParams {
     int n_tiles, n_dtiles, n_items;
     int n_dt64;       // 64-channel slices per row in the partial-sum buffer
     int64_t head_partial_offset;
+    // split schedule (see Sched): adjoint carries handed from CTA to CTA
+    int split;
+    float *carry;
+    unsigned *flags;
 };
 
 constexpr int kBwdStages = 2;
@@ -715,7 +810,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
-    const int64_t n_items = p.n_items;
+    const Sched sched(p.n_items, p.n_tiles, p.split != 0);
     auto log2_decay = [&](float v) { return conv ? v * 1.4426950408889634f : log2f(v); };
 
     if (warp < 4) {
@@ -724,11 +819,12 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             // ---------------- TMA producer ----------------
             if (lane == 0) {
                 uint32_t it = 0;
-                for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                    const int dtile = static_cast<int>(item % p.n_dtiles);
-                    const int64_t row = item / p.n_dtiles;
+                for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
+                    const Piece pc = sched.get<false>(pi);
+                    const int dtile = static_cast<int>(pc.item % p.n_dtiles);
+                    const int64_t row = pc.item / p.n_dtiles;
                     const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
-                    for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
+                    for (int k = pc.k1 - 1; k >= pc.k0; --k, ++it) {
                         const int s = it % kBwdStages;
                         const uint32_t ph = (it / kBwdStages) & 1;
                         if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 11)) break;
@@ -752,9 +848,10 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                                          make_desc_sw128(sbase + BwdSmem::m_z, 16, 1024)};
                 const uint64_t ud[2] = {make_desc_sw128(sbase + BwdSmem::m_u00, 16, 1024),
                                         make_desc_sw128(sbase + BwdSmem::m_uk1, 16, 1024)};
-                for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                    const int hi = static_cast<int>((item / p.n_dtiles) % p.h);
-                    for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
+                for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
+                    const Piece pc = sched.get<false>(pi);
+                    const int hi = static_cast<int>((pc.item / p.n_dtiles) % p.h);
+                    for (int k = pc.k1 - 1; k >= pc.k0; --k, ++it) {
                         const int s = it % kBwdStages;
                         const uint32_t ph = (it / kBwdStages) & 1;
                         const int acc = it & 1;
@@ -788,12 +885,13 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             // ---------------- TMA store issuer ----------------
             if (tid == kStoreThread) {
                 uint32_t it = 0;
-                for (int64_t item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                    const int dtile = static_cast<int>(item % p.n_dtiles);
-                    const int64_t row = item / p.n_dtiles;
+                for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
+                    const Piece pc = sched.get<false>(pi);
+                    const int dtile = static_cast<int>(pc.item % p.n_dtiles);
+                    const int64_t row = pc.item / p.n_dtiles;
                     const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
                     const bool two = dtile * DT + kBlockCols < p.d;   // the second 64-channel block exists
-                    for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
+                    for (int k = pc.k1 - 1; k >= pc.k0; --k, ++it) {
                         const uint32_t src = sbase + BwdSmem::ostage;
                         if (!mbar_wait(bar(B_STG_FULL + 0), it & 1, abort_flag, 19)) break;
                         tma_store_4d(&tm_o, src, dtile * DT, hi, k * QT, bi);
@@ -821,10 +919,13 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         const bool loader = half == 0;  // 128 threads: thread m fetches channel m of the saved states
         uint32_t it = 0, mt = 0;
         int cur_head = -1;
-        for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-            const int dtile = static_cast<int>(item % p.n_dtiles);
-            const int64_t row = item / p.n_dtiles;
+        for (int pi = 0; pi < sched.n; ++pi) {
+            const Piece pc = sched.get<false>(pi);
+            const int dtile = static_cast<int>(pc.item % p.n_dtiles);
+            const int64_t row = pc.item / p.n_dtiles;
             const int hi = static_cast<int>(row % p.h);
+            const bool publish = pc.k0 > 0;   // the item continues to the left in another CTA: hand it the adjoint
+            float *carry_item = p.carry + pc.item * DT;
             const int c0 = dtile * DT;
             const bool ch_ok = loader && c0 + m < p.d;
             const float *ts_item = p.tile_states + row * p.n_tiles * p.d + c0 + m;
@@ -838,18 +939,26 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             float hs_next = 0.f;
             if (loader) {
                 const int slot0 = it & (kRing - 1);
-                hs_sm[slot0 * DT + m] = ch_ok ? ts_item[static_cast<int64_t>(p.n_tiles - 1) * p.d] : 0.f;
-                g_sm[slot0 * DT + m] = (p.dfinal_state && ch_ok) ? p.dfinal_state[row * p.d + c0 + m] : 0.f;
+                hs_sm[slot0 * DT + m] = ch_ok ? ts_item[static_cast<int64_t>(pc.k1 - 1) * p.d] : 0.f;
+                float gv;
+                if (pc.k1 < p.n_tiles) {   // left part of a cut item: the adjoint comes from the CTA that made the right part
+                    if (lane == 0) wait_carry(p.flags + pc.item, abort_flag, 23);
+                    __syncwarp();
+                    gv = __ldcg(carry_item + m);
+                } else {
+                    gv = (p.dfinal_state && ch_ok) ? p.dfinal_state[row * p.d + c0 + m] : 0.f;
+                }
+                g_sm[slot0 * DT + m] = gv;
             }
             bar_sync(1, kEpiThreads);
             if (m == 0) mbar_arrive(bar(B_G + (it & (kRing - 1))));
             if (loader && lane == 0) mbar_arrive(bar(B_G + (it & (kRing - 1))));
-            for (int k = p.n_tiles - 1; k >= 0; --k, ++it) {
+            for (int k = pc.k1 - 1; k >= pc.k0; --k, ++it) {
                 const int acc = it & 1, slot = it & (kRing - 1), nslot = (it + 1) & (kRing - 1);
                 const uint32_t aph = (it >> 1) & 1, gph = (it / kRing) & 1;
                 if (per_step || hi != cur_head) { cur_head = hi; ++mt; }
                 // prefetch the saved state of the next tile to the left while this one is being finished
-                if (loader && k > 0) hs_next = ch_ok ? ts_item[static_cast<int64_t>(k - 1) * p.d] : 0.f;
+                if (loader && k > pc.k0) hs_next = ch_ok ? ts_item[static_cast<int64_t>(k - 1) * p.d] : 0.f;
                 if (lane == 0) mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 15);
                 __syncwarp();
                 tc_fence_after_sync();
@@ -859,7 +968,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 // F: a time-invariant decay uses one Toeplitz table; the rightmost tile of the sequence stops at
                 // step L-1, where the adjoint entering from the right applies undamped
                 float F = rs[QT + m];
-                if (!per_step && k == p.n_tiles - 1) {
+                if (!per_step && k == p.n_tiles - 1) {   // (always the first tile of a piece that starts at the end)
                     const int lim = L - k * QT;  // valid rows in this tile
                     float f = 1.f;
                     for (int j = m + 1; j < lim; ++j) f *= a_m;
@@ -898,12 +1007,21 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         lam[c + 3] = fmaf(F, gv.w, lam[c + 3]);
                     }
                     if (m == 0) {
-                        if (k > 0) {  // row 0 of the adjoint is what the tile on the left receives
+                        if (k > pc.k0) {  // row 0 of the adjoint is what the tile on the left receives
                             float *gout = g_sm + nslot * DT + cb;
 #pragma unroll
                             for (int c = 0; c < 32; c += 4)
                                 *reinterpret_cast<float4 *>(gout + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
                             if (pass == 1) mbar_arrive(bar(B_G + nslot));
+                        } else if (publish) {   // the tile on the left is another CTA's
+                            float *co = carry_item + cb;
+#pragma unroll
+                            for (int c = 0; c < 32; c += 4)
+                                *reinterpret_cast<float4 *>(co + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
+                            if (pass == 1) {   // this half of the carry is complete
+                                __threadfence();
+                                atomicAdd(p.flags + pc.item, 1u);
+                            }
                         } else if (p.dinit_state) {
                             float *di = p.dinit_state + row * p.d + c0 + cb;
 #pragma unroll
@@ -928,7 +1046,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         *reinterpret_cast<uint4 *>(stg + sw128_offset(m, pass * 4 + j)) = qv;
                     }
                 }
-                if (loader && k > 0) {  // the saved state the tile on the left will need
+                if (loader && k > pc.k0) {  // the saved state the tile on the left will need
                     hs_sm[nslot * DT + m] = hs_next;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar(B_G + nslot));
@@ -1009,8 +1127,9 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             ++mt;
         };
         const float ident = conv ? 0.f : 1.f;  // raw value of an identity step
-        for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
-            const int64_t row = item / p.n_dtiles;
+        for (int pi = 0; pi < sched.n; ++pi) {
+            const Piece pc = sched.get<false>(pi);
+            const int64_t row = pc.item / p.n_dtiles;
             const int64_t bi = row / p.h, hi = row % p.h;
             const float *arow = p.decay + (per_step ? bi * p.a_sb + hi * p.a_sh : hi * p.a_sh);
             if (!per_step) {
@@ -1023,11 +1142,11 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             auto load_v = [&](int t) {
                 return (row_owner && t >= 0 && t < L) ? arow[static_cast<int64_t>(t) * p.a_sl] : ident;
             };
-            float v_next = load_v((p.n_tiles - 1) * QT + r);
-            float edge_next = ident;  // step n_tiles*128 is past the end
-            for (int k = p.n_tiles - 1; k >= 0; --k) {
+            float v_next = load_v((pc.k1 - 1) * QT + r);
+            float edge_next = load_v(pc.k1 * QT);  // past the end (identity) unless the item continues in another CTA
+            for (int k = pc.k1 - 1; k >= pc.k0; --k) {
                 const float v = v_next, edge = edge_next;
-                if (k > 0) {
+                if (k > pc.k0) {
                     v_next = load_v((k - 1) * QT + r);
                     edge_next = load_v(k * QT);
                 }
@@ -1124,6 +1243,50 @@ bool tc_tensor_ok(const void *base, int64_t d, int64_t sb, int64_t sl, int64_t s
     return encode_fn() != nullptr;
 }
 
+// Scratch of the split schedule: one arrival counter and 128 floats of carry per work item.
+static size_t sync_flag_bytes(int64_t n_items) { return static_cast<size_t>((n_items * 4 + 255) / 256 * 256); }
+size_t tc_sync_bytes(int64_t b, int64_t h, int64_t d) {
+    const int64_t n_items = b * h * ((d + tc::DT - 1) / tc::DT);
+    return sync_flag_bytes(n_items) + static_cast<size_t>(n_items) * tc::DT * sizeof(float);
+}
+static int g_split = -1;   // -1: not read yet; 0 / 1
+static bool split_enabled() {
+    if (g_split < 0) {
+        const char *e = getenv("EMA_B200_SPLIT");
+        g_split = (e && e[0] == '0') ? 0 : 1;
+    }
+    return g_split != 0;
+}
+int tc_set_split(int on) {
+    const int before = split_enabled() ? 1 : 0;
+    g_split = on ? 1 : 0;
+    return before;
+}
+// Decides the grid.  Whole items per CTA when they divide evenly (or when there is no scratch); otherwise one
+// CTA per SM, each with a contiguous range of tiles (tc::Sched).  Clears the arrival counters on the stream.
+static int plan_grid(const FusedParams &fp, int n_items, bool allow_split, cudaStream_t stream, int *grid, int *split,
+                     float **carry, unsigned **flags) {
+    const int sms = sm_count();
+    const int rounds = (n_items + sms - 1) / sms;
+    *grid = (n_items + rounds - 1) / rounds;
+    *split = 0;
+    *carry = nullptr;
+    *flags = nullptr;
+    // cutting pays when whole items would leave a noticeable share of the SM-rounds idle (256 items on 148 SMs: 13.5 %)
+    const bool uneven = static_cast<int64_t>(rounds) * sms * 92 > static_cast<int64_t>(n_items) * 100;
+    if (!allow_split || !split_enabled() || n_items < sms || !uneven || !fp.sync_ws ||
+        fp.sync_ws_bytes < tc_sync_bytes(fp.b, fp.h, fp.d))
+        return EMA_OK;
+    const size_t fb = sync_flag_bytes(n_items);
+    cudaError_t e = cudaMemsetAsync(fp.sync_ws, 0, fb, stream);
+    if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
+    *flags = static_cast<unsigned *>(fp.sync_ws);
+    *carry = reinterpret_cast<float *>(static_cast<uint8_t *>(fp.sync_ws) + fb);
+    *grid = sms;
+    *split = 1;
+    return EMA_OK;
+}
+
 int launch_fused_fwd_tc(const FusedParams &fp, cudaStream_t stream) {
     CUtensorMap tm_x, tm_y;
     int rc = make_tmap(&tm_x, fp.x, fp.b, fp.L, fp.h, fp.d, fp.x_sb, fp.x_sl, fp.x_sh);
@@ -1141,9 +1304,10 @@ int launch_fused_fwd_tc(const FusedParams &fp, cudaStream_t stream) {
     p.n_dtiles = static_cast<int>((fp.d + tc::DT - 1) / tc::DT);
     p.n_items = static_cast<int>(fp.b * fp.h * p.n_dtiles);
     p.n_chunks = fp.n_chunks;
-    const int sms = sm_count();
-    const int rounds = (p.n_items + sms - 1) / sms;
-    const int grid = (p.n_items + rounds - 1) / rounds;
+    int grid = 0;
+    // the sum of the log decays is accumulated per item by one CTA: no cutting when it is asked for
+    rc = plan_grid(fp, p.n_items, fp.log_decay_sum == nullptr, stream, &grid, &p.split, &p.carry, &p.flags);
+    if (rc) return rc;
     cudaError_t e = cudaFuncSetAttribute(tc::ema_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          tc::kFwdSmemBytes);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
@@ -1173,9 +1337,9 @@ int launch_fused_bwd_tc(const FusedParams &fp, cudaStream_t stream) {
     p.n_items = static_cast<int>(fp.b * fp.h * p.n_dtiles);
     p.n_dt64 = static_cast<int>((fp.d + 63) / 64);
     p.head_partial_offset = kHeadPartialOffset(fp.b * fp.h);
-    const int sms = sm_count();
-    const int rounds = (p.n_items + sms - 1) / sms;
-    const int grid = (p.n_items + rounds - 1) / rounds;
+    int grid = 0;
+    rc = plan_grid(fp, p.n_items, true, stream, &grid, &p.split, &p.carry, &p.flags);
+    if (rc) return rc;
     cudaError_t e = cudaFuncSetAttribute(tc::ema_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          tc::kBwdSmemBytes);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }

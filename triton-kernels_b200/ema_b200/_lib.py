@@ -54,10 +54,12 @@ def lib():
         "ema_b200_device_status": (ci, [ci]),
         "ema_b200_set_path": (ci, [ci]),
         "ema_b200_last_path": (ci, []),
+        "ema_b200_set_split": (ci, [ci]),
         "ema_b200_tile_steps": (ci, [pp]),
         "ema_b200_tile_states_bytes": (sz, [pp]),
         "ema_b200_bwd_workspace_bytes": (sz, [pp]),
-        "ema_b200_fwd": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp]),
+        "ema_b200_fwd_workspace_bytes": (sz, [pp]),
+        "ema_b200_fwd": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp, sz, vp]),
         "ema_b200_bwd": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp, sz, vp]),
         "ema_b200_static_scratch_limit": (sz, []),
         "ema_b200_bwd_static_scratch": (ci, [pp, vp, vp, vp, vp, vp, vp, vp]),

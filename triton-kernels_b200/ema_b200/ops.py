@@ -60,12 +60,14 @@ def n_tiles_of(x, decay, convention=CONV_NORTH_STAR):
 
 def ema_fwd(x, decay, *, chunk=0, prescaled_log=False, init_state=None, want_chunk_states=False,
             want_tile_states=False, want_final=False, want_log_decay_sum=False, stop_below=0.0,
-            out=None, tile_states=None):
+            out=None, tile_states=None, workspace=None):
     """Forward scan.  Returns a dict with 'y' and the requested extras.
 
     x[b,L,h,d] (fp32|bf16, last dim contiguous), decay a[b,L,h] or a[h] (fp32).
     prescaled_log=True selects the reference's (A_ema, X_ema) convention: decay = log a, x = (1-a) x.
     `out` / `tile_states` let a caller re-scan a prefix in place (sequence-parallel fix-up).
+    `workspace` (returned as 'fwd_workspace') is the small scratch that lets the kernels spread uneven work
+    over all SMs; pass it back in to avoid the allocation, never to two calls that may overlap.
     """
     x, decay = _check_inputs(x, decay)
     dev = require_cuda(x, decay, init_state, out, tile_states)
@@ -96,9 +98,14 @@ def ema_fwd(x, decay, *, chunk=0, prescaled_log=False, init_state=None, want_chu
         if tuple(init_state.shape) != (b, h, d) or init_state.dtype != torch.float32:
             raise ValueError("init_state must be fp32 [b, h, d]")
         init_state = init_state.contiguous()
+    ws_bytes = L_.ema_b200_fwd_workspace_bytes(ctypes.byref(p))
+    if workspace is None and ws_bytes > 0:
+        workspace = torch.empty(((ws_bytes + 3) // 4,), dtype=torch.float32, device=dev)
+    res["fwd_workspace"] = workspace
     with torch.cuda.device(dev):
         rc = L_.ema_b200_fwd(ctypes.byref(p), ptr(x), ptr(decay), ptr(y), ptr(cs), ptr(ts), ptr(init_state),
-                             ptr(fin), ptr(lds), ctypes.c_float(stop_below), stream_ptr(dev))
+                             ptr(fin), ptr(lds), ctypes.c_float(stop_below), ptr(workspace),
+                             ctypes.c_size_t(0 if workspace is None else workspace.numel() * 4), stream_ptr(dev))
     check("ema_b200_fwd", rc)
     return res
 
