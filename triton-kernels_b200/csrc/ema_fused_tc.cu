@@ -1262,6 +1262,17 @@ int tc_set_split(int on) {
     g_split = on ? 1 : 0;
     return before;
 }
+// SMs the split schedule leaves free for small kernels of other streams (a collective that overlaps the scan):
+// a thread block that has to wait for such a kernel to leave its SM would finish late by that kernel's run time
+// and hold the whole grid back.
+static int spare_sms() {
+    static const int n = [] {
+        const char *e = getenv("EMA_B200_SPARE_SMS");
+        const int v = e ? atoi(e) : 2;
+        return v < 0 ? 0 : (v > 16 ? 16 : v);
+    }();
+    return n;
+}
 // Decides the grid.  Whole items per CTA when they divide evenly (or when there is no scratch); otherwise one
 // CTA per SM, each with a contiguous range of tiles (tc::Sched).  Clears the arrival counters on the stream.
 static int plan_grid(const FusedParams &fp, int n_items, bool allow_split, cudaStream_t stream, int *grid, int *split,
@@ -1282,7 +1293,7 @@ static int plan_grid(const FusedParams &fp, int n_items, bool allow_split, cudaS
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     *flags = static_cast<unsigned *>(fp.sync_ws);
     *carry = reinterpret_cast<float *>(static_cast<uint8_t *>(fp.sync_ws) + fb);
-    *grid = sms;
+    *grid = sms - spare_sms();
     *split = 1;
     return EMA_OK;
 }
