@@ -179,3 +179,32 @@ def test_items_cut_across_thread_blocks_give_identical_results(shape, per_head, 
     assert_close_bf16(f["y"], y_ref, "y")
     assert_close_bf16(g["dx"], dx_ref, "dx")
     assert_close_bf16(g["ddecay"], da_ref, "da")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_decays_from_zero_to_one(dtype, _lib):
+    """Per-step decays over the whole range, exact 0 and exact 1 included: the log-domain matrices of the tensor-core
+    kernels and the plain recurrence of the CUDA-core kernels must both stay finite and agree with the oracle."""
+    E = _E()
+    b, L, h, d = 2, 700, 2, 128
+    x, a, dy, _ = make_inputs(31, b, L, h, d, lo=-20.0, hi=12.0, per_head=False, dtype=dtype)
+    g = torch.Generator().manual_seed(5)
+    pick = torch.randint(0, 12, a.shape, generator=g).cuda()
+    special = torch.tensor([0.0, 1e-30, 1e-6, 1.0], device="cuda")
+    a = torch.where(pick < 4, special[pick.clamp(max=3)], a).contiguous()
+    np_in = (x.float().cpu().numpy(), a.cpu().numpy(), dy.float().cpu().numpy())
+    f = E.ops.ema_fwd(x, a, want_tile_states=True)
+    r = E.ops.ema_bwd(x, a, dy, f["tile_states"])
+    torch.cuda.synchronize()
+    assert _lib.ema_b200_last_path() == (1 if dtype == torch.bfloat16 else 0)
+    y_ref, dx_ref, da_ref = oracle_fwd_bwd(np_in)
+    for got in (f["y"], r["dx"], r["ddecay"]):
+        assert bool(torch.isfinite(got.float()).all())
+    if dtype == torch.bfloat16:
+        assert_close_bf16(f["y"], y_ref, "y")
+        assert_close_bf16(r["dx"], dx_ref, "dx")
+        assert_close_bf16(r["ddecay"], da_ref, "da")
+    else:
+        assert np.abs(f["y"].cpu().numpy() - y_ref).max() <= 1e-4
+        assert np.abs(r["dx"].cpu().numpy() - dx_ref).max() <= 1e-4
+        assert np.abs(r["ddecay"].cpu().numpy() - da_ref).max() <= 1e-4 + 2e-5 * np.abs(da_ref).max()

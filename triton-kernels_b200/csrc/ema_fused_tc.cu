@@ -161,8 +161,11 @@ __device__ __forceinline__ void compute_off(const OffGeom &g, const uint8_t *cs_
         const float cb = ld_f32(cs_b, UPPER ? g.c[s] - 4u : g.c[s] + 28u);   // cs[8c - 1] | cs[8c + 7]
         const float sc = ex2_approx(UPPER ? cb - ca : ca - cb);     // <= 0 either way
         const float4 w0 = ld_f32x4(tab_b, g.c[s]), w1 = ld_f32x4(tab_b, g.c[s] + 16);
-        out.v[s] = make_uint4(pack_bf16x2(w0.x * sc, w0.y * sc), pack_bf16x2(w0.z * sc, w0.w * sc),
-                              pack_bf16x2(w1.x * sc, w1.y * sc), pack_bf16x2(w1.z * sc, w1.w * sc));
+        const float2 sc2 = make_float2(sc, sc);
+        const float2 v0 = __fmul2_rn(make_float2(w0.x, w0.y), sc2), v1 = __fmul2_rn(make_float2(w0.z, w0.w), sc2),
+                     v2 = __fmul2_rn(make_float2(w1.x, w1.y), sc2), v3 = __fmul2_rn(make_float2(w1.z, w1.w), sc2);
+        out.v[s] = make_uint4(pack_bf16x2(v0.x, v0.y), pack_bf16x2(v1.x, v1.y), pack_bf16x2(v2.x, v2.y),
+                              pack_bf16x2(v3.x, v3.y));
     }
 }
 // diagonal half chunks: one ex2 per element; `diag` is the value on the diagonal itself (SHIFT = 1 only)
@@ -397,7 +400,8 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 
     const Sched sched(p.n_items, p.n_tiles, p.split != 0);
     // log2 of the multiplicative decay of one step
-    auto log2_decay = [&](float v) { return conv ? v * 1.4426950408889634f : log2f(v); };
+    // (clamped: a decay of exactly 0 would make the prefix sums -inf and their differences NaN; 2^-30000 is 0 anyway)
+    auto log2_decay = [&](float v) { return fmaxf(conv ? v * 1.4426950408889634f : log2f(v), -30000.f); };
 
     if (warp < 4) {
         reg_dec<kRegsLight>();
@@ -550,13 +554,13 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + acc));  // one arrival per warp
                     }
                     const int cb = half * 64 + pass * 32;
+                    const float2 E2 = make_float2(E, E);   // two columns per instruction (packed fp32 FMA)
 #pragma unroll
                     for (int c = 0; c < 32; c += 4) {
                         const float4 hv = *reinterpret_cast<const float4 *>(hin + cb + c);
-                        y[c] = fmaf(E, hv.x, y[c]);
-                        y[c + 1] = fmaf(E, hv.y, y[c + 1]);
-                        y[c + 2] = fmaf(E, hv.z, y[c + 2]);
-                        y[c + 3] = fmaf(E, hv.w, y[c + 3]);
+                        const float2 lo = __ffma2_rn(E2, make_float2(hv.x, hv.y), make_float2(y[c], y[c + 1]));
+                        const float2 hi2 = __ffma2_rn(E2, make_float2(hv.z, hv.w), make_float2(y[c + 2], y[c + 3]));
+                        y[c] = lo.x; y[c + 1] = lo.y; y[c + 2] = hi2.x; y[c + 3] = hi2.y;
                     }
                     if (m == QT - 1 && k + 1 < pc.k1) {  // the last row is the state entering the next tile
                         float *hout = h_sm + ((it + 1) & (kRing - 1)) * DT + cb;
@@ -811,7 +815,8 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
 
     const Sched sched(p.n_items, p.n_tiles, p.split != 0);
-    auto log2_decay = [&](float v) { return conv ? v * 1.4426950408889634f : log2f(v); };
+    // (clamped: a decay of exactly 0 would make the prefix sums -inf and their differences NaN; 2^-30000 is 0 anyway)
+    auto log2_decay = [&](float v) { return fmaxf(conv ? v * 1.4426950408889634f : log2f(v), -30000.f); };
 
     if (warp < 4) {
         reg_dec<kRegsLight>();
@@ -977,7 +982,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 if (lane == 0) mbar_wait(bar(B_G + slot), gph, abort_flag, 16);
                 __syncwarp();
                 const int t = k * QT + m;
-                float dacc = 0.f;
+                float2 dacc2 = make_float2(0.f, 0.f);   // even / odd columns
                 // dx staging: this half's 64-channel block, free once the store of the previous tile has read it
                 uint8_t *stg = smem + BwdSmem::ostage + half * kBlockBytes;
                 if (lane == 0) mbar_wait(bar(B_STG_EMPTY + half), (it & 1) ^ 1, abort_flag, 17);
@@ -998,13 +1003,13 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     }
                     const float *hin = hs_sm + slot * DT + cb;
                     const float *gin = g_sm + slot * DT + cb;
+                    const float2 F2 = make_float2(F, F);   // two columns per instruction (packed fp32 math) throughout
 #pragma unroll
                     for (int c = 0; c < 32; c += 4) {
                         const float4 gv = *reinterpret_cast<const float4 *>(gin + c);
-                        lam[c] = fmaf(F, gv.x, lam[c]);
-                        lam[c + 1] = fmaf(F, gv.y, lam[c + 1]);
-                        lam[c + 2] = fmaf(F, gv.z, lam[c + 2]);
-                        lam[c + 3] = fmaf(F, gv.w, lam[c + 3]);
+                        const float2 lo = __ffma2_rn(F2, make_float2(gv.x, gv.y), make_float2(lam[c], lam[c + 1]));
+                        const float2 hi2 = __ffma2_rn(F2, make_float2(gv.z, gv.w), make_float2(lam[c + 2], lam[c + 3]));
+                        lam[c] = lo.x; lam[c + 1] = lo.y; lam[c + 2] = hi2.x; lam[c + 3] = hi2.y;
                     }
                     if (m == 0) {
                         if (k > pc.k0) {  // row 0 of the adjoint is what the tile on the left receives
@@ -1029,20 +1034,23 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                                 if (c0 + cb + c < p.d) di[c] = a_m * lam[c];
                         }
                     }
+                    const float2 Ep2 = make_float2(Eprev, Eprev), p2 = make_float2(p_m, p_m);
 #pragma unroll
                     for (int c = 0; c < 32; c += 4) {
                         const float4 hv = *reinterpret_cast<const float4 *>(hin + c);
-                        dacc = fmaf(lam[c], fmaf(Eprev, hv.x, z[c]), dacc);
-                        dacc = fmaf(lam[c + 1], fmaf(Eprev, hv.y, z[c + 1]), dacc);
-                        dacc = fmaf(lam[c + 2], fmaf(Eprev, hv.z, z[c + 2]), dacc);
-                        dacc = fmaf(lam[c + 3], fmaf(Eprev, hv.w, z[c + 3]), dacc);
+                        const float2 z0 = __ffma2_rn(Ep2, make_float2(hv.x, hv.y), make_float2(z[c], z[c + 1]));
+                        const float2 z1 = __ffma2_rn(Ep2, make_float2(hv.z, hv.w), make_float2(z[c + 2], z[c + 3]));
+                        dacc2 = __ffma2_rn(make_float2(lam[c], lam[c + 1]), z0, dacc2);
+                        dacc2 = __ffma2_rn(make_float2(lam[c + 2], lam[c + 3]), z1, dacc2);
                     }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const uint4 qv = make_uint4(pack_bf16x2(p_m * lam[8 * j], p_m * lam[8 * j + 1]),
-                                                    pack_bf16x2(p_m * lam[8 * j + 2], p_m * lam[8 * j + 3]),
-                                                    pack_bf16x2(p_m * lam[8 * j + 4], p_m * lam[8 * j + 5]),
-                                                    pack_bf16x2(p_m * lam[8 * j + 6], p_m * lam[8 * j + 7]));
+                        const float2 d0 = __fmul2_rn(p2, make_float2(lam[8 * j], lam[8 * j + 1]));
+                        const float2 d1 = __fmul2_rn(p2, make_float2(lam[8 * j + 2], lam[8 * j + 3]));
+                        const float2 d2 = __fmul2_rn(p2, make_float2(lam[8 * j + 4], lam[8 * j + 5]));
+                        const float2 d3 = __fmul2_rn(p2, make_float2(lam[8 * j + 6], lam[8 * j + 7]));
+                        const uint4 qv = make_uint4(pack_bf16x2(d0.x, d0.y), pack_bf16x2(d1.x, d1.y),
+                                                    pack_bf16x2(d2.x, d2.y), pack_bf16x2(d3.x, d3.y));
                         *reinterpret_cast<uint4 *>(stg + sw128_offset(m, pass * 4 + j)) = qv;
                     }
                 }
@@ -1051,6 +1059,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar(B_G + nslot));
                 }
+                float dacc = dacc2.x + dacc2.y;
                 if (conv) dacc *= a_m;
                 if (t >= L) dacc = 0.f;
                 if (per_step) {
