@@ -152,7 +152,8 @@ __device__ __forceinline__ float4 ld_f32x4(const uint8_t *base, uint32_t off) {
 }
 
 // off-diagonal chunks: row scalar x column table
-template <bool UPPER>
+// (PACKED: two products per instruction; measured faster in the backward kernel, slower in the forward one)
+template <bool UPPER, bool PACKED>
 __device__ __forceinline__ void compute_off(const OffGeom &g, const uint8_t *cs_b, const uint8_t *tab_b, RowChunks &out) {
 #pragma unroll
     for (int s = 0; s < kOffSlots; ++s) {
@@ -161,11 +162,16 @@ __device__ __forceinline__ void compute_off(const OffGeom &g, const uint8_t *cs_
         const float cb = ld_f32(cs_b, UPPER ? g.c[s] - 4u : g.c[s] + 28u);   // cs[8c - 1] | cs[8c + 7]
         const float sc = ex2_approx(UPPER ? cb - ca : ca - cb);     // <= 0 either way
         const float4 w0 = ld_f32x4(tab_b, g.c[s]), w1 = ld_f32x4(tab_b, g.c[s] + 16);
-        const float2 sc2 = make_float2(sc, sc);
-        const float2 v0 = __fmul2_rn(make_float2(w0.x, w0.y), sc2), v1 = __fmul2_rn(make_float2(w0.z, w0.w), sc2),
-                     v2 = __fmul2_rn(make_float2(w1.x, w1.y), sc2), v3 = __fmul2_rn(make_float2(w1.z, w1.w), sc2);
-        out.v[s] = make_uint4(pack_bf16x2(v0.x, v0.y), pack_bf16x2(v1.x, v1.y), pack_bf16x2(v2.x, v2.y),
-                              pack_bf16x2(v3.x, v3.y));
+        if constexpr (PACKED) {
+            const float2 sc2 = make_float2(sc, sc);
+            const float2 v0 = __fmul2_rn(make_float2(w0.x, w0.y), sc2), v1 = __fmul2_rn(make_float2(w0.z, w0.w), sc2),
+                         v2 = __fmul2_rn(make_float2(w1.x, w1.y), sc2), v3 = __fmul2_rn(make_float2(w1.z, w1.w), sc2);
+            out.v[s] = make_uint4(pack_bf16x2(v0.x, v0.y), pack_bf16x2(v1.x, v1.y), pack_bf16x2(v2.x, v2.y),
+                                  pack_bf16x2(v3.x, v3.y));
+        } else {
+            out.v[s] = make_uint4(pack_bf16x2(w0.x * sc, w0.y * sc), pack_bf16x2(w0.z * sc, w0.w * sc),
+                                  pack_bf16x2(w1.x * sc, w1.y * sc), pack_bf16x2(w1.z * sc, w1.w * sc));
+        }
     }
 }
 // diagonal half chunks: one ex2 per element; `diag` is the value on the diagonal itself (SHIFT = 1 only)
@@ -554,13 +560,13 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         if (lane == 0) mbar_arrive(bar(B_ACC_EMPTY + acc));  // one arrival per warp
                     }
                     const int cb = half * 64 + pass * 32;
-                    const float2 E2 = make_float2(E, E);   // two columns per instruction (packed fp32 FMA)
 #pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
+                    for (int c = 0; c < 32; c += 4) {   // (packed fp32 FMAs were measured slower here)
                         const float4 hv = *reinterpret_cast<const float4 *>(hin + cb + c);
-                        const float2 lo = __ffma2_rn(E2, make_float2(hv.x, hv.y), make_float2(y[c], y[c + 1]));
-                        const float2 hi2 = __ffma2_rn(E2, make_float2(hv.z, hv.w), make_float2(y[c + 2], y[c + 3]));
-                        y[c] = lo.x; y[c + 1] = lo.y; y[c + 2] = hi2.x; y[c + 3] = hi2.y;
+                        y[c] = fmaf(E, hv.x, y[c]);
+                        y[c + 1] = fmaf(E, hv.y, y[c + 1]);
+                        y[c + 2] = fmaf(E, hv.z, y[c + 2]);
+                        y[c + 3] = fmaf(E, hv.w, y[c + 3]);
                     }
                     if (m == QT - 1 && k + 1 < pc.k1) {  // the last row is the state entering the next tile
                         float *hout = h_sm + ((it + 1) & (kRing - 1)) * DT + cb;
@@ -633,7 +639,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             bar_sync(2, kBuildThreads);
             RowChunks g;
             compute_diag_lower<0>(dgm, cs_b, p_b, 0.f, g);
-            compute_off<false>(og, cs_b, wlo_b, g);
+            compute_off<false, false>(og, cs_b, wlo_b, g);
             const float E = ex2_approx(cs_sm[r]);
             if (lane == 0) mbar_wait(bar(B_MAT_EMPTY + mb), ((mt / kFwdMatBufs) & 1) ^ 1, abort_flag, 8);
             __syncwarp();
@@ -1114,9 +1120,9 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             bar_sync(2, kBuildThreads);
             RowChunks ca, cu;
             compute_diag_lower<1>(dga, cs_b, p_b, diag, ca);
-            compute_off<false>(oga, cs_b, wlo_b, ca);
+            compute_off<false, true>(oga, cs_b, wlo_b, ca);
             compute_diag_upper(dgu, cs_b, cu);
-            compute_off<true>(ogu, cs_b, rup_b, cu);
+            compute_off<true, true>(ogu, cs_b, rup_b, cu);
             const float cs_r = cs_sm[r];
             const float Eprev = ex2_approx(cs_r - l2);                       // prod_{j<r} a_j
             const float Fr = ex2_approx(cs_sm[QT - 1] - cs_r + log2_decay(v_edge));
