@@ -32,7 +32,8 @@ from golden_inputs import gen_inputs  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("EMA_REFERENCE_CHECKOUT"), required=os.environ.get("EMA_REFERENCE_CHECKOUT") is None,
+                    help="path of a checkout of the reference project (kartiksrinivas007/triton-kernels)")
     ap.add_argument("--out", default=os.path.dirname(os.path.abspath(__file__)))
     args = ap.parse_args()
 
