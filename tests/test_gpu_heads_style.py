@@ -7,7 +7,7 @@ import torch.nn.functional as F
 from helpers import BF16_REL, FP32_ATOL
 
 
-def _loop(x, dt, A, B, C, D, z, dt_bias, init, softplus, limit):
+def _loop(x, dt, A, B, C, D, z, dt_bias, init, softplus, limit, seq_idx=None):
     """fp64 sequential definition (the recurrence of the reference's chunked kernels, ema_combined.py:12-66)."""
     b, L, h, p = x.shape
     rep = h // B.shape[2]
@@ -20,6 +20,8 @@ def _loop(x, dt, A, B, C, D, z, dt_bias, init, softplus, limit):
     s = torch.zeros((b, h, p), dtype=x.dtype) if init is None else init[..., 0]
     ys = []
     for t in range(L):
+        if seq_idx is not None and t > 0:   # a new sequence starts from a zero state
+            s = s * (seq_idx[:, t] == seq_idx[:, t - 1]).to(s.dtype).view(b, 1, 1)
         s = torch.exp(d[:, t] * A).unsqueeze(-1) * s + (d[:, t] * Bh[:, t]).unsqueeze(-1) * x[:, t]
         ys.append(Ch[:, t].unsqueeze(-1) * s)
     y = torch.stack(ys, dim=1)
@@ -79,6 +81,33 @@ def test_heads_style_matches_sequential_loop(dtype, full, ema_lib):
         close(dev[k].grad, leaves[k].grad, f"d{k}")
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_sequence_ids_restart_the_state(dtype, ema_lib):
+    from kernels.ema_combined import ema_chunk_scan_combined
+    b, L, h, p, g = 2, 300, 2, 64, 1
+    t = _make(8, b, L, h, p, g, dtype, False)
+    seq_idx = torch.zeros(b, L, dtype=torch.int32)
+    seq_idx[0, 100:] = 1
+    seq_idx[0, 128:] = 2          # a restart exactly on a tile boundary
+    seq_idx[1, 257:] = 5
+    leaves = {k: v.double().requires_grad_(True) for k, v in t.items()}
+    y_ref, fin_ref = _loop(leaves["x"], leaves["dt"], leaves["A"], leaves["B"], leaves["C"], None, None, None, None,
+                           False, (0.0, float("inf")), seq_idx=seq_idx)
+    dy = torch.randn(y_ref.shape, generator=torch.Generator().manual_seed(3)).to(dtype).float()
+    (y_ref * dy.double()).sum().backward()
+    dev = {k: (v.to(dtype) if k == "x" else v).cuda().requires_grad_(True) for k, v in t.items()}
+    out, fin = ema_chunk_scan_combined(dev["x"], dev["dt"], dev["A"], dev["B"], dev["C"], 64, seq_idx=seq_idx.cuda(),
+                                       return_final_states=True)
+    (out.float() * dy.cuda()).sum().backward()
+    tol = BF16_REL if dtype == torch.bfloat16 else 1e-4
+    for got, ref, what in ((out, y_ref, "out"), (fin, fin_ref, "final"), (dev["x"].grad, leaves["x"].grad, "dx"),
+                           (dev["dt"].grad, leaves["dt"].grad, "ddt"), (dev["B"].grad, leaves["B"].grad, "dB")):
+        got, ref = got.detach().float().cpu(), ref.detach().float()
+        assert bool(torch.isfinite(got).all()), what
+        assert float((got - ref).abs().max()) <= tol * max(float(ref.abs().max()), 1.0), what
+
+
 def test_rejects_what_is_not_the_ema_case():
     from kernels.ema_combined import ema_chunk_scan_combined
     x, dt, A = torch.zeros(1, 8, 2, 4), torch.zeros(1, 8, 2), -torch.ones(2)
@@ -87,6 +116,6 @@ def test_rejects_what_is_not_the_ema_case():
         ema_chunk_scan_combined(x, dt, A, B2, B2, 4)                       # state size 2
     B1 = torch.zeros(1, 8, 1, 1)
     with pytest.raises(NotImplementedError):
-        ema_chunk_scan_combined(x, dt, A, B1, B1, 4, seq_idx=torch.zeros(1, 8, dtype=torch.int32))
+        ema_chunk_scan_combined(x, dt, A, B1, B1, 4, cu_seqlens=torch.tensor([0, 8]), return_varlen_states=True)
     with pytest.raises(AssertionError):
         ema_chunk_scan_combined(x, dt[:, :4], A, B1, B1, 4)               # dt of the wrong length

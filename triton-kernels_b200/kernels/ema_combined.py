@@ -11,8 +11,9 @@ weight, C = 1, kernels/benchmarks/ema_bench.py:104-117):
 The recurrence runs in the fused scan kernels (pre-scaled log-decay convention: decay = dt' A, input =
 dt' B x); what surrounds it is elementwise torch, so gradients reach every tensor argument through autograd.
 The reference's own backward for this entry point is a stub that returns None for every input (:89-92).
-State sizes above 1, seq_idx and cu_seqlens are rejected: they belong to the general state-space scan, not to
-the EMA path.
+`seq_idx` (a sequence id per position: the state restarts from zero where the id changes, as in the reference's
+chunked kernels) is a decay of exactly 0 at the first step of every new sequence.  State sizes above 1 and
+cu_seqlens (variable-length final states) are rejected: they belong to the general state-space scan.
 """
 import torch
 import torch.nn.functional as F
@@ -64,13 +65,19 @@ def _ema_chunk_scan_combined_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, dt_
         assert D.shape == (nheads, headdim) or D.shape == (nheads,)
     if dstate != 1:
         raise NotImplementedError("only the EMA special case (state size 1) is built on this path")
-    if seq_idx is not None or cu_seqlens is not None:
-        raise NotImplementedError("seq_idx / cu_seqlens (variable-length resets) are not part of the EMA path")
+    if cu_seqlens is not None:
+        raise NotImplementedError("cu_seqlens (variable-length final states) is not part of the EMA path")
+    if seq_idx is not None:
+        assert seq_idx.shape == (batch, seqlen)
     if initial_states is not None:
         assert initial_states.shape == (batch, nheads, headdim, dstate)
     rep = nheads // ngroups
     dtp = _processed_dt(dt, dt_bias, dt_softplus, dt_limit)                     # [b, l, h] fp32
     a_log = dtp * A.float()                                                      # log decay per step
+    if seq_idx is not None:   # a new sequence starts from a zero state: log decay -inf, i.e. decay 0, at its first step
+        new_seq = torch.zeros_like(seq_idx, dtype=torch.bool)
+        new_seq[:, 1:] = seq_idx[:, 1:] != seq_idx[:, :-1]
+        a_log = a_log.masked_fill(new_seq.unsqueeze(-1), float("-inf"))
     Bh = B[..., 0].float().repeat_interleave(rep, dim=2)                         # [b, l, h]
     Ch = C[..., 0].float().repeat_interleave(rep, dim=2)
     u = (x.float() * (dtp * Bh).unsqueeze(-1)).to(x.dtype)
