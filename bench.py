@@ -184,6 +184,8 @@ def run_gpu(args):
 
     import ema_b200
     from ema_b200 import ops
+    # one process per GPU: keep the process (and the pinned buffers of the end-to-end leg) on the GPU's NUMA node
+    numa_node = ema_b200.bind_to_gpu_numa_node(dev)
 
     if world > 1:
         # Every step ends with a small collective that overlaps the next step's kernels.  Keep whole work items per
@@ -360,7 +362,7 @@ def run_gpu(args):
                "h2d_bytes_per_step": 2 * nbytes + 4 * a.numel(), "d2h_bytes_per_step": 2 * nbytes + 4 * a.numel(),
                "api": "ema_b200.HostPipeline.run: pinned host x, dy, a -> y, dx, da; 8 batch slices, "
                       "H2D / kernels / D2H on three streams",
-               "gpu_launches_per_step": pipe.n_launches}
+               "gpu_launches_per_step": pipe.n_launches, "numa_node": numa_node}
         del hx, hdy, hy, hdx, pipe
     except RuntimeError as exc:  # e.g. pinned allocation refused
         e2e = {"value": None, "unit": UNIT, "error": str(exc)[:200]}

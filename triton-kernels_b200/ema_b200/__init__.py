@@ -16,4 +16,4 @@ package `kernels`.
 from ._lib import EmaB200Error, lib, lib_path  # noqa: F401
 from .ops import (ema, ema_fwd, ema_bwd, ema_scan_folded_fwd, ema_scan_folded_bwd,  # noqa: F401
                   EmaFunction)
-from .host import HostPipeline, ema_fwd_bwd_host  # noqa: F401
+from .host import HostPipeline, bind_to_gpu_numa_node, ema_fwd_bwd_host  # noqa: F401

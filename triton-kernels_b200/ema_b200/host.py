@@ -20,6 +20,35 @@ from . import ops
 from ._lib import lib
 
 
+def bind_to_gpu_numa_node(device=None):
+    """Restricts the calling process to the CPUs of the NUMA node the GPU hangs off, so that pinned host buffers
+    allocated afterwards are local to the GPU's PCIe root.  On a two-socket host with one process per GPU this keeps the
+    copies of half of the GPUs off the inter-socket link.  Returns the node number, or None when the platform does not
+    tell (no sysfs entry, node -1, not Linux): then nothing is changed.  Call it before allocating pinned memory."""
+    import os
+    try:
+        dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        props = torch.cuda.get_device_properties(dev)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            spec = f.read().strip()
+        cpus = set()
+        for part in spec.split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        return None
+
+
 class HostPipeline:
     def __init__(self, shape, dtype, per_head, device="cuda", slices=8, depth=3, prescaled_log=False):
         b, L, h, d = shape
