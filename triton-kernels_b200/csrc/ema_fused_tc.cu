@@ -407,7 +407,8 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     const Sched sched(p.n_items, p.n_tiles, p.split != 0);
     // log2 of the multiplicative decay of one step
     // (clamped: a decay of exactly 0 would make the prefix sums -inf and their differences NaN; 2^-30000 is 0 anyway)
-    auto log2_decay = [&](float v) { return fmaxf(conv ? v * 1.4426950408889634f : log2f(v), -30000.f); };
+    // lg2.approx (absolute error 2^-22): the decays end up in bf16 matrix elements and in carry factors over 128 steps
+    auto log2_decay = [&](float v) { return fmaxf(conv ? v * 1.4426950408889634f : __log2f(v), -30000.f); };
 
     if (warp < 4) {
         reg_dec<kRegsLight>();
@@ -822,7 +823,8 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 
     const Sched sched(p.n_items, p.n_tiles, p.split != 0);
     // (clamped: a decay of exactly 0 would make the prefix sums -inf and their differences NaN; 2^-30000 is 0 anyway)
-    auto log2_decay = [&](float v) { return fmaxf(conv ? v * 1.4426950408889634f : log2f(v), -30000.f); };
+    // lg2.approx (absolute error 2^-22): the decays end up in bf16 matrix elements and in carry factors over 128 steps
+    auto log2_decay = [&](float v) { return fmaxf(conv ? v * 1.4426950408889634f : __log2f(v), -30000.f); };
 
     if (warp < 4) {
         reg_dec<kRegsLight>();
