@@ -208,3 +208,33 @@ def test_decays_from_zero_to_one(dtype, _lib):
         assert np.abs(f["y"].cpu().numpy() - y_ref).max() <= 1e-4
         assert np.abs(r["dx"].cpu().numpy() - dx_ref).max() <= 1e-4
         assert np.abs(r["ddecay"].cpu().numpy() - da_ref).max() <= 1e-4 + 2e-5 * np.abs(da_ref).max()
+
+
+def test_calls_can_be_captured_in_cuda_graphs(_lib):
+    """With caller-provided buffers a forward and a backward call only queue stream work (kernels and two small
+    memsets), so they capture into CUDA graphs; a replay must reproduce the eager results bit for bit."""
+    E = _E()
+    b, L, h, d = 10, 640, 2, 1024   # enough items for the tile-range schedule, whose counters a memset node clears
+    x, a, dy, _ = make_inputs(91, b, L, h, d, per_head=True, dtype=torch.bfloat16)
+    y, dx, da = torch.empty_like(x), torch.empty_like(x), torch.empty_like(a)
+    f = E.ops.ema_fwd(x, a, out=y, want_tile_states=True)
+    ts, fws = f["tile_states"], f["fwd_workspace"]
+    ws = E.ops.ema_bwd(x, a, dy, ts, dx=dx, ddecay=da)["workspace"]
+    torch.cuda.synchronize()
+    ref = (y.clone(), dx.clone(), da.clone())
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):   # warm-up on a side stream, as graph capture wants
+        E.ops.ema_fwd(x, a, out=y, tile_states=ts, workspace=fws)
+        E.ops.ema_bwd(x, a, dy, ts, dx=dx, ddecay=da, workspace=ws)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        E.ops.ema_fwd(x, a, out=y, tile_states=ts, workspace=fws)
+        E.ops.ema_bwd(x, a, dy, ts, dx=dx, ddecay=da, workspace=ws)
+    for _ in range(2):
+        y.zero_(); dx.zero_(); da.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y, ref[0]) and torch.equal(dx, ref[1]) and torch.equal(da, ref[2])
+    assert _lib.ema_b200_device_status(0) == 0
