@@ -10,7 +10,9 @@ the copies.  Device memory holds `depth` slices of each tensor, whatever the bat
     pipe.run(x_host, a_host, dy_host, y_host, dx_host, da_host)      # host tensors, ideally pinned
 
 `run` orders everything after the caller's current stream and, unless told otherwise, returns once the last
-copy has landed in the output tensors.
+copy has landed in the output tensors.  With sync=False it only queues the work: consecutive runs then overlap (the
+next run's first copies travel while the previous run's last results are still on their way back), and `wait()`
+makes the caller's stream wait for everything queued so far.
 """
 import ctypes
 
@@ -72,7 +74,12 @@ class HostPipeline:
                             convention=ops.CONV_PRESCALED_LOG if prescaled_log else ops.CONV_NORTH_STAR)
         ws_floats = (lib().ema_b200_bwd_workspace_bytes(ctypes.byref(prob)) + 3) // 4
         self.workspace = [torch.empty((ws_floats,), dtype=torch.float32, device=dev) for _ in range(depth)]
-        self.a = torch.empty((h,) if per_head else (b, L, h), dtype=torch.float32, device=dev)
+        # the decay lives in two device buffers used by alternate runs, so that a run's copy of it need not wait for
+        # the kernels of the run before
+        self.a2 = [torch.empty((h,) if per_head else (b, L, h), dtype=torch.float32, device=dev) for _ in range(2)]
+        self.a = self.a2[0]
+        self.ev_a_free = [torch.cuda.Event() for _ in range(2)]
+        self.n_runs = 0
         # per-head decay: one partial gradient per slice, summed in slice order at the end (deterministic)
         self.da = torch.empty((slices, h) if per_head else (b, L, h), dtype=torch.float32, device=dev)
         self.da_sum = torch.empty((h,), dtype=torch.float32, device=dev) if per_head else None
@@ -84,8 +91,8 @@ class HostPipeline:
     def run(self, x, a, dy, y, dx, da, sync=True):
         """x, dy -> y, dx (host tensors shaped like the problem); a -> da (host, fp32).
 
-        With sync=False the call only queues the work; the caller's current stream waits for it, and the outputs
-        are valid once that stream has been synchronised."""
+        With sync=False the call only queues the work on the pipeline's streams; call wait() (or a run with
+        sync=True) before touching the outputs."""
         b, L, h, d = self.shape
         for t in (x, dy, y, dx):
             if tuple(t.shape) != (b, L, h, d) or t.dtype != self.dtype or t.is_cuda:
@@ -98,8 +105,12 @@ class HostPipeline:
         start.record(cur)
         for s in (self.s_in, self.s_comp, self.s_out):
             s.wait_event(start)
+        again = self.n_runs > 0          # the ring slots and events carry state from the previous run
+        a_dev = self.a2[self.n_runs % 2]
         with torch.cuda.stream(self.s_in):
-            self.a.copy_(a, non_blocking=True)
+            if self.n_runs >= 2:
+                self.s_in.wait_event(self.ev_a_free[self.n_runs % 2])   # the run before last has read this buffer
+            a_dev.copy_(a, non_blocking=True)
             ev_a = torch.cuda.Event()
             ev_a.record(self.s_in)
         self.s_comp.wait_event(ev_a)
@@ -109,16 +120,16 @@ class HostPipeline:
             k, slot = hi - lo, i % self.depth
             xs, dys, ys, dxs = self.x[slot][:k], self.dy[slot][:k], self.y[slot][:k], self.dx[slot][:k]
             with torch.cuda.stream(self.s_in):
-                if i >= self.depth:
-                    self.s_in.wait_event(self.ev_comp[slot])     # the kernels of slice i - depth have read x, dy
+                if i >= self.depth or again:
+                    self.s_in.wait_event(self.ev_comp[slot])     # the kernels that last used this slot have read x, dy
                 xs.copy_(x[lo:hi], non_blocking=True)
                 dys.copy_(dy[lo:hi], non_blocking=True)
                 self.ev_in[slot].record(self.s_in)
             with torch.cuda.stream(self.s_comp):
                 self.s_comp.wait_event(self.ev_in[slot])
-                if i >= self.depth:
-                    self.s_comp.wait_event(self.ev_out[slot])    # y, dx of slice i - depth have left
-                a_i = self.a if self.per_head else self.a[lo:hi]
+                if i >= self.depth or again:
+                    self.s_comp.wait_event(self.ev_out[slot])    # y, dx of the slice that last used this slot have left
+                a_i = a_dev if self.per_head else a_dev[lo:hi]
                 da_i = self.da[i] if self.per_head else self.da[lo:hi]
                 ts = self.tile_states[slot][: k * h]
                 ops.ema_fwd(xs, a_i, out=ys, tile_states=ts, prescaled_log=self.prescaled_log)
@@ -137,12 +148,19 @@ class HostPipeline:
                 da.copy_(self.da_sum, non_blocking=True)
             else:
                 da.copy_(self.da, non_blocking=True)
-        for s in (self.s_comp, self.s_out):
-            cur.wait_stream(s)
+            self.ev_a_free[self.n_runs % 2].record(self.s_comp)
+        self.n_runs += 1
         self.n_launches = launches
         if sync:
+            self.wait()
             cur.synchronize()
         return y, dx, da
+
+    def wait(self):
+        """Makes the caller's current stream wait for every run queued so far."""
+        cur = torch.cuda.current_stream(self.device)
+        for s in (self.s_comp, self.s_out):
+            cur.wait_stream(s)
 
 
 def ema_fwd_bwd_host(x, a, dy, y=None, dx=None, da=None, device="cuda", slices=8, depth=3, prescaled_log=False):
