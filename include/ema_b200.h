@@ -125,7 +125,8 @@ size_t ema_b200_bwd_workspace_bytes(const ema_b200_problem *p);
  *   stop_below    0 to scan all L steps.  > 0: stop after the first tile at whose end the
  *                 product of decays since step 0 is below this value - used to re-scan only the
  *                 prefix an incoming carry can still influence (sequence-parallel fix-up).
- *   workspace     optional scratch of ema_b200_fwd_workspace_bytes(p) bytes, 16-byte aligned.  With
+ *   workspace     optional scratch of ema_b200_fwd_workspace_bytes(p) bytes (a few hundred KB, whatever
+ *                 the problem size), 16-byte aligned.  With
  *                 it, and when the work items (scan row x 128 channels) do not divide evenly among
  *                 the SMs, the bf16 kernels cut items across thread blocks and pass the carries
  *                 through this scratch, so that every SM has work; without it each item stays on

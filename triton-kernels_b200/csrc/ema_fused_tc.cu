@@ -260,7 +260,8 @@ struct TcParams {
     int n_tiles;      // 128-step tiles; one saved state per tile and row (layout shared with the CUDA-core path)
     int n_dtiles, n_items;
     int64_t n_chunks;
-    // split schedule (see Sched): carries handed from CTA to CTA, 128 floats and one arrival counter per work item
+    // split schedule (see Sched): carries handed from CTA to CTA, 128 floats and one arrival counter per cut,
+    // indexed by the number of the CTA on the right-hand side of the cut
     int split;
     float *carry;
     unsigned *flags;
@@ -272,7 +273,7 @@ struct TcParams {
 // item-major order, are cut into one contiguous range per CTA.  A range is at least one item long, so it is a
 // possibly partial first item, whole items, and a possibly partial last item, and every item is cut at most
 // once.  The CTA that owns the first part of a cut item hands the carry to the owner of the second part through
-// global memory (128 floats + an arrival counter per item).  Each CTA works on the piece that somebody waits
+// global memory (128 floats + an arrival counter per cut; cut j lies between the ranges of CTA j - 1 and CTA j).  Each CTA works on the piece that somebody waits
 // for FIRST and on the piece that waits for somebody LAST, so that a carry is published a whole range ahead of
 // its use and no wait depends on another wait; the wait itself is bounded like every other wait of the kernel.
 // ---------------------------------------------------------------------------------------------
@@ -519,13 +520,15 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const bool ch_ok = loader && c0 + m < p.d;
             float *ts_item = p.tile_states ? p.tile_states + row * p.n_tiles * p.d + c0 : nullptr;
             const bool publish = pc.k1 < p.n_tiles;   // the item continues in another CTA: hand it the state
-            float *carry_item = p.carry + pc.item * DT;
+            // a piece that ends inside an item hands its state to the next CTA (cut blockIdx.x + 1); a piece that starts
+            // inside an item takes it from the previous one (cut blockIdx.x)
+            float *carry_out = p.carry + static_cast<int64_t>(blockIdx.x + 1) * DT;
             if (loader) {
                 float v;
                 if (pc.k0 > 0) {   // second part of a cut item: the state comes from the CTA that made the first part
-                    if (lane == 0) wait_carry(p.flags + pc.item, abort_flag, 22);
+                    if (lane == 0) wait_carry(p.flags + blockIdx.x, abort_flag, 22);
                     __syncwarp();
-                    v = __ldcg(carry_item + m);
+                    v = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x) * DT + m);
                 } else {
                     v = (p.init_state && ch_ok) ? p.init_state[row * p.d + c0 + m] : 0.f;
                     if (p.chunk_states && ch_ok) p.chunk_states[(row * p.n_chunks) * p.d + c0 + m] = v;
@@ -590,10 +593,10 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                             store_row32(p.chunk_states + (row * p.n_chunks + (t + 1) / p.chunk) * p.d + c0 + cb, tmp, n_valid);
                         if (at_last_step) store_row32(p.final_state + row * p.d + c0 + cb, tmp, n_valid);
                         if (at_cut) {
-                            store_row32(carry_item + cb, tmp, 32);
+                            store_row32(carry_out + cb, tmp, 32);
                             if (pass == 1) {   // this half of the carry is complete
                                 __threadfence();
-                                atomicAdd(p.flags + pc.item, 1u);
+                                atomicAdd(p.flags + blockIdx.x + 1, 1u);
                             }
                         }
                     }
@@ -938,7 +941,8 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const int64_t row = pc.item / p.n_dtiles;
             const int hi = static_cast<int>(row % p.h);
             const bool publish = pc.k0 > 0;   // the item continues to the left in another CTA: hand it the adjoint
-            float *carry_item = p.carry + pc.item * DT;
+            // cut blockIdx.x is this CTA's left edge (it publishes there), cut blockIdx.x + 1 its right edge (it reads there)
+            float *carry_out = p.carry + static_cast<int64_t>(blockIdx.x) * DT;
             const int c0 = dtile * DT;
             const bool ch_ok = loader && c0 + m < p.d;
             const float *ts_item = p.tile_states + row * p.n_tiles * p.d + c0 + m;
@@ -955,9 +959,9 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 hs_sm[slot0 * DT + m] = ch_ok ? ts_item[static_cast<int64_t>(pc.k1 - 1) * p.d] : 0.f;
                 float gv;
                 if (pc.k1 < p.n_tiles) {   // left part of a cut item: the adjoint comes from the CTA that made the right part
-                    if (lane == 0) wait_carry(p.flags + pc.item, abort_flag, 23);
+                    if (lane == 0) wait_carry(p.flags + blockIdx.x + 1, abort_flag, 23);
                     __syncwarp();
-                    gv = __ldcg(carry_item + m);
+                    gv = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x + 1) * DT + m);
                 } else {
                     gv = (p.dfinal_state && ch_ok) ? p.dfinal_state[row * p.d + c0 + m] : 0.f;
                 }
@@ -1027,13 +1031,13 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                                 *reinterpret_cast<float4 *>(gout + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
                             if (pass == 1) mbar_arrive(bar(B_G + nslot));
                         } else if (publish) {   // the tile on the left is another CTA's
-                            float *co = carry_item + cb;
+                            float *co = carry_out + cb;
 #pragma unroll
                             for (int c = 0; c < 32; c += 4)
                                 *reinterpret_cast<float4 *>(co + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
                             if (pass == 1) {   // this half of the carry is complete
                                 __threadfence();
-                                atomicAdd(p.flags + pc.item, 1u);
+                                atomicAdd(p.flags + blockIdx.x, 1u);
                             }
                         } else if (p.dinit_state) {
                             float *di = p.dinit_state + row * p.d + c0 + cb;
@@ -1260,11 +1264,12 @@ bool tc_tensor_ok(const void *base, int64_t d, int64_t sb, int64_t sl, int64_t s
     return encode_fn() != nullptr;
 }
 
-// Scratch of the split schedule: one arrival counter and 128 floats of carry per work item.
-static size_t sync_flag_bytes(int64_t n_items) { return static_cast<size_t>((n_items * 4 + 255) / 256 * 256); }
-size_t tc_sync_bytes(int64_t b, int64_t h, int64_t d) {
-    const int64_t n_items = b * h * ((d + tc::DT - 1) / tc::DT);
-    return sync_flag_bytes(n_items) + static_cast<size_t>(n_items) * tc::DT * sizeof(float);
+// Scratch of the split schedule: one arrival counter and 128 floats of carry per cut between two thread blocks'
+// ranges, for up to kMaxSplitGrid thread blocks (one per SM).  Its size does not depend on the problem.
+constexpr int kMaxSplitGrid = 512;
+static size_t sync_flag_bytes() { return static_cast<size_t>(kMaxSplitGrid + 1) * 4 / 256 * 256 + 256; }
+size_t tc_sync_bytes(int64_t, int64_t, int64_t) {
+    return sync_flag_bytes() + static_cast<size_t>(kMaxSplitGrid + 1) * tc::DT * sizeof(float);
 }
 static int g_split = -1;   // -1: not read yet; 0 / 1
 static bool split_enabled() {
@@ -1302,10 +1307,10 @@ static int plan_grid(const FusedParams &fp, int n_items, bool allow_split, cudaS
     *flags = nullptr;
     // cutting pays when whole items would leave a noticeable share of the SM-rounds idle (256 items on 148 SMs: 13.5 %)
     const bool uneven = static_cast<int64_t>(rounds) * sms * 92 > static_cast<int64_t>(n_items) * 100;
-    if (!allow_split || !split_enabled() || n_items < sms || !uneven || !fp.sync_ws ||
+    if (!allow_split || !split_enabled() || n_items < sms || sms > kMaxSplitGrid || !uneven || !fp.sync_ws ||
         fp.sync_ws_bytes < tc_sync_bytes(fp.b, fp.h, fp.d))
         return EMA_OK;
-    const size_t fb = sync_flag_bytes(n_items);
+    const size_t fb = sync_flag_bytes();
     cudaError_t e = cudaMemsetAsync(fp.sync_ws, 0, fb, stream);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     *flags = static_cast<unsigned *>(fp.sync_ws);
