@@ -108,6 +108,26 @@ def test_sequence_ids_restart_the_state(dtype, ema_lib):
         assert float((got - ref).abs().max()) <= tol * max(float(ref.abs().max()), 1.0), what
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_inference_path_equals_training_path(dtype, ema_lib):
+    """Without gradients the entry point takes a shorter elementwise route around the same scan."""
+    from kernels.ema_combined import ema_chunk_scan_combined
+    b, L, h, p, g = 2, 260, 4, 64, 2
+    t = _make(13, b, L, h, p, g, dtype, False)
+    dev = {k: (v.to(dtype) if k == "x" else v).cuda() for k, v in t.items()}
+    init = torch.randn(b, h, p, 1, device="cuda")
+    with torch.no_grad():
+        out0, fin0 = ema_chunk_scan_combined(dev["x"], dev["dt"], dev["A"], dev["B"], dev["C"], 64, initial_states=init,
+                                             return_final_states=True)
+    xg = dev["x"].clone().requires_grad_(True)
+    out1, fin1 = ema_chunk_scan_combined(xg, dev["dt"], dev["A"], dev["B"], dev["C"], 64, initial_states=init,
+                                         return_final_states=True)
+    tol = BF16_REL if dtype == torch.bfloat16 else 1e-5
+    assert float((out0.float() - out1.float()).abs().max()) <= tol * max(float(out1.float().abs().max()), 1.0)
+    assert float((fin0 - fin1).abs().max()) <= tol * max(float(fin1.abs().max()), 1.0)
+
+
 def test_rejects_what_is_not_the_ema_case():
     from kernels.ema_combined import ema_chunk_scan_combined
     x, dt, A = torch.zeros(1, 8, 2, 4), torch.zeros(1, 8, 2), -torch.ones(2)

@@ -80,8 +80,19 @@ def _ema_chunk_scan_combined_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, dt_
         a_log = a_log.masked_fill(new_seq.unsqueeze(-1), float("-inf"))
     Bh = B[..., 0].float().repeat_interleave(rep, dim=2)                         # [b, l, h]
     Ch = C[..., 0].float().repeat_interleave(rep, dim=2)
-    u = (x.float() * (dtp * Bh).unsqueeze(-1)).to(x.dtype)
     init = None if initial_states is None else initial_states[..., 0].float().contiguous()
+    needs_grad = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (x, dt, A, B, C, D, z, dt_bias, initial_states))
+    if not needs_grad and D is None and z is None:
+        # inference: one pass over x before the scan and one over the result after it, each written in x's dtype
+        # (the product is formed in fp32 and rounded once)
+        u = torch.empty_like(x, memory_format=torch.contiguous_format)
+        torch.mul(x, (dtp * Bh).unsqueeze(-1), out=u)
+        r = ops.ema_fwd(u, a_log.contiguous(), prescaled_log=True, init_state=init, want_final=True)
+        out = r["y"]
+        torch.mul(out, Ch.unsqueeze(-1), out=out)
+        return out, r["final_state"].unsqueeze(-1)
+    u = (x.float() * (dtp * Bh).unsqueeze(-1)).to(x.dtype)
     s, final = _PrescaledScan.apply(u.contiguous(), a_log.contiguous(), init)
     out = s.float() * Ch.unsqueeze(-1)
     if D is not None:
