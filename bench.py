@@ -213,6 +213,7 @@ def run_gpu(args):
     ts, nt = ops.n_tiles_of(x, a)
     tile_states = torch.empty((b * h, nt, d), dtype=torch.float32, device=dev)
     ws = None
+    fws = ops.ema_fwd(x, a, out=y, tile_states=tile_states)["fwd_workspace"]   # the forward's scratch, reused by every step
 
     def reduce_da():
         nonlocal n_steps_done
@@ -245,7 +246,7 @@ def run_gpu(args):
             _, _, out = sp_forward()
             out.backward(dy)
             return
-        ops.ema_fwd(x, a, out=y, tile_states=tile_states)
+        ops.ema_fwd(x, a, out=y, tile_states=tile_states, workspace=fws)
         if fwd_only:
             return
         r = ops.ema_bwd(x, a, dy, tile_states, dx=dx, ddecay=da_slot(), workspace=ws)
@@ -264,7 +265,7 @@ def run_gpu(args):
         bev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(5)]
         for e in bev:
             e[0].record()
-            ops.ema_fwd(x, a, out=y, tile_states=tile_states)
+            ops.ema_fwd(x, a, out=y, tile_states=tile_states, workspace=fws)
             e[1].record()
             ops.ema_bwd(x, a, dy, tile_states, dx=dx, ddecay=da_bufs[0], workspace=ws)
             e[2].record()
@@ -309,7 +310,7 @@ def run_gpu(args):
             ev[i][2].record()
             del out
             continue
-        ops.ema_fwd(x, a, out=y, tile_states=tile_states)
+        ops.ema_fwd(x, a, out=y, tile_states=tile_states, workspace=fws)
         ev[i][1].record()
         if not fwd_only:
             ops.ema_bwd(x, a, dy, tile_states, dx=dx, ddecay=da_slot(), workspace=ws)

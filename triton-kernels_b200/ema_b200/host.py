@@ -74,6 +74,8 @@ class HostPipeline:
                             convention=ops.CONV_PRESCALED_LOG if prescaled_log else ops.CONV_NORTH_STAR)
         ws_floats = (lib().ema_b200_bwd_workspace_bytes(ctypes.byref(prob)) + 3) // 4
         self.workspace = [torch.empty((ws_floats,), dtype=torch.float32, device=dev) for _ in range(depth)]
+        fws_floats = (lib().ema_b200_fwd_workspace_bytes(ctypes.byref(prob)) + 3) // 4
+        self.fwd_workspace = [torch.empty((max(fws_floats, 1),), dtype=torch.float32, device=dev) for _ in range(depth)]
         # the decay lives in two device buffers used by alternate runs, so that a run's copy of it need not wait for
         # the kernels of the run before
         self.a2 = [torch.empty((h,) if per_head else (b, L, h), dtype=torch.float32, device=dev) for _ in range(2)]
@@ -132,7 +134,8 @@ class HostPipeline:
                 a_i = a_dev if self.per_head else a_dev[lo:hi]
                 da_i = self.da[i] if self.per_head else self.da[lo:hi]
                 ts = self.tile_states[slot][: k * h]
-                ops.ema_fwd(xs, a_i, out=ys, tile_states=ts, prescaled_log=self.prescaled_log)
+                ops.ema_fwd(xs, a_i, out=ys, tile_states=ts, prescaled_log=self.prescaled_log,
+                            workspace=self.fwd_workspace[slot])
                 ops.ema_bwd(xs, a_i, dys, ts, dx=dxs, ddecay=da_i, workspace=self.workspace[slot],
                             prescaled_log=self.prescaled_log)
                 launches += 4 if self.per_head else 3
