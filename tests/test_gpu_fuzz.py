@@ -1,0 +1,59 @@
+"""Randomised cross-check of the two kernel families on bf16 problems: the tensor-core path against the CUDA-core
+path over random shapes (ragged L and d, many or few rows), strided views, both decay modes and conventions, initial
+and incoming adjoint states, chunk states.  Seeds are fixed; a mismatch prints the configuration."""
+import random
+
+import pytest
+import torch
+
+from helpers import BF16_REL
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_tensor_core_and_cuda_core_paths_agree(seed, ema_lib):
+    from ema_b200 import ops
+    rnd = random.Random(seed)
+    failures = []
+    for case in range(40):
+        b = rnd.choice([1, 2, 3, 5, 19, 40]); h = rnd.choice([1, 2, 3, 8]); d = rnd.choice([8, 24, 64, 72, 128, 136, 256, 520, 1024])
+        L = rnd.choice([1, 7, 127, 128, 129, 300, 513, 1000, 2049])
+        if b * h * d * L > 3e7:
+            L = max(1, int(3e7 // (b * h * d)))
+        per_head, conv, strided = rnd.random() < 0.5, rnd.random() < 0.3, rnd.random() < 0.3
+        lo, hi = rnd.choice([(2, 6), (-3, 8), (4, 12), (-20, 12)])
+        g = torch.Generator().manual_seed(1000 * seed + case)
+        hh = h + 1 if strided else h
+        xb = torch.randn((b, L, hh, d), generator=g).to(torch.bfloat16).cuda()
+        dyb = torch.randn((b, L, hh, d), generator=g).to(torch.bfloat16).cuda()
+        x, dy = (xb[:, :, :h], dyb[:, :, :h]) if strided else (xb, dyb)
+        a = torch.sigmoid(lo + (hi - lo) * torch.rand((h,) if per_head else (b, L, h), generator=g)).cuda()
+        dec = torch.log(a) if conv else a
+        init = torch.randn(b, h, d, generator=g).cuda() if rnd.random() < 0.5 else None
+        dfin = torch.randn(b, h, d, generator=g).cuda() if rnd.random() < 0.5 else None
+        chunk = rnd.choice([0, 64, 128, 256])
+        outs = []
+        for path in (0, 1):
+            ema_lib.ema_b200_set_path(path)
+            f = ops.ema_fwd(x, dec, prescaled_log=conv, init_state=init, want_tile_states=True, want_final=True,
+                            chunk=chunk, want_chunk_states=chunk > 0)
+            r = ops.ema_bwd(x, dec, dy, f["tile_states"], prescaled_log=conv, dfinal_state=dfin, want_dinit=True)
+            torch.cuda.synchronize()
+            outs.append((f["y"].float(), f["final_state"], r["dx"].float(), r["ddecay"], r["dinit_state"],
+                         f.get("chunk_states")))
+        ema_lib.ema_b200_set_path(0)
+        for i, name in enumerate(("y", "final", "dx", "da", "dinit", "chunk_states")):
+            got, ref = outs[0][i], outs[1][i]
+            if got is None:
+                continue
+            # a per-head decay gradient is one number per head, the sum of b*L*d terms of either sign: its error is
+            # relative to the size of the terms, not of their sum
+            tol = 0.15 if (name == "da" and per_head) else 1.25 * BF16_REL
+            scale = max(float(ref.abs().max()), 1e-3)
+            err = float((got - ref).abs().max()) / scale
+            if not bool(torch.isfinite(got).all()) or err > tol:
+                failures.append((dict(b=b, L=L, h=h, d=d, per_head=per_head, conv=conv, strided=strided, lohi=(lo, hi),
+                                      init=init is not None, dfin=dfin is not None, chunk=chunk), name, err))
+    assert not failures, failures
+    assert ema_lib.ema_b200_device_status(0) == 0
