@@ -145,6 +145,8 @@ SPLIT_SHAPES = [
     (10, 640, 2, 1024),    # 160 items of 5 tiles on 148 SMs
     (19, 300, 1, 1024),    # 152 items of 3 tiles, ragged last tile
     (3, 2000, 7, 1000),    # 168 items of 16 tiles, d not a multiple of 128
+    (19, 300, 8, 1024),    # per-step decay: 608 two-tile items cut over the SMs; per-head: 1216 items
+    (37, 260, 1, 640),     # 185 items per-head; five channel tiles, i.e. an odd one left over when they are paired
 ]
 
 

@@ -259,6 +259,7 @@ struct TcParams {
     int decay_mode, convention, chunk;
     int n_tiles;      // 128-step tiles; one saved state per tile and row (layout shared with the CUDA-core path)
     int n_dtiles, n_items;
+    int sub, n_groups;   // channel tiles per work item (1 or 2) and work items per scan row
     int64_t n_chunks;
     // split schedule (see Sched): carries handed from CTA to CTA, 128 floats and one arrival counter per cut,
     // indexed by the number of the CTA on the right-hand side of the cut
@@ -316,12 +317,13 @@ struct Sched {
         return pc;
     }
 };
-// Bounded wait for the two halves of a carry (one arrival per 64-channel half).
-__device__ __forceinline__ bool wait_carry(const unsigned *flag, volatile int *abort_flag, int site) {
+constexpr int kCarryFloats = 2 * DT;   // per cut: the carries of up to two channel tiles
+// Bounded wait for a carry: one arrival per 64-channel half of every channel tile of the item.
+__device__ __forceinline__ bool wait_carry(const unsigned *flag, unsigned need, volatile int *abort_flag, int site) {
     for (uint32_t i = 0; i < kWaitLimit; ++i) {
         unsigned v;
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-        if (v >= 2u) return true;
+        if (v >= need) return true;
         if (*abort_flag) return false;
         __nanosleep(64);
     }
@@ -335,18 +337,23 @@ __device__ __forceinline__ bool wait_carry(const unsigned *flag, volatile int *a
 // ---------------------------------------------------------------------------------------------
 constexpr int kFwdStages = 4;
 constexpr int kFwdMatBufs = 2;
+// A forward work item may hold two channel tiles of one scan row, walked side by side (tile k of the first, tile k of
+// the second, tile k + 1 of the first, ...), so that one decay matrix serves two products: with a per-step decay the
+// builders are the bottleneck otherwise.  A carry is then used two sub-tiles after it was made, which takes a deeper
+// ring than kRing (the fastest epilogue warp may be two sub-tiles ahead of the slowest).
+constexpr int kFwdHRing = 8;
 struct FwdSmem {
     static constexpr int mat = 0;
     static constexpr int x = mat + kFwdMatBufs * kMatBytes;   // stages: x tile in, y tile out
-    static constexpr int h = x + kFwdStages * kTileBytes;     // float[kRing][128] carry entering a tile
-    static constexpr int e = h + kRing * DT * 4;               // float[kRing][128] E_m per build
+    static constexpr int h = x + kFwdStages * kTileBytes;     // float[kFwdHRing][128] carry entering a sub-tile
+    static constexpr int e = h + kFwdHRing * DT * 4;           // float[kRing][128] E_m per build
     static constexpr int cs = e + kRing * QT * 4;              // float[128] cumulative log2 decay
     static constexpr int pw = cs + QT * 4;                     // float[128] input weights
     static constexpr int wlo = pw + QT * 4;                    // float[128] column table of the off-diagonal chunks
     static constexpr int wt = wlo + QT * 4;                    // float[4] scan scratch
     static constexpr int bars = wt + 16;
     // stage full/empty/staged, acc full/empty, matrix full/empty, carry ready
-    static constexpr int n_bars = 3 * kFwdStages + 4 + 2 * kFwdMatBufs + kRing;
+    static constexpr int n_bars = 3 * kFwdStages + 4 + 2 * kFwdMatBufs + kFwdHRing;
     static constexpr int tmem_slot = bars + n_bars * 8;
     static constexpr int abort_flag = tmem_slot + 4;
     static constexpr int total = abort_flag + 4;
@@ -387,7 +394,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
         for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiWarps); }
         for (int i = 0; i < kFwdMatBufs; ++i) { mbar_init(bar(B_MAT_FULL + i), kBuildWarps); mbar_init(bar(B_MAT_EMPTY + i), 1); }
-        for (int i = 0; i < kRing; ++i) mbar_init(bar(B_H + i), 2);           // one arrival per channel half
+        for (int i = 0; i < kFwdHRing; ++i) mbar_init(bar(B_H + i), 2);       // one arrival per channel half
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tm_x);
@@ -406,6 +413,13 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
 
     const Sched sched(p.n_items, p.n_tiles, p.split != 0);
+    // item -> scan row, first channel tile, number of channel tiles (1 or 2)
+    auto item_row = [&](int64_t item) { return item / p.n_groups; };
+    auto item_dt0 = [&](int64_t item) { return static_cast<int>(item % p.n_groups) * p.sub; };
+    auto item_nsub = [&](int64_t item) {
+        const int left = p.n_dtiles - static_cast<int>(item % p.n_groups) * p.sub;
+        return left < p.sub ? left : p.sub;
+    };
     // log2 of the multiplicative decay of one step
     // (clamped: a decay of exactly 0 would make the prefix sums -inf and their differences NaN; 2^-30000 is 0 anyway)
     // lg2.approx (absolute error 2^-22): the decays end up in bf16 matrix elements and in carry factors over 128 steps
@@ -419,17 +433,20 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 uint32_t it = 0;
                 for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
                     const Piece pc = sched.get<true>(pi);
-                    const int dtile = static_cast<int>(pc.item % p.n_dtiles);
-                    const int64_t row = pc.item / p.n_dtiles;
+                    const int dt0 = item_dt0(pc.item), nsub = item_nsub(pc.item);
+                    const int64_t row = item_row(pc.item);
                     const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
-                    for (int k = pc.k0; k < pc.k1; ++k, ++it) {
-                        const int s = it % kFwdStages;
-                        const uint32_t ph = (it / kFwdStages) & 1;
-                        if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 1)) break;
-                        mbar_expect_tx(bar(B_FULL + s), kTileBytes);
-                        const uint32_t dst = sbase + FwdSmem::x + s * kTileBytes;
-                        tma_load_4d(dst, &tm_x, bar(B_FULL + s), dtile * DT, hi, k * QT, bi);
-                        tma_load_4d(dst + kBlockBytes, &tm_x, bar(B_FULL + s), dtile * DT + kBlockCols, hi, k * QT, bi);
+                    for (int k = pc.k0; k < pc.k1 && !*abort_flag; ++k) {
+                        for (int u = 0; u < nsub; ++u, ++it) {
+                            const int dtile = dt0 + u;
+                            const int s = it % kFwdStages;
+                            const uint32_t ph = (it / kFwdStages) & 1;
+                            if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 1)) break;
+                            mbar_expect_tx(bar(B_FULL + s), kTileBytes);
+                            const uint32_t dst = sbase + FwdSmem::x + s * kTileBytes;
+                            tma_load_4d(dst, &tm_x, bar(B_FULL + s), dtile * DT, hi, k * QT, bi);
+                            tma_load_4d(dst + kBlockBytes, &tm_x, bar(B_FULL + s), dtile * DT + kBlockCols, hi, k * QT, bi);
+                        }
                     }
                 }
             }
@@ -443,13 +460,15 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 int cur_head = -1, mb_cur = 0;
                 for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
                     const Piece pc = sched.get<true>(pi);
-                    const int hi = static_cast<int>((pc.item / p.n_dtiles) % p.h);
-                    for (int k = pc.k0; k < pc.k1; ++k, ++it) {
+                    const int hi = static_cast<int>(item_row(pc.item) % p.h);
+                    const int nsub = item_nsub(pc.item);
+                    for (int k = pc.k0; k < pc.k1 && !*abort_flag; ++k)
+                    for (int u = 0; u < nsub; ++u, ++it) {
                         const int s = it % kFwdStages;
                         const uint32_t ph = (it / kFwdStages) & 1;
                         const int acc = it & 1;
                         const uint32_t aph = (it >> 1) & 1;
-                        if (per_step || hi != cur_head) {
+                        if (u == 0 && (per_step || hi != cur_head)) {
                             // every MMA that read the previous head's matrix has been issued: release its buffer
                             if (!per_step && mt > 0) umma_commit(bar(B_MAT_EMPTY + ((mt - 1) % kFwdMatBufs)));
                             mb_cur = mt % kFwdMatBufs;
@@ -470,7 +489,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                             umma_bf16(tmem_base + acc * DT, ad, bd, kIdesc, kb > 0 ? 1u : 0u);
                         }
                         umma_commit(bar(B_ACC_FULL + acc));
-                        if (per_step) umma_commit(bar(B_MAT_EMPTY + mb_cur));
+                        if (per_step && u == nsub - 1) umma_commit(bar(B_MAT_EMPTY + mb_cur));
                     }
                 }
             }
@@ -480,11 +499,13 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 uint32_t it = 0;
                 for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
                     const Piece pc = sched.get<true>(pi);
-                    const int dtile = static_cast<int>(pc.item % p.n_dtiles);
-                    const int64_t row = pc.item / p.n_dtiles;
+                    const int dt0 = item_dt0(pc.item), nsub = item_nsub(pc.item);
+                    const int64_t row = item_row(pc.item);
                     const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
-                    const bool two = dtile * DT + kBlockCols < p.d;   // the second 64-channel block exists
-                    for (int k = pc.k0; k < pc.k1; ++k, ++it) {
+                    for (int k = pc.k0; k < pc.k1 && !*abort_flag; ++k)
+                    for (int u = 0; u < nsub; ++u, ++it) {
+                        const int dtile = dt0 + u;
+                        const bool two = dtile * DT + kBlockCols < p.d;   // the second 64-channel block exists
                         const int s = it % kFwdStages;
                         if (!mbar_wait(bar(B_STAGED + s), (it / kFwdStages) & 1, abort_flag, 9)) break;
                         const uint32_t src = sbase + FwdSmem::x + s * kTileBytes;
@@ -513,34 +534,42 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         int cur_head = -1;
         for (int pi = 0; pi < sched.n; ++pi) {
             const Piece pc = sched.get<true>(pi);
-            const int dtile = static_cast<int>(pc.item % p.n_dtiles);
-            const int64_t row = pc.item / p.n_dtiles;
+            const int dt0 = item_dt0(pc.item), nsub = item_nsub(pc.item);
+            const int64_t row = item_row(pc.item);
             const int hi = static_cast<int>(row % p.h);
-            const int c0 = dtile * DT;
-            const bool ch_ok = loader && c0 + m < p.d;
-            float *ts_item = p.tile_states ? p.tile_states + row * p.n_tiles * p.d + c0 : nullptr;
             const bool publish = pc.k1 < p.n_tiles;   // the item continues in another CTA: hand it the state
             // a piece that ends inside an item hands its state to the next CTA (cut blockIdx.x + 1); a piece that starts
-            // inside an item takes it from the previous one (cut blockIdx.x)
-            float *carry_out = p.carry + static_cast<int64_t>(blockIdx.x + 1) * DT;
+            // inside an item takes it from the previous one (cut blockIdx.x); kCarryFloats floats per cut
+            float *carry_out = p.carry + static_cast<int64_t>(blockIdx.x + 1) * kCarryFloats;
             if (loader) {
-                float v;
                 if (pc.k0 > 0) {   // second part of a cut item: the state comes from the CTA that made the first part
-                    if (lane == 0) wait_carry(p.flags + blockIdx.x, abort_flag, 22);
+                    if (lane == 0) wait_carry(p.flags + blockIdx.x, 2u * nsub, abort_flag, 22);
                     __syncwarp();
-                    v = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x) * DT + m);
-                } else {
-                    v = (p.init_state && ch_ok) ? p.init_state[row * p.d + c0 + m] : 0.f;
-                    if (p.chunk_states && ch_ok) p.chunk_states[(row * p.n_chunks) * p.d + c0 + m] = v;
                 }
-                h_sm[(it & (kRing - 1)) * DT + m] = v;
+                for (int u = 0; u < nsub; ++u) {
+                    const int c0u = (dt0 + u) * DT;
+                    const bool ok = c0u + m < p.d;
+                    float v;
+                    if (pc.k0 > 0) {
+                        v = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x) * kCarryFloats + u * DT + m);
+                    } else {
+                        v = (p.init_state && ok) ? p.init_state[row * p.d + c0u + m] : 0.f;
+                        if (p.chunk_states && ok) p.chunk_states[(row * p.n_chunks) * p.d + c0u + m] = v;
+                    }
+                    h_sm[((it + u) & (kFwdHRing - 1)) * DT + m] = v;
+                }
             }
             bar_sync(1, kEpiThreads);  // once per piece: the previous one is finished everywhere, the state is in place
-            if (m == QT - 1) mbar_arrive(bar(B_H + (it & (kRing - 1))));
-            for (int k = pc.k0; k < pc.k1; ++k, ++it) {
-                const int acc = it & 1, slot = it & (kRing - 1), s = it % kFwdStages;
-                const uint32_t aph = (it >> 1) & 1, hph = (it / kRing) & 1;
-                if (per_step || hi != cur_head) { cur_head = hi; ++mt; }
+            if (m == QT - 1)
+                for (int u = 0; u < nsub; ++u) mbar_arrive(bar(B_H + ((it + u) & (kFwdHRing - 1))));
+            for (int k = pc.k0; k < pc.k1; ++k)
+            for (int u = 0; u < nsub; ++u, ++it) {
+                const int c0 = (dt0 + u) * DT;
+                const bool ch_ok = loader && c0 + m < p.d;
+                float *ts_item = p.tile_states ? p.tile_states + row * p.n_tiles * p.d + c0 : nullptr;
+                const int acc = it & 1, slot = it & (kFwdHRing - 1), s = it % kFwdStages;
+                const uint32_t aph = (it >> 1) & 1, hph = (it / kFwdHRing) & 1;
+                if (u == 0 && (per_step || hi != cur_head)) { cur_head = hi; ++mt; }
                 if (lane == 0) mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 5);  // one poller per warp
                 __syncwarp();
                 tc_fence_after_sync();
@@ -572,12 +601,12 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         y[c + 2] = fmaf(E, hv.z, y[c + 2]);
                         y[c + 3] = fmaf(E, hv.w, y[c + 3]);
                     }
-                    if (m == QT - 1 && k + 1 < pc.k1) {  // the last row is the state entering the next tile
-                        float *hout = h_sm + ((it + 1) & (kRing - 1)) * DT + cb;
+                    if (m == QT - 1 && k + 1 < pc.k1) {  // the last row is the state entering this channel tile's next tile
+                        float *hout = h_sm + ((it + nsub) & (kFwdHRing - 1)) * DT + cb;
 #pragma unroll
                         for (int c = 0; c < 32; c += 4)
                             *reinterpret_cast<float4 *>(hout + c) = make_float4(y[c], y[c + 1], y[c + 2], y[c + 3]);
-                        if (pass == 1) mbar_arrive(bar(B_H + ((it + 1) & (kRing - 1))));
+                        if (pass == 1) mbar_arrive(bar(B_H + ((it + nsub) & (kFwdHRing - 1))));
                     }
                     // rare side outputs (a chunk boundary, the last step): kept out of line so that they do not
                     // cost the common path registers
@@ -593,7 +622,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                             store_row32(p.chunk_states + (row * p.n_chunks + (t + 1) / p.chunk) * p.d + c0 + cb, tmp, n_valid);
                         if (at_last_step) store_row32(p.final_state + row * p.d + c0 + cb, tmp, n_valid);
                         if (at_cut) {
-                            store_row32(carry_out + cb, tmp, 32);
+                            store_row32(carry_out + u * DT + cb, tmp, 32);
                             if (pass == 1) {   // this half of the carry is complete
                                 __threadfence();
                                 atomicAdd(p.flags + blockIdx.x + 1, 1u);
@@ -656,8 +685,8 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         };
         for (int pi = 0; pi < sched.n; ++pi) {
             const Piece pc = sched.get<true>(pi);
-            const int64_t row = pc.item / p.n_dtiles;
-            const int dtile = static_cast<int>(pc.item % p.n_dtiles);
+            const int64_t row = item_row(pc.item);
+            const int dtile = item_dt0(pc.item);
             const int64_t bi = row / p.h, hi = row % p.h;
             const float *arow = p.decay + (per_step ? bi * p.a_sb + hi * p.a_sh : hi * p.a_sh);
             if (!per_step) {
@@ -942,7 +971,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const int hi = static_cast<int>(row % p.h);
             const bool publish = pc.k0 > 0;   // the item continues to the left in another CTA: hand it the adjoint
             // cut blockIdx.x is this CTA's left edge (it publishes there), cut blockIdx.x + 1 its right edge (it reads there)
-            float *carry_out = p.carry + static_cast<int64_t>(blockIdx.x) * DT;
+            float *carry_out = p.carry + static_cast<int64_t>(blockIdx.x) * kCarryFloats;
             const int c0 = dtile * DT;
             const bool ch_ok = loader && c0 + m < p.d;
             const float *ts_item = p.tile_states + row * p.n_tiles * p.d + c0 + m;
@@ -959,9 +988,9 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 hs_sm[slot0 * DT + m] = ch_ok ? ts_item[static_cast<int64_t>(pc.k1 - 1) * p.d] : 0.f;
                 float gv;
                 if (pc.k1 < p.n_tiles) {   // left part of a cut item: the adjoint comes from the CTA that made the right part
-                    if (lane == 0) wait_carry(p.flags + blockIdx.x + 1, abort_flag, 23);
+                    if (lane == 0) wait_carry(p.flags + blockIdx.x + 1, 2u, abort_flag, 23);
                     __syncwarp();
-                    gv = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x + 1) * DT + m);
+                    gv = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x + 1) * kCarryFloats + m);
                 } else {
                     gv = (p.dfinal_state && ch_ok) ? p.dfinal_state[row * p.d + c0 + m] : 0.f;
                 }
@@ -1269,7 +1298,7 @@ bool tc_tensor_ok(const void *base, int64_t d, int64_t sb, int64_t sl, int64_t s
 constexpr int kMaxSplitGrid = 512;
 static size_t sync_flag_bytes() { return static_cast<size_t>(kMaxSplitGrid + 1) * 4 / 256 * 256 + 256; }
 size_t tc_sync_bytes(int64_t, int64_t, int64_t) {
-    return sync_flag_bytes() + static_cast<size_t>(kMaxSplitGrid + 1) * tc::DT * sizeof(float);
+    return sync_flag_bytes() + static_cast<size_t>(kMaxSplitGrid + 1) * tc::kCarryFloats * sizeof(float);
 }
 static int g_split = -1;   // -1: not read yet; 0 / 1
 static bool split_enabled() {
@@ -1335,7 +1364,16 @@ int launch_fused_fwd_tc(const FusedParams &fp, cudaStream_t stream) {
     p.decay_mode = fp.decay_mode; p.convention = fp.convention; p.chunk = fp.chunk;
     p.n_tiles = static_cast<int>((fp.L + tc::QT - 1) / tc::QT);
     p.n_dtiles = static_cast<int>((fp.d + tc::DT - 1) / tc::DT);
-    p.n_items = static_cast<int>(fp.b * fp.h * p.n_dtiles);
+    // With a per-step decay every tile needs its own matrix and the builders set the pace: let one matrix serve two
+    // channel tiles of the row, unless halving the number of work items would leave noticeably more SMs without one.
+    {
+        const int64_t rows = fp.b * fp.h, sms = sm_count();
+        const int64_t single = rows * p.n_dtiles, paired = rows * ((p.n_dtiles + 1) / 2);
+        const int64_t busy_single = single < sms ? single : sms, busy_paired = paired < sms ? paired : sms;
+        p.sub = (fp.decay_mode == EMA_DECAY_PER_STEP && p.n_dtiles > 1 && busy_paired * 100 >= busy_single * 85) ? 2 : 1;
+    }
+    p.n_groups = (p.n_dtiles + p.sub - 1) / p.sub;
+    p.n_items = static_cast<int>(fp.b * fp.h * p.n_groups);
     p.n_chunks = fp.n_chunks;
     int grid = 0;
     // the sum of the log decays is accumulated per item by one CTA: no cutting when it is asked for
