@@ -28,6 +28,7 @@
 // stage staged.  Every wait is bounded (ema_tc_common.cuh): after a timeout the roles run their loops to
 // the end without waiting, the CTA tears down normally and the host sees EMA_ERR_TIMEOUT.
 #include <cstdlib>
+#include <cuda_fp16.h>
 
 #include "ema_common.cuh"
 #include "ema_tc_common.cuh"
@@ -208,6 +209,48 @@ __device__ __forceinline__ void store_matrix(const OffGeom &og, const DiagGeom &
     *reinterpret_cast<uint2 *>(mat + dg.st) = in.dg;
 }
 
+// The same with the column table in half precision (8 halves = one 16-byte load), two products per instruction.
+// Tables that carry an input weight (the lower matrices) are stored times 2^kHalfShift, so that weights down to
+// 2^-24 (the smallest 1 - a above 0 in fp32) stay normal halves; the row scalar takes the factor back.  What still
+// underflows is below 2^-24 of the largest element of its chunk row.
+constexpr int kHalfShift = 10;
+template <bool UPPER>
+__device__ __forceinline__ void compute_off_half(const OffGeom &g, const uint8_t *cs_b, const uint8_t *tab_b, RowChunks &out) {
+#pragma unroll
+    for (int s = 0; s < kOffSlots; ++s) {
+        if (s == kOffSlots - 1 && !g.last_valid) continue;
+        const float ca = ld_f32(cs_b, g.a[s]);
+        const float cb = ld_f32(cs_b, UPPER ? g.c[s] - 4u : g.c[s] + 28u);   // cs[8c - 1] | cs[8c + 7]
+        const float sc = ex2_approx(UPPER ? cb - ca : ca - cb - static_cast<float>(kHalfShift));
+        const uint4 t = *reinterpret_cast<const uint4 *>(tab_b + (g.c[s] >> 1));
+        const float2 sc2 = make_float2(sc, sc);
+        const float2 v0 = __fmul2_rn(__half22float2(*reinterpret_cast<const __half2 *>(&t.x)), sc2),
+                     v1 = __fmul2_rn(__half22float2(*reinterpret_cast<const __half2 *>(&t.y)), sc2),
+                     v2 = __fmul2_rn(__half22float2(*reinterpret_cast<const __half2 *>(&t.z)), sc2),
+                     v3 = __fmul2_rn(__half22float2(*reinterpret_cast<const __half2 *>(&t.w)), sc2);
+        out.v[s] = make_uint4(pack_bf16x2(v0.x, v0.y), pack_bf16x2(v1.x, v1.y), pack_bf16x2(v2.x, v2.y),
+                              pack_bf16x2(v3.x, v3.y));
+    }
+}
+// Diagonal half chunk of a lower matrix with the input weights in half precision, scaled by 2^kHalfShift.
+template <int SHIFT>
+__device__ __forceinline__ void compute_diag_lower_half(const DiagGeom &g, const uint8_t *cs_b, const uint8_t *p_b, float diag,
+                                                        RowChunks &out) {
+    const float cm = (g.has_top ? ld_f32(cs_b, g.top) : 0.f) - static_cast<float>(kHalfShift);
+    const float4 c4 = ld_f32x4(cs_b, g.k);
+    const uint2 pp = *reinterpret_cast<const uint2 *>(p_b + (g.k >> 1));
+    const float2 p01 = __half22float2(*reinterpret_cast<const __half2 *>(&pp.x)),
+                 p23 = __half22float2(*reinterpret_cast<const __half2 *>(&pp.y));
+    const float cs4[4] = {c4.x, c4.y, c4.z, c4.w}, pw4[4] = {p01.x, p01.y, p23.x, p23.y};
+    float v[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        // past the diagonal the exponent is positive: clamp it so that the discarded value stays finite
+        const float gv = pw4[e] * ex2_approx(fminf(cm - cs4[e], -static_cast<float>(kHalfShift)));
+        v[e] = (e <= g.lim) ? gv : ((SHIFT == 1 && e == g.lim + 1) ? diag : 0.f);
+    }
+    out.dg = make_uint2(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]));
+}
 // Inclusive scan of one value per row (builder threads 0-127, 4 warps) through shared memory; all 256 builder
 // threads call it.  Leaves cs_sm[r] = sum_{i<=r} v_i, visible to the first 128 threads only: the caller's next
 // 256-thread barrier publishes it.  The first barrier also fences the previous use of the tables.
@@ -421,9 +464,10 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         return left < p.sub ? left : p.sub;
     };
     // log2 of the multiplicative decay of one step
-    // (clamped: a decay of exactly 0 would make the prefix sums -inf and their differences NaN; 2^-30000 is 0 anyway)
+    // (clamped: a decay of exactly 0 would make the prefix sums -inf and their differences NaN; 2^-160 is 0 in fp32,
+    // and a small bound keeps the prefix sums of a tile with many such steps precise)
     // lg2.approx (absolute error 2^-22): the decays end up in bf16 matrix elements and in carry factors over 128 steps
-    auto log2_decay = [&](float v) { return fmaxf(conv ? v * 1.4426950408889634f : __log2f(v), -30000.f); };
+    auto log2_decay = [&](float v) { return fmaxf(conv ? v * 1.4426950408889634f : __log2f(v), -160.f); };
 
     if (warp < 4) {
         reg_dec<kRegsLight>();
@@ -753,6 +797,7 @@ struct TcBwdParams {
     int64_t a_sb, a_sl, a_sh;
     int decay_mode, convention;
     int n_tiles, n_dtiles, n_items;
+    int sub, n_groups;   // channel tiles per work item (1 or 2) and work items per scan row (see the forward kernel)
     int n_dt64;       // 64-channel slices per row in the partial-sum buffer
     int64_t head_partial_offset;
     // split schedule (see Sched): adjoint carries handed from CTA to CTA
@@ -763,6 +808,11 @@ struct TcBwdParams {
 
 constexpr int kBwdStages = 2;
 constexpr int kRowRing = 3;   // per-row scalar tables: a build's table is read early in the tile that uses it
+// Depth of the carry rings (saved state and adjoint entering a sub-tile).  With two channel tiles per item a carry is
+// used two sub-tiles after it was made and the fastest epilogue warp may be two sub-tiles ahead of the slowest: five
+// slots.  (Shared memory is full: to make room the builders' column tables are kept in half precision - they only
+// multiply into bf16 matrix elements.)
+constexpr int kBwdCRing = 5;
 // The two matrices are triangular: the upper-right 64x64 quadrant of A1 and the lower-left one of U are zero.
 // Stored by 64-wide K blocks (rows of 128 bytes), the zero quadrants are one shared 8 KB region Z:
 //   [A1 K-block 0, rows 0-127][U K-block 0, rows 0-63][Z][A1 K-block 1, rows 64-127][U K-block 1, rows 0-127]
@@ -776,17 +826,17 @@ struct BwdSmem {
     static constexpr int mat_bytes = m_uk1 + kBlockBytes;              // 56 KB
     static constexpr int xg = mat_bytes;                               // stages of [x tile | dy tile]
     static constexpr int ostage = xg + kBwdStages * 2 * kTileBytes;    // dx staging: one tile, a 64-channel block per half
-    static constexpr int hs = ostage + kTileBytes;                     // float[kRing][128] saved state entering the tile
-    static constexpr int g = hs + kRing * DT * 4;                      // float[kRing][128] adjoint carry
-    static constexpr int rowsc = g + kRing * DT * 4;                   // float[kRowRing][3][128]: Eprev, F, a per build
+    static constexpr int hs = ostage + kTileBytes;                     // float[kBwdCRing][128] saved state entering the sub-tile
+    static constexpr int g = hs + kBwdCRing * DT * 4;                  // float[kBwdCRing][128] adjoint carry
+    static constexpr int rowsc = g + kBwdCRing * DT * 4;               // float[kRowRing][3][128]: Eprev, F, a per build
     static constexpr int cs = rowsc + kRowRing * 3 * QT * 4;           // float[128]
-    static constexpr int pw = cs + QT * 4;                             // float[128]
-    static constexpr int wlo = pw + QT * 4;                            // float[128] column table, lower matrix
-    static constexpr int rup = wlo + QT * 4;                           // float[128] column table, upper matrix
-    static constexpr int wt = rup + QT * 4;                            // float[4]
+    static constexpr int pw = cs + QT * 4;                             // half[128] input weights * 2^kHalfShift
+    static constexpr int wlo = pw + QT * 2;                            // half[128] column table, lower matrix (same scale)
+    static constexpr int rup = wlo + QT * 2;                           // half[128] column table, upper matrix
+    static constexpr int wt = rup + QT * 2;                            // float[4]
     static constexpr int bars = wt + 16;
     // stage full/empty, staging full/empty per half, acc full/empty, matrix full/empty, carry ready
-    static constexpr int n_bars = 2 * kBwdStages + 4 + 4 + 2 + kRing;
+    static constexpr int n_bars = 2 * kBwdStages + 4 + 4 + 2 + kBwdCRing;
     static constexpr int tmem_slot = bars + n_bars * 8;
     static constexpr int abort_flag = tmem_slot + 4;
     static constexpr int total = abort_flag + 4;
@@ -816,9 +866,9 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     float *g_sm = reinterpret_cast<float *>(smem + BwdSmem::g);
     float *rowsc = reinterpret_cast<float *>(smem + BwdSmem::rowsc);
     float *cs_sm = reinterpret_cast<float *>(smem + BwdSmem::cs);
-    float *p_sm = reinterpret_cast<float *>(smem + BwdSmem::pw);
-    float *wlo_sm = reinterpret_cast<float *>(smem + BwdSmem::wlo);
-    float *rup_sm = reinterpret_cast<float *>(smem + BwdSmem::rup);
+    __half *p_sm = reinterpret_cast<__half *>(smem + BwdSmem::pw);
+    __half *wlo_sm = reinterpret_cast<__half *>(smem + BwdSmem::wlo);
+    __half *rup_sm = reinterpret_cast<__half *>(smem + BwdSmem::rup);
     float *wt_sm = reinterpret_cast<float *>(smem + BwdSmem::wt);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + BwdSmem::abort_flag);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + BwdSmem::tmem_slot);
@@ -835,7 +885,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         mbar_init(bar(B_MAT_FULL), kBuildWarps);
         mbar_init(bar(B_MAT_EMPTY), 1);
         // carry ready: the two halves of the adjoint row and the four warps that fetch the saved state
-        for (int i = 0; i < kRing; ++i) mbar_init(bar(B_G + i), 6);
+        for (int i = 0; i < kBwdCRing; ++i) mbar_init(bar(B_G + i), 6);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tm_x);
@@ -854,9 +904,17 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     const uint32_t tmem_base = *tmem_slot;
 
     const Sched sched(p.n_items, p.n_tiles, p.split != 0);
-    // (clamped: a decay of exactly 0 would make the prefix sums -inf and their differences NaN; 2^-30000 is 0 anyway)
+    // item -> scan row, first channel tile, number of channel tiles (1 or 2)
+    auto item_row = [&](int64_t item) { return item / p.n_groups; };
+    auto item_dt0 = [&](int64_t item) { return static_cast<int>(item % p.n_groups) * p.sub; };
+    auto item_nsub = [&](int64_t item) {
+        const int left = p.n_dtiles - static_cast<int>(item % p.n_groups) * p.sub;
+        return left < p.sub ? left : p.sub;
+    };
+    // (clamped: a decay of exactly 0 would make the prefix sums -inf and their differences NaN; 2^-160 is 0 in fp32,
+    // and a small bound keeps the prefix sums of a tile with many such steps precise)
     // lg2.approx (absolute error 2^-22): the decays end up in bf16 matrix elements and in carry factors over 128 steps
-    auto log2_decay = [&](float v) { return fmaxf(conv ? v * 1.4426950408889634f : __log2f(v), -30000.f); };
+    auto log2_decay = [&](float v) { return fmaxf(conv ? v * 1.4426950408889634f : __log2f(v), -160.f); };
 
     if (warp < 4) {
         reg_dec<kRegsLight>();
@@ -866,16 +924,17 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 uint32_t it = 0;
                 for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
                     const Piece pc = sched.get<false>(pi);
-                    const int dtile = static_cast<int>(pc.item % p.n_dtiles);
-                    const int64_t row = pc.item / p.n_dtiles;
+                    const int dt0 = item_dt0(pc.item), nsub = item_nsub(pc.item);
+                    const int64_t row = item_row(pc.item);
                     const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
-                    for (int k = pc.k1 - 1; k >= pc.k0; --k, ++it) {
+                    for (int k = pc.k1 - 1; k >= pc.k0 && !*abort_flag; --k)
+                    for (int u = 0; u < nsub; ++u, ++it) {
                         const int s = it % kBwdStages;
                         const uint32_t ph = (it / kBwdStages) & 1;
                         if (!mbar_wait(bar(B_EMPTY + s), ph ^ 1, abort_flag, 11)) break;
                         mbar_expect_tx(bar(B_FULL + s), 2 * kTileBytes);
                         const uint32_t dst = sbase + BwdSmem::xg + s * 2 * kTileBytes;
-                        const int c0 = dtile * DT;
+                        const int c0 = (dt0 + u) * DT;
                         tma_load_4d(dst, &tm_x, bar(B_FULL + s), c0, hi, k * QT, bi);
                         tma_load_4d(dst + kBlockBytes, &tm_x, bar(B_FULL + s), c0 + kBlockCols, hi, k * QT, bi);
                         tma_load_4d(dst + kTileBytes, &tm_g, bar(B_FULL + s), c0, hi, k * QT, bi);
@@ -895,13 +954,15 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                                         make_desc_sw128(sbase + BwdSmem::m_uk1, 16, 1024)};
                 for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
                     const Piece pc = sched.get<false>(pi);
-                    const int hi = static_cast<int>((pc.item / p.n_dtiles) % p.h);
-                    for (int k = pc.k1 - 1; k >= pc.k0; --k, ++it) {
+                    const int hi = static_cast<int>(item_row(pc.item) % p.h);
+                    const int nsub = item_nsub(pc.item);
+                    for (int k = pc.k1 - 1; k >= pc.k0 && !*abort_flag; --k)
+                    for (int u = 0; u < nsub; ++u, ++it) {
                         const int s = it % kBwdStages;
                         const uint32_t ph = (it / kBwdStages) & 1;
                         const int acc = it & 1;
                         const uint32_t aph = (it >> 1) & 1;
-                        if (per_step || hi != cur_head) {
+                        if (u == 0 && (per_step || hi != cur_head)) {
                             // single matrix buffer: hand it back to the builders once the MMAs issued so far are done
                             if (!per_step && mt > 0) umma_commit(bar(B_MAT_EMPTY));
                             if (!mbar_wait(bar(B_MAT_FULL), mt & 1, abort_flag, 12)) break;
@@ -922,7 +983,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                             umma_bf16(d_l, ud[kb >> 2] + (((kb & 3) * 32) >> 4), gd0 + ((kb * 2048) >> 4), kIdesc, kb > 0 ? 1u : 0u);
                         umma_commit(bar(B_EMPTY + s));   // the stage is free as soon as the MMAs have read it
                         umma_commit(bar(B_ACC_FULL + acc));
-                        if (per_step) umma_commit(bar(B_MAT_EMPTY));
+                        if (per_step && u == nsub - 1) umma_commit(bar(B_MAT_EMPTY));
                     }
                 }
             }
@@ -932,11 +993,13 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 uint32_t it = 0;
                 for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
                     const Piece pc = sched.get<false>(pi);
-                    const int dtile = static_cast<int>(pc.item % p.n_dtiles);
-                    const int64_t row = pc.item / p.n_dtiles;
+                    const int dt0 = item_dt0(pc.item), nsub = item_nsub(pc.item);
+                    const int64_t row = item_row(pc.item);
                     const int bi = static_cast<int>(row / p.h), hi = static_cast<int>(row % p.h);
-                    const bool two = dtile * DT + kBlockCols < p.d;   // the second 64-channel block exists
-                    for (int k = pc.k1 - 1; k >= pc.k0; --k, ++it) {
+                    for (int k = pc.k1 - 1; k >= pc.k0 && !*abort_flag; --k)
+                    for (int u = 0; u < nsub; ++u, ++it) {
+                        const int dtile = dt0 + u;
+                        const bool two = dtile * DT + kBlockCols < p.d;   // the second 64-channel block exists
                         const uint32_t src = sbase + BwdSmem::ostage;
                         if (!mbar_wait(bar(B_STG_FULL + 0), it & 1, abort_flag, 19)) break;
                         tma_store_4d(&tm_o, src, dtile * DT, hi, k * QT, bi);
@@ -966,43 +1029,53 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         int cur_head = -1;
         for (int pi = 0; pi < sched.n; ++pi) {
             const Piece pc = sched.get<false>(pi);
-            const int dtile = static_cast<int>(pc.item % p.n_dtiles);
-            const int64_t row = pc.item / p.n_dtiles;
+            const int dt0 = item_dt0(pc.item), nsub = item_nsub(pc.item);
+            const int64_t row = item_row(pc.item);
             const int hi = static_cast<int>(row % p.h);
             const bool publish = pc.k0 > 0;   // the item continues to the left in another CTA: hand it the adjoint
             // cut blockIdx.x is this CTA's left edge (it publishes there), cut blockIdx.x + 1 its right edge (it reads there)
             float *carry_out = p.carry + static_cast<int64_t>(blockIdx.x) * kCarryFloats;
-            const int c0 = dtile * DT;
-            const bool ch_ok = loader && c0 + m < p.d;
-            const float *ts_item = p.tile_states + row * p.n_tiles * p.d + c0 + m;
-            // Partial sums of the decay gradient, in the layout of the CUDA-core kernel (so that a suffix re-scan by
-            // that kernel can overwrite some tiles of a pass made by this one): one slice per 64 channels,
-            // [row][slice][t] for a per-step decay, [row][slice][tile][8] for a per-head decay.
-            const int slice = 2 * dtile + half;
-            const bool slice_ok = slice < p.n_dt64;   // the second half of the last tile may hold no channels
-            float *dap_step = p.da_partial + (row * p.n_dt64 + slice) * (static_cast<int64_t>(p.n_tiles) * QT);
-            float *dap_head = p.da_partial + p.head_partial_offset + (row * p.n_dt64 + slice) * p.n_tiles * 8;
             float hs_next = 0.f;
             if (loader) {
-                const int slot0 = it & (kRing - 1);
-                hs_sm[slot0 * DT + m] = ch_ok ? ts_item[static_cast<int64_t>(pc.k1 - 1) * p.d] : 0.f;
-                float gv;
                 if (pc.k1 < p.n_tiles) {   // left part of a cut item: the adjoint comes from the CTA that made the right part
-                    if (lane == 0) wait_carry(p.flags + blockIdx.x + 1, 2u, abort_flag, 23);
+                    if (lane == 0) wait_carry(p.flags + blockIdx.x + 1, 2u * nsub, abort_flag, 23);
                     __syncwarp();
-                    gv = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x + 1) * kCarryFloats + m);
-                } else {
-                    gv = (p.dfinal_state && ch_ok) ? p.dfinal_state[row * p.d + c0 + m] : 0.f;
                 }
-                g_sm[slot0 * DT + m] = gv;
+                for (int u = 0; u < nsub; ++u) {
+                    const int c0u = (dt0 + u) * DT;
+                    const bool ok = c0u + m < p.d;
+                    const int slot0 = (it + u) % kBwdCRing;
+                    hs_sm[slot0 * DT + m] =
+                        ok ? p.tile_states[(row * p.n_tiles + (pc.k1 - 1)) * p.d + c0u + m] : 0.f;
+                    float gv;
+                    if (pc.k1 < p.n_tiles)
+                        gv = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x + 1) * kCarryFloats + u * DT + m);
+                    else
+                        gv = (p.dfinal_state && ok) ? p.dfinal_state[row * p.d + c0u + m] : 0.f;
+                    g_sm[slot0 * DT + m] = gv;
+                }
             }
             bar_sync(1, kEpiThreads);
-            if (m == 0) mbar_arrive(bar(B_G + (it & (kRing - 1))));
-            if (loader && lane == 0) mbar_arrive(bar(B_G + (it & (kRing - 1))));
-            for (int k = pc.k1 - 1; k >= pc.k0; --k, ++it) {
-                const int acc = it & 1, slot = it & (kRing - 1), nslot = (it + 1) & (kRing - 1);
-                const uint32_t aph = (it >> 1) & 1, gph = (it / kRing) & 1;
-                if (per_step || hi != cur_head) { cur_head = hi; ++mt; }
+            for (int u = 0; u < nsub; ++u) {
+                if (m == 0) mbar_arrive(bar(B_G + (it + u) % kBwdCRing));
+                if (loader && lane == 0) mbar_arrive(bar(B_G + (it + u) % kBwdCRing));
+            }
+            for (int k = pc.k1 - 1; k >= pc.k0; --k)
+            for (int u = 0; u < nsub; ++u, ++it) {
+                const int dtile = dt0 + u;
+                const int c0 = dtile * DT;
+                const bool ch_ok = loader && c0 + m < p.d;
+                const float *ts_item = p.tile_states + row * p.n_tiles * p.d + c0 + m;
+                // Partial sums of the decay gradient, in the layout of the CUDA-core kernel (so that a suffix re-scan by
+                // that kernel can overwrite some tiles of a pass made by this one): one slice per 64 channels,
+                // [row][slice][t] for a per-step decay, [row][slice][tile][8] for a per-head decay.
+                const int slice = 2 * dtile + half;
+                const bool slice_ok = slice < p.n_dt64;   // the second half of the last tile may hold no channels
+                float *dap_step = p.da_partial + (row * p.n_dt64 + slice) * (static_cast<int64_t>(p.n_tiles) * QT);
+                float *dap_head = p.da_partial + p.head_partial_offset + (row * p.n_dt64 + slice) * p.n_tiles * 8;
+                const int acc = it & 1, slot = it % kBwdCRing, nslot = (it + nsub) % kBwdCRing;
+                const uint32_t aph = (it >> 1) & 1, gph = (it / kBwdCRing) & 1;
+                if (u == 0 && (per_step || hi != cur_head)) { cur_head = hi; ++mt; }
                 // prefetch the saved state of the next tile to the left while this one is being finished
                 if (loader && k > pc.k0) hs_next = ch_ok ? ts_item[static_cast<int64_t>(k - 1) * p.d] : 0.f;
                 if (lane == 0) mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 15);
@@ -1060,7 +1133,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                                 *reinterpret_cast<float4 *>(gout + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
                             if (pass == 1) mbar_arrive(bar(B_G + nslot));
                         } else if (publish) {   // the tile on the left is another CTA's
-                            float *co = carry_out + cb;
+                            float *co = carry_out + u * DT + cb;
 #pragma unroll
                             for (int c = 0; c < 32; c += 4)
                                 *reinterpret_cast<float4 *>(co + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
@@ -1148,16 +1221,17 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             builder_scan(l2, bt, cs_sm, wt_sm, to_end, from_start);
             if (row_owner) {
                 const float pw = conv ? 1.f : 1.f - v;
-                p_sm[r] = pw;
-                wlo_sm[r] = pw * ex2_approx(to_end);
-                rup_sm[r] = ex2_approx(from_start);
+                const float pws = pw * static_cast<float>(1 << kHalfShift);
+                p_sm[r] = __float2half_rn(pws);
+                wlo_sm[r] = __float2half_rn(pws * ex2_approx(to_end));
+                rup_sm[r] = __float2half_rn(ex2_approx(from_start));
             }
             bar_sync(2, kBuildThreads);
             RowChunks ca, cu;
-            compute_diag_lower<1>(dga, cs_b, p_b, diag, ca);
-            compute_off<false, true>(oga, cs_b, wlo_b, ca);
+            compute_diag_lower_half<1>(dga, cs_b, p_b, diag, ca);
+            compute_off_half<false>(oga, cs_b, wlo_b, ca);
             compute_diag_upper(dgu, cs_b, cu);
-            compute_off<true, true>(ogu, cs_b, rup_b, cu);
+            compute_off_half<true>(ogu, cs_b, rup_b, cu);
             const float cs_r = cs_sm[r];
             const float Eprev = ex2_approx(cs_r - l2);                       // prod_{j<r} a_j
             const float Fr = ex2_approx(cs_sm[QT - 1] - cs_r + log2_decay(v_edge));
@@ -1179,7 +1253,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         const float ident = conv ? 0.f : 1.f;  // raw value of an identity step
         for (int pi = 0; pi < sched.n; ++pi) {
             const Piece pc = sched.get<false>(pi);
-            const int64_t row = pc.item / p.n_dtiles;
+            const int64_t row = item_row(pc.item);
             const int64_t bi = row / p.h, hi = row % p.h;
             const float *arow = p.decay + (per_step ? bi * p.a_sb + hi * p.a_sh : hi * p.a_sh);
             if (!per_step) {
@@ -1405,7 +1479,14 @@ int launch_fused_bwd_tc(const FusedParams &fp, cudaStream_t stream) {
     p.decay_mode = fp.decay_mode; p.convention = fp.convention;
     p.n_tiles = static_cast<int>((fp.L + tc::QT - 1) / tc::QT);
     p.n_dtiles = static_cast<int>((fp.d + tc::DT - 1) / tc::DT);
-    p.n_items = static_cast<int>(fp.b * fp.h * p.n_dtiles);
+    {   // same pairing rule as the forward kernel
+        const int64_t rows = fp.b * fp.h, sms = sm_count();
+        const int64_t single = rows * p.n_dtiles, paired = rows * ((p.n_dtiles + 1) / 2);
+        const int64_t busy_single = single < sms ? single : sms, busy_paired = paired < sms ? paired : sms;
+        p.sub = (fp.decay_mode == EMA_DECAY_PER_STEP && p.n_dtiles > 1 && busy_paired * 100 >= busy_single * 85) ? 2 : 1;
+    }
+    p.n_groups = (p.n_dtiles + p.sub - 1) / p.sub;
+    p.n_items = static_cast<int>(fp.b * fp.h * p.n_groups);
     p.n_dt64 = static_cast<int>((fp.d + 63) / 64);
     p.head_partial_offset = kHeadPartialOffset(fp.b * fp.h);
     int grid = 0;
