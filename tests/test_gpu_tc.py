@@ -212,6 +212,30 @@ def test_decays_from_zero_to_one(dtype, _lib):
         assert np.abs(r["ddecay"].cpu().numpy() - da_ref).max() <= 1e-4 + 2e-5 * np.abs(da_ref).max()
 
 
+def test_many_restarts_inside_a_tile(_lib):
+    """Short packed sequences: a decay of exactly 0 every third step (the state restarts there) and slow decays in
+    between.  The prefix sums of the log decays inside a tile cross dozens of such steps and must stay precise."""
+    E = _E()
+    b, L, h, d = 2, 520, 2, 256
+    x, a, dy, _ = make_inputs(47, b, L, h, d, lo=3.0, hi=8.0, per_head=False, dtype=torch.bfloat16)
+    a = a.clone()
+    a[:, ::3] = 0.0
+    np_in = (x.float().cpu().numpy(), a.cpu().numpy(), dy.float().cpu().numpy())
+    f = E.ops.ema_fwd(x, a, want_tile_states=True)
+    r = E.ops.ema_bwd(x, a, dy, f["tile_states"])
+    torch.cuda.synchronize()
+    assert _lib.ema_b200_last_path() == 1
+    y_ref, dx_ref, da_ref = oracle_fwd_bwd(np_in)
+    assert_close_bf16(f["y"], y_ref, "y")
+    assert_close_bf16(r["dx"], dx_ref, "dx")
+    assert_close_bf16(r["ddecay"], da_ref, "da")
+    # the steps between restarts carry small weights (1 - a down to 3e-4): check them on their own scale
+    mid = np.ones(L, dtype=bool)
+    mid[::3] = False
+    got, ref = r["dx"].float().cpu().numpy()[:, mid], dx_ref[:, mid]
+    assert np.abs(got - ref).max() <= 2e-2 * np.abs(ref).max()
+
+
 def test_calls_can_be_captured_in_cuda_graphs(_lib):
     """With caller-provided buffers a forward and a backward call only queue stream work (kernels and two small
     memsets), so they capture into CUDA graphs; a replay must reproduce the eager results bit for bit."""
