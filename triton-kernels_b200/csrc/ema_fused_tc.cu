@@ -52,7 +52,7 @@ constexpr int kBuildThreads = 256;
 constexpr int kBuildWarps = kBuildThreads / 32;
 // registers per thread after the role split; 128*48 + 256*136 + 256*80 = 640*96, the allocation at launch
 constexpr int kRegsLight = 48, kRegsEpilogue = 136, kRegsBuilder = 80;
-constexpr int kRing = 4;                   // depth of the carry ring and of the per-row scalar tables
+constexpr int kRing = 4;                   // depth of the forward kernel's ring of per-build carry factors
 constexpr uint32_t kIdesc = make_idesc_bf16(QT, DT, 0, 1);
 
 // named barriers (id 0 is __syncthreads)
