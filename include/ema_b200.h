@@ -138,6 +138,20 @@ int ema_b200_fwd(const ema_b200_problem *p, const void *x, const float *decay, v
                  float *log_decay_sum, float stop_below, void *workspace, size_t workspace_bytes,
                  void *stream);
 
+/* Forward scan with per-step weights folded into the same pass:
+ *     s_t = a_t s_{t-1} + in_weight_t x_t ,     y_t = out_weight_t s_t
+ * Replaces the elementwise passes over x and over the result that surround the scan in the heads-style entry point
+ * ema_chunk_scan_combined (kernels/ema_combined.py:100-128) for state size 1: in_weight = dt' B, out_weight = C,
+ * decay = dt' A as a log decay (dt' as in kernels/ema_kernels/ema_chunk_state.py:69-78).
+ *   in_weight   optional [b, L, h] fp32 with the decay's strides; null: the convention's weight (1 - a, or 1)
+ *   out_weight  optional [b, L, h] fp32 with the decay's strides; null: 1
+ * Needs a per-step decay (EMA_ERR_UNSUPPORTED otherwise).  chunk_states, tile_states and final_state receive the
+ * states s themselves, not the weighted output.  Everything else as in ema_b200_fwd. */
+int ema_b200_fwd_weighted(const ema_b200_problem *p, const void *x, const float *decay, const float *in_weight,
+                          const float *out_weight, void *y, float *chunk_states, float *tile_states,
+                          const float *init_state, float *final_state, float *log_decay_sum, float stop_below,
+                          void *workspace, size_t workspace_bytes, void *stream);
+
 /* Backward scan: reads x, dy and the saved tile states once, writes dx and d(decay).
  * Replaces the nine launches and the torch glue of _ema_chunk_scan_combined_bwd
  * (kernels/ema_kernels_bwd/ema_combined_bwd.py:13-82).

@@ -87,6 +87,11 @@ def test_null_and_misaligned_pointers(ema_lib):
     assert ema_lib.ema_b200_bwd(ctypes.byref(p), ok, ok, ok, ok, ok, ok, None, None, f0, ok, 16, None) == -6
     assert ema_lib.ema_b200_bwd(ctypes.byref(p), ok, ok, None, ok, ok, ok, None, None, f0, ok, 1 << 30, None) == -1
     assert ema_lib.ema_b200_set_path(5) == -1
+    # weighted forward: per-step weights need a per-step decay; weights are fp32
+    ph = _problem(decay_mode=1)
+    assert ema_lib.ema_b200_fwd_weighted(ctypes.byref(ph), ok, ok, ok, None, ok, None, None, None, None, None, f0, None, 0, None) == -3
+    assert ema_lib.ema_b200_fwd_weighted(ctypes.byref(p), ok, ok, ctypes.c_void_p(258), None, ok, None, None, None, None, None, f0, None, 0, None) == -2
+    assert ema_lib.ema_b200_fwd_weighted(ctypes.byref(p), None, ok, ok, ok, ok, None, None, None, None, None, f0, None, 0, None) == -1
 
 
 def test_stage_entry_points_reject_bad_sizes(ema_lib):

@@ -1,0 +1,101 @@
+"""Forward scan with per-step weights folded into the pass (ema_b200_fwd_weighted):
+
+    s_t = a_t s_{t-1} + w_t x_t ,     y_t = c_t s_t
+
+against the CPU oracle run on the explicitly weighted input (u = w x in fp32, pre-scaled convention) and scaled
+afterwards.  This is what the heads-style entry point (kernels/ema_combined.py of the reference) computes with
+w = dt' B and c = C for state size 1.  Both kernel families, either weight alone, states unweighted.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import BF16_REL
+from oracle import ema_oracle as eo
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(seed, b, L, h, d, dtype):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn((b, L, h, d), generator=g, device="cuda", dtype=torch.float32).to(dtype)
+    a = torch.sigmoid(1.0 + 5.0 * torch.rand((b, L, h), generator=g, device="cuda"))
+    w = 0.05 + 1.5 * torch.rand((b, L, h), generator=g, device="cuda")
+    c = torch.randn((b, L, h), generator=g, device="cuda")
+    return x, a, w, c
+
+
+def _reference(x, a, w, c, init=None):
+    """(y, s) in float64-accumulated fp32: the states s and the weighted output y."""
+    xn = x.float().cpu().numpy()
+    u = xn if w is None else xn * w.cpu().numpy()[..., None]
+    A = np.log(a.cpu().numpy().astype(np.float64)).astype(np.float32)
+    s = eo.fwd(np.ascontiguousarray(u, dtype=np.float32), A, convention=eo.REFERENCE, acc64=True)
+    assert init is None
+    y = s if c is None else s * c.cpu().numpy()[..., None]
+    return y, s
+
+
+def _check(got, ref, dtype, what):
+    g = got.float().cpu().numpy()
+    if dtype == torch.float32:
+        assert np.abs(g - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max()), what
+    else:
+        assert np.abs(g - ref).max() <= BF16_REL * np.abs(ref).max(), what
+
+
+SHAPES = [
+    (2, 300, 2, 64),
+    (1, 1000, 3, 100),     # d not a multiple of 8: narrow vectors in the CUDA-core kernel, ragged channel tile otherwise
+    (2, 129, 2, 24),
+    (5, 300, 2, 1024),     # bf16: work items of two channel tiles
+    (19, 300, 8, 256),     # bf16: 304 two-tile items, cut across thread blocks
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("which", ["both", "in", "out"])
+def test_weighted_forward_matches_oracle(shape, dtype, which, ema_lib):
+    from ema_b200 import ops
+    b, L, h, d = shape
+    x, a, w, c = _inputs(300 + L + d, b, L, h, d, dtype)
+    if which == "in":
+        c = None
+    if which == "out":
+        w = None
+    log_a = torch.log(a)
+    r = ops.ema_fwd(x, log_a, prescaled_log=True, in_weight=w, out_weight=c, want_final=True, want_tile_states=True)
+    torch.cuda.synchronize()
+    if dtype == torch.bfloat16 and d % 8 == 0:
+        assert ema_lib.ema_b200_last_path() == 1
+    y_ref, s_ref = _reference(x, a, w, c)
+    _check(r["y"], y_ref, dtype, "y")
+    _check(r["final_state"], np.ascontiguousarray(s_ref[:, -1]), dtype, "final state (unweighted)")
+    # saved states: the state entering every 128-step tile, unweighted
+    nt = r["tile_states"].shape[1]
+    ts = r["tile_states"].view(b, h, nt, d).float().cpu().numpy()
+    for k in range(1, nt):
+        ref_k = s_ref[:, 128 * k - 1]      # [b, h, d]
+        err = np.abs(ts[:, :, k] - ref_k).max()
+        assert err <= (1e-4 if dtype == torch.float32 else BF16_REL) * max(1.0, np.abs(s_ref).max()), f"tile state {k}"
+    assert ema_lib.ema_b200_device_status(0) == 0
+
+
+def test_input_weight_replaces_the_conventions_weight(ema_lib):
+    """With the decay given as `a` (not its log) the input weight still replaces 1 - a; in_weight = 1 - a gives the
+    plain EMA bit for bit in fp32."""
+    from ema_b200 import ops
+    x, a, _, _ = _inputs(11, 2, 520, 2, 128, torch.float32)
+    plain = ops.ema_fwd(x, a)["y"]
+    weighted = ops.ema_fwd(x, a, in_weight=(1.0 - a))["y"]
+    assert torch.equal(plain, weighted)
+
+
+def test_weights_need_a_per_step_decay(ema_lib):
+    from ema_b200 import ops
+    x, a, w, _ = _inputs(12, 1, 64, 2, 32, torch.float32)
+    with pytest.raises(ValueError):
+        ops.ema_fwd(x, a[0, 0].contiguous(), in_weight=w)
+    with pytest.raises(ValueError):
+        ops.ema_fwd(x, a, in_weight=w[:, :10])

@@ -137,12 +137,14 @@ extern "C" size_t ema_b200_fwd_workspace_bytes(const ema_b200_problem *p) {
     return sync_bytes(p);
 }
 
-extern "C" int ema_b200_fwd(const ema_b200_problem *p, const void *x, const float *decay, void *y,
-                            float *chunk_states, float *tile_states, const float *init_state,
-                            float *final_state, float *log_decay_sum, float stop_below, void *workspace,
-                            size_t workspace_bytes, void *stream) {
+static int fwd_impl(const ema_b200_problem *p, const void *x, const float *decay, const float *in_weight,
+                    const float *out_weight, void *y, float *chunk_states, float *tile_states,
+                    const float *init_state, float *final_state, float *log_decay_sum, float stop_below,
+                    void *workspace, size_t workspace_bytes, void *stream) {
     int rc = check_problem(p);
     if (rc) return rc;
+    if ((in_weight || out_weight) && p->decay_mode != EMA_DECAY_PER_STEP) return EMA_ERR_UNSUPPORTED;
+    if (!aligned(in_weight, 4) || !aligned(out_weight, 4)) return EMA_ERR_ALIGN;
     if (chunk_states && p->chunk <= 0) return EMA_ERR_BADARG;
     if (!(stop_below >= 0.f)) return EMA_ERR_BADARG;
     const size_t es = p->dtype == EMA_F32 ? 4 : 2;
@@ -169,6 +171,7 @@ extern "C" int ema_b200_fwd(const ema_b200_problem *p, const void *x, const floa
     FusedParams fp;
     fill_params(fp, p, vec);
     fp.x = x; fp.decay = decay; fp.out = y;
+    fp.in_weight = in_weight; fp.out_weight = out_weight;
     fp.chunk_states = chunk_states; fp.tile_states = tile_states;
     fp.init_state = init_state; fp.final_state = final_state;
     fp.log_decay_sum = log_decay_sum;
@@ -187,6 +190,23 @@ extern "C" int ema_b200_fwd(const ema_b200_problem *p, const void *x, const floa
     }
     g_last_path = 0;
     return launch_fused_fwd_fma(fp, p->dtype, vec, st);
+}
+
+extern "C" int ema_b200_fwd(const ema_b200_problem *p, const void *x, const float *decay, void *y,
+                            float *chunk_states, float *tile_states, const float *init_state,
+                            float *final_state, float *log_decay_sum, float stop_below, void *workspace,
+                            size_t workspace_bytes, void *stream) {
+    return fwd_impl(p, x, decay, nullptr, nullptr, y, chunk_states, tile_states, init_state, final_state,
+                    log_decay_sum, stop_below, workspace, workspace_bytes, stream);
+}
+
+extern "C" int ema_b200_fwd_weighted(const ema_b200_problem *p, const void *x, const float *decay,
+                                     const float *in_weight, const float *out_weight, void *y,
+                                     float *chunk_states, float *tile_states, const float *init_state,
+                                     float *final_state, float *log_decay_sum, float stop_below,
+                                     void *workspace, size_t workspace_bytes, void *stream) {
+    return fwd_impl(p, x, decay, in_weight, out_weight, y, chunk_states, tile_states, init_state, final_state,
+                    log_decay_sum, stop_below, workspace, workspace_bytes, stream);
 }
 
 extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const float *decay, const void *dy,

@@ -13,6 +13,10 @@ namespace ema {
 struct FusedParams {
     const void *x;
     const float *decay;
+    // forward only, optional: per-step input weights [b, L, h] replacing the convention's (1 - a or 1), and per-step
+    // output weights applied to what is written (the states stay unweighted); both with the decay's strides
+    const float *in_weight;
+    const float *out_weight;
     const void *dy;
     void *out;  // y (forward) or dx (backward)
     float *chunk_states;

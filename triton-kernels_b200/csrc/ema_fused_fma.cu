@@ -25,11 +25,16 @@ __device__ __forceinline__ raw_t<T, VEC> load_or_zero(const T *p, bool ok) {
 // ------------------------------------------------------------------------------------------------
 // forward
 // ------------------------------------------------------------------------------------------------
-template <typename T, int VEC>
+// WEIGHTED: the input weight of step t is in_weight[b,t,h] instead of the convention's (1 - a_t or 1), and what is
+// written is out_weight[b,t,h] * state (when given); the saved, chunk and final states are the states themselves.
+template <typename T, int VEC, bool WEIGHTED>
 __global__ void __launch_bounds__(kFmaThreads) ema_fwd_fma_kernel(const FusedParams p) {
     constexpr int CT = kFmaCT, SB = kFmaSB, NS = kFmaNS, QT = kFmaTile, DT = CT * VEC;
     using R = raw_t<T, VEC>;
+    constexpr int WQ = WEIGHTED ? QT : 1;   // the weight tables exist only in the weighted kernel
     __shared__ float a_sm[2][QT];
+    __shared__ float w_sm[2][WQ];   // input weights of the tile
+    __shared__ float c_sm[2][WQ];   // output weights
     __shared__ float S_sm[2][NS][DT];
     __shared__ float P_sm[2][NS];
     __shared__ float h_sm[2][DT];
@@ -56,6 +61,12 @@ __global__ void __launch_bounds__(kFmaThreads) ema_fwd_fma_kernel(const FusedPar
         const float v = arow[static_cast<int64_t>(t) * p.a_sl];
         return conv ? expf(v) : v;
     };
+    // per-step weights share the decay's strides; a missing tensor means weight 1
+    const int64_t w_off = bi * p.a_sb + hi * p.a_sh;
+    auto load_w = [&](const float *w, int t) -> float {
+        if (!w) return 1.f;
+        return t < L ? w[w_off + static_cast<int64_t>(t) * p.a_sl] : 0.f;
+    };
 
     float h[VEC];
 #pragma unroll
@@ -66,6 +77,12 @@ __global__ void __launch_bounds__(kFmaThreads) ema_fwd_fma_kernel(const FusedPar
         for (int v = 0; v < VEC; ++v) h_sm[0][lc * VEC + v] = h[v];
     }
     if (tid < QT) a_sm[0][tid] = load_a(tid);
+    if constexpr (WEIGHTED) {
+        if (tid < QT) {
+            w_sm[0][tid] = load_w(p.in_weight, tid);
+            c_sm[0][tid] = load_w(p.out_weight, tid);
+        }
+    }
 
     R cur[SB], nxt[SB];
 #pragma unroll
@@ -80,7 +97,7 @@ __global__ void __launch_bounds__(kFmaThreads) ema_fwd_fma_kernel(const FusedPar
         const int par = k & 1;
         const int t0 = k * QT + sub * SB;
         const bool more = k + 1 < p.n_tiles;
-        float a_pref = 1.f;
+        float a_pref = 1.f, w_pref = 0.f, c_pref = 0.f;
         if (more) {
 #pragma unroll
             for (int s = 0; s < SB; ++s) {
@@ -88,6 +105,12 @@ __global__ void __launch_bounds__(kFmaThreads) ema_fwd_fma_kernel(const FusedPar
                 nxt[s] = load_or_zero<T, VEC>(xrow + static_cast<int64_t>(t) * p.x_sl, c_ok && t < L);
             }
             if (tid < QT) a_pref = load_a((k + 1) * QT + tid);
+            if constexpr (WEIGHTED) {
+                if (tid < QT) {
+                    w_pref = load_w(p.in_weight, (k + 1) * QT + tid);
+                    c_pref = load_w(p.out_weight, (k + 1) * QT + tid);
+                }
+            }
         }
 
         // phase 1: local scan from a zero state
@@ -102,7 +125,7 @@ __global__ void __launch_bounds__(kFmaThreads) ema_fwd_fma_kernel(const FusedPar
         for (int s = 0; s < SB; ++s) {
             float xf[VEC];
             unpack<T, VEC>(cur[s], xf);
-            const float pw = conv ? 1.f : 1.f - a_r[s];
+            const float pw = WEIGHTED ? w_sm[par][(sub * SB + s) % WQ] : (conv ? 1.f : 1.f - a_r[s]);
 #pragma unroll
             for (int v = 0; v < VEC; ++v) st[v] = fmaf(a_r[s], st[v], pw * xf[v]);
             Pl *= a_r[s];
@@ -111,6 +134,12 @@ __global__ void __launch_bounds__(kFmaThreads) ema_fwd_fma_kernel(const FusedPar
         for (int v = 0; v < VEC; ++v) S_sm[par][sub][lc * VEC + v] = st[v];
         if (lc == 0) P_sm[par][sub] = Pl;
         if (more && tid < QT) a_sm[par ^ 1][tid] = a_pref;
+        if constexpr (WEIGHTED) {
+            if (more && tid < QT) {
+                w_sm[par ^ 1][tid] = w_pref;
+                c_sm[par ^ 1][tid] = c_pref;
+            }
+        }
         __syncthreads();
 
         // carry: state entering this sub-block
@@ -144,12 +173,22 @@ __global__ void __launch_bounds__(kFmaThreads) ema_fwd_fma_kernel(const FusedPar
         for (int s = 0; s < SB; ++s) {
             float xf[VEC];
             unpack<T, VEC>(cur[s], xf);
-            const float pw = conv ? 1.f : 1.f - a_r[s];
+            const float pw = WEIGHTED ? w_sm[par][(sub * SB + s) % WQ] : (conv ? 1.f : 1.f - a_r[s]);
 #pragma unroll
             for (int v = 0; v < VEC; ++v) h[v] = fmaf(a_r[s], h[v], pw * xf[v]);
             const int t = t0 + s;
             if (c_ok && t < L) {
-                if (p.out) st_stream<T, VEC>(yrow + static_cast<int64_t>(t) * p.o_sl, pack<T, VEC>(h));
+                if constexpr (WEIGHTED) {
+                    if (p.out) {
+                        const float cw = c_sm[par][(sub * SB + s) % WQ];
+                        float ys[VEC];
+#pragma unroll
+                        for (int v = 0; v < VEC; ++v) ys[v] = cw * h[v];
+                        st_stream<T, VEC>(yrow + static_cast<int64_t>(t) * p.o_sl, pack<T, VEC>(ys));
+                    }
+                } else {
+                    if (p.out) st_stream<T, VEC>(yrow + static_cast<int64_t>(t) * p.o_sl, pack<T, VEC>(h));
+                }
                 if (p.chunk_states) {
                     // y_t is the state at the start of chunk (t+1)/chunk when t+1 is a boundary
                     if (c_rem == 0 && t + 1 < L) {
@@ -499,7 +538,10 @@ __global__ void da_reduce_head_kernel(const double *__restrict__ row_sum, float 
 template <typename T, int VEC>
 int launch_fwd(const FusedParams &p, cudaStream_t stream) {
     const int64_t blocks = p.b * p.h * p.n_dtiles;
-    ema_fwd_fma_kernel<T, VEC><<<static_cast<unsigned>(blocks), kFmaThreads, 0, stream>>>(p);
+    if (p.in_weight || p.out_weight)
+        ema_fwd_fma_kernel<T, VEC, true><<<static_cast<unsigned>(blocks), kFmaThreads, 0, stream>>>(p);
+    else
+        ema_fwd_fma_kernel<T, VEC, false><<<static_cast<unsigned>(blocks), kFmaThreads, 0, stream>>>(p);
     return check_launch();
 }
 template <typename T, int VEC, bool PF>

@@ -296,6 +296,9 @@ __device__ __forceinline__ uint64_t tile_desc(uint32_t addr) { return make_desc_
 struct TcParams {
     const float *decay;
     float *chunk_states, *tile_states, *final_state, *log_decay_sum;
+    // optional per-step weights [b, L, h] with the decay's strides (per-step decay only): in_weight replaces the
+    // convention's input weight inside the decay matrix, out_weight scales the rows of what is written
+    const float *in_weight, *out_weight;
     const float *init_state;
     int64_t b, L, h, d;
     int64_t a_sb, a_sl, a_sh;
@@ -614,6 +617,11 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 const int acc = it & 1, slot = it & (kFwdHRing - 1), s = it % kFwdStages;
                 const uint32_t aph = (it >> 1) & 1, hph = (it / kFwdHRing) & 1;
                 if (u == 0 && (per_step || hi != cur_head)) { cur_head = hi; ++mt; }
+                float out_w = 1.f;   // fetched before the wait, used after the side outputs
+                if (p.out_weight) {
+                    const int tw = k * QT + m;
+                    out_w = tw < L ? p.out_weight[(row / p.h) * p.a_sb + static_cast<int64_t>(tw) * p.a_sl + hi * p.a_sh] : 0.f;
+                }
                 if (lane == 0) mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 5);  // one poller per warp
                 __syncwarp();
                 tc_fence_after_sync();
@@ -672,6 +680,10 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                                 atomicAdd(p.flags + blockIdx.x + 1, 1u);
                             }
                         }
+                    }
+                    if (p.out_weight) {   // (uniform branch; the states above are the unweighted ones)
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) y[c] *= out_w;
                     }
                     // bf16 -> the stage, in the TMA's 128-byte swizzle
 #pragma unroll
@@ -747,13 +759,16 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             float logsum = 0.f;
             const float ident = conv ? 0.f : 1.f;   // raw value of an identity step (past L)
             float v_next = (row_owner && pc.k0 * QT + r < L) ? arow[static_cast<int64_t>(pc.k0 * QT + r) * p.a_sl] : ident;
+            const float *wrow = p.in_weight ? p.in_weight + bi * p.a_sb + hi * p.a_sh : nullptr;
+            float w_next = (wrow && row_owner && pc.k0 * QT + r < L) ? wrow[static_cast<int64_t>(pc.k0 * QT + r) * p.a_sl] : 0.f;
             for (int k = pc.k0; k < pc.k1; ++k) {
-                const float v = v_next;
+                const float v = v_next, w = w_next;
                 if (k + 1 < pc.k1) {
                     const int t = (k + 1) * QT + r;
                     v_next = (row_owner && t < L) ? arow[static_cast<int64_t>(t) * p.a_sl] : ident;
+                    if (wrow) w_next = (row_owner && t < L) ? wrow[static_cast<int64_t>(t) * p.a_sl] : 0.f;
                 }
-                build(log2_decay(v), conv ? 1.f : 1.f - v);
+                build(log2_decay(v), wrow ? w : (conv ? 1.f : 1.f - v));
                 // cs_sm[127] now holds log2 of the product of this tile's decays
                 if (p.log_decay_sum && bt == 0) logsum += cs_sm[QT - 1] * 0.6931471805599453f;
             }
@@ -1433,6 +1448,7 @@ int launch_fused_fwd_tc(const FusedParams &fp, cudaStream_t stream) {
     p.decay = fp.decay;
     p.chunk_states = fp.chunk_states; p.tile_states = fp.tile_states; p.final_state = fp.final_state;
     p.log_decay_sum = fp.log_decay_sum; p.init_state = fp.init_state;
+    p.in_weight = fp.in_weight; p.out_weight = fp.out_weight;
     p.b = fp.b; p.L = fp.L; p.h = fp.h; p.d = fp.d;
     p.a_sb = fp.a_sb; p.a_sl = fp.a_sl; p.a_sh = fp.a_sh;
     p.decay_mode = fp.decay_mode; p.convention = fp.convention; p.chunk = fp.chunk;

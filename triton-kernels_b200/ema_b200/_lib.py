@@ -60,6 +60,7 @@ def lib():
         "ema_b200_bwd_workspace_bytes": (sz, [pp]),
         "ema_b200_fwd_workspace_bytes": (sz, [pp]),
         "ema_b200_fwd": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp, sz, vp]),
+        "ema_b200_fwd_weighted": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp, sz, vp]),
         "ema_b200_bwd": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp, sz, vp]),
         "ema_b200_static_scratch_limit": (sz, []),
         "ema_b200_bwd_static_scratch": (ci, [pp, vp, vp, vp, vp, vp, vp, vp]),

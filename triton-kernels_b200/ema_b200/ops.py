@@ -60,7 +60,7 @@ def n_tiles_of(x, decay, convention=CONV_NORTH_STAR):
 
 def ema_fwd(x, decay, *, chunk=0, prescaled_log=False, init_state=None, want_chunk_states=False,
             want_tile_states=False, want_final=False, want_log_decay_sum=False, stop_below=0.0,
-            out=None, tile_states=None, workspace=None):
+            out=None, tile_states=None, workspace=None, in_weight=None, out_weight=None):
     """Forward scan.  Returns a dict with 'y' and the requested extras.
 
     x[b,L,h,d] (fp32|bf16, last dim contiguous), decay a[b,L,h] or a[h] (fp32).
@@ -68,10 +68,25 @@ def ema_fwd(x, decay, *, chunk=0, prescaled_log=False, init_state=None, want_chu
     `out` / `tile_states` let a caller re-scan a prefix in place (sequence-parallel fix-up).
     `workspace` (returned as 'fwd_workspace') is the small scratch that lets the kernels spread uneven work
     over all SMs; pass it back in to avoid the allocation, never to two calls that may overlap.
+    `in_weight` / `out_weight` (fp32 [b,L,h], per-step decay only) fold per-step weights into the same pass:
+    s_t = a_t s_{t-1} + in_weight_t x_t, y_t = out_weight_t s_t; the returned states are the s themselves.
     """
     x, decay = _check_inputs(x, decay)
-    dev = require_cuda(x, decay, init_state, out, tile_states)
+    dev = require_cuda(x, decay, init_state, out, tile_states, in_weight, out_weight)
     b, L, h, d = x.shape
+    weighted = in_weight is not None or out_weight is not None
+    if weighted:
+        if decay.dim() != 3:
+            raise ValueError("per-step weights need a per-step decay [b, L, h]")
+        decay = decay.contiguous()
+
+        def _as_weight(w, name):
+            if w is None:
+                return None
+            if tuple(w.shape) != (b, L, h) or w.dtype != torch.float32:
+                raise ValueError(f"{name} must be fp32 [b, L, h]")
+            return w.contiguous()   # the kernels index the weights with the decay's strides
+        in_weight, out_weight = _as_weight(in_weight, "in_weight"), _as_weight(out_weight, "out_weight")
     conv = CONV_PRESCALED_LOG if prescaled_log else CONV_NORTH_STAR
     y = out if out is not None else torch.empty((b, L, h, d), dtype=x.dtype, device=dev)
     p = _problem(x, decay, y, convention=conv, chunk=chunk)
@@ -102,11 +117,17 @@ def ema_fwd(x, decay, *, chunk=0, prescaled_log=False, init_state=None, want_chu
     if workspace is None and ws_bytes > 0:
         workspace = torch.empty(((ws_bytes + 3) // 4,), dtype=torch.float32, device=dev)
     res["fwd_workspace"] = workspace
+    ws_size = ctypes.c_size_t(0 if workspace is None else workspace.numel() * 4)
     with torch.cuda.device(dev):
-        rc = L_.ema_b200_fwd(ctypes.byref(p), ptr(x), ptr(decay), ptr(y), ptr(cs), ptr(ts), ptr(init_state),
-                             ptr(fin), ptr(lds), ctypes.c_float(stop_below), ptr(workspace),
-                             ctypes.c_size_t(0 if workspace is None else workspace.numel() * 4), stream_ptr(dev))
-    check("ema_b200_fwd", rc)
+        if weighted:
+            rc = L_.ema_b200_fwd_weighted(ctypes.byref(p), ptr(x), ptr(decay), ptr(in_weight), ptr(out_weight), ptr(y),
+                                          ptr(cs), ptr(ts), ptr(init_state), ptr(fin), ptr(lds),
+                                          ctypes.c_float(stop_below), ptr(workspace), ws_size, stream_ptr(dev))
+        else:
+            rc = L_.ema_b200_fwd(ctypes.byref(p), ptr(x), ptr(decay), ptr(y), ptr(cs), ptr(ts), ptr(init_state),
+                                 ptr(fin), ptr(lds), ctypes.c_float(stop_below), ptr(workspace), ws_size,
+                                 stream_ptr(dev))
+    check("ema_b200_fwd_weighted" if weighted else "ema_b200_fwd", rc)
     return res
 
 

@@ -9,7 +9,9 @@ weight, C = 1, kernels/benchmarks/ema_bench.py:104-117):
     s_t  = exp(dt'_t A_h) s_{t-1} + dt'_t B_t x_t ,     y_t = C_t s_t  (+ D x_t)  (* silu(z_t))
 
 The recurrence runs in the fused scan kernels (pre-scaled log-decay convention: decay = dt' A, input =
-dt' B x); what surrounds it is elementwise torch, so gradients reach every tensor argument through autograd.
+dt' B x).  Without gradients, D and z, the weights dt' B and C are folded into the scan kernel (one read of x, one
+write of the result); otherwise what surrounds the scan is elementwise torch, so gradients reach every tensor
+argument through autograd.
 The reference's own backward for this entry point is a stub that returns None for every input (:89-92).
 `seq_idx` (a sequence id per position: the state restarts from zero where the id changes, as in the reference's
 chunked kernels) is a decay of exactly 0 at the first step of every new sequence.  State sizes above 1 and
@@ -84,14 +86,11 @@ def _ema_chunk_scan_combined_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, dt_
     needs_grad = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (x, dt, A, B, C, D, z, dt_bias, initial_states))
     if not needs_grad and D is None and z is None:
-        # inference: one pass over x before the scan and one over the result after it, each written in x's dtype
-        # (the product is formed in fp32 and rounded once)
-        u = torch.empty_like(x, memory_format=torch.contiguous_format)
-        torch.mul(x, (dtp * Bh).unsqueeze(-1), out=u)
-        r = ops.ema_fwd(u, a_log.contiguous(), prescaled_log=True, init_state=init, want_final=True)
-        out = r["y"]
-        torch.mul(out, Ch.unsqueeze(-1), out=out)
-        return out, r["final_state"].unsqueeze(-1)
+        # inference: the weights dt' B (input) and C (output) go into the scan kernel itself, so x is read once and the
+        # result written once; only the [b, l, h]-sized weight tensors are prepared here
+        r = ops.ema_fwd(x, a_log.contiguous(), prescaled_log=True, init_state=init, want_final=True,
+                        in_weight=(dtp * Bh).contiguous(), out_weight=Ch.contiguous())
+        return r["y"], r["final_state"].unsqueeze(-1)
     u = (x.float() * (dtp * Bh).unsqueeze(-1)).to(x.dtype)
     s, final = _PrescaledScan.apply(u.contiguous(), a_log.contiguous(), init)
     out = s.float() * Ch.unsqueeze(-1)
