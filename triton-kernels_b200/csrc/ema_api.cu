@@ -188,6 +188,11 @@ static int fwd_impl(const ema_b200_problem *p, const void *x, const float *decay
         if (rc == EMA_OK) g_last_path = 1;
         if (rc != EMA_ERR_UNSUPPORTED) return rc;  // a tensor map the driver refuses falls through to the FMA path
     }
+    if (p->dtype == EMA_F32 && vec == 4 && tc_enabled()) {
+        rc = launch_fused_fwd_fma_tma(fp, st);
+        if (rc == EMA_OK) g_last_path = 2;
+        if (rc != EMA_ERR_UNSUPPORTED) return rc;
+    }
     g_last_path = 0;
     return launch_fused_fwd_fma(fp, p->dtype, vec, st);
 }

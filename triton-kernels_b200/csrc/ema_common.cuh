@@ -170,6 +170,8 @@ int launch_da_reduce(const FusedParams &p, float *ddecay, int tile_steps, cudaSt
 bool tc_tensor_ok(const void *base, int64_t d, int64_t sb, int64_t sl, int64_t sh, int64_t b, int64_t L, int64_t h);
 int launch_fused_fwd_tc(const FusedParams &p, cudaStream_t stream);
 int launch_fused_bwd_tc(const FusedParams &p, cudaStream_t stream);
+// fp32 forward on the CUDA cores with x brought in by TMA; p.n_dtiles must count 64-channel tiles (vec 4)
+int launch_fused_fwd_fma_tma(const FusedParams &p, cudaStream_t stream);
 int read_tc_status(int clear);
 // bytes of scratch that let the tensor-core kernels cut work items across CTAs (0 = never needed)
 size_t tc_sync_bytes(int64_t b, int64_t h, int64_t d);

@@ -32,6 +32,7 @@
 
 #include "ema_common.cuh"
 #include "ema_tc_common.cuh"
+#include "ema_fwd_fma_kernel.cuh"
 
 namespace ema {
 namespace tc {
@@ -407,6 +408,10 @@ struct FwdSmem {
 constexpr int kFwdSmemBytes = FwdSmem::total + 1024;  // + slack for the manual 1024-byte alignment
 static_assert(kFwdSmemBytes <= 227 * 1024, "forward shared memory exceeds the per-CTA limit");
 
+// WEIGHTED: per-step input weights inside the decay matrix and output weights on the rows of what is written, as its
+// own instantiation: in the plain kernel even a never-taken branch for them costs 40 % of the per-step speed (the
+// five roles' code competes for the instruction cache).
+template <bool WEIGHTED>
 __global__ void __launch_bounds__(kThreads, 1)
 ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                   const TcParams p) {
@@ -618,7 +623,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 const uint32_t aph = (it >> 1) & 1, hph = (it / kFwdHRing) & 1;
                 if (u == 0 && (per_step || hi != cur_head)) { cur_head = hi; ++mt; }
                 float out_w = 1.f;   // fetched before the wait, used after the side outputs
-                if (p.out_weight) {
+                if (WEIGHTED && p.out_weight) {
                     const int tw = k * QT + m;
                     out_w = tw < L ? p.out_weight[(row / p.h) * p.a_sb + static_cast<int64_t>(tw) * p.a_sl + hi * p.a_sh] : 0.f;
                 }
@@ -681,9 +686,13 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                             }
                         }
                     }
-                    if (p.out_weight) {   // (uniform branch; the states above are the unweighted ones)
+                    if constexpr (WEIGHTED) {   // (1 without output weights; the states above are the unweighted ones)
+                        const float2 w2 = make_float2(out_w, out_w);
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) y[c] *= out_w;
+                        for (int c = 0; c < 32; c += 2) {   // two products per instruction: the code must stay small
+                            const float2 v = __fmul2_rn(make_float2(y[c], y[c + 1]), w2);
+                            y[c] = v.x; y[c + 1] = v.y;
+                        }
                     }
                     // bf16 -> the stage, in the TMA's 128-byte swizzle
 #pragma unroll
@@ -759,16 +768,21 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             float logsum = 0.f;
             const float ident = conv ? 0.f : 1.f;   // raw value of an identity step (past L)
             float v_next = (row_owner && pc.k0 * QT + r < L) ? arow[static_cast<int64_t>(pc.k0 * QT + r) * p.a_sl] : ident;
-            const float *wrow = p.in_weight ? p.in_weight + bi * p.a_sb + hi * p.a_sh : nullptr;
-            float w_next = (wrow && row_owner && pc.k0 * QT + r < L) ? wrow[static_cast<int64_t>(pc.k0 * QT + r) * p.a_sl] : 0.f;
+            // input weights (WEIGHTED only): same strides as the decay; free of branches on the pointer (without an
+            // input-weight tensor the decay is simply read twice)
+            const bool has_w = WEIGHTED && p.in_weight != nullptr;
+            const float *wrow = (has_w ? p.in_weight : p.decay) + bi * p.a_sb + hi * p.a_sh;
+            float w_next = 0.f;
+            if constexpr (WEIGHTED)
+                w_next = (row_owner && pc.k0 * QT + r < L) ? wrow[static_cast<int64_t>(pc.k0 * QT + r) * p.a_sl] : 0.f;
             for (int k = pc.k0; k < pc.k1; ++k) {
                 const float v = v_next, w = w_next;
                 if (k + 1 < pc.k1) {
                     const int t = (k + 1) * QT + r;
                     v_next = (row_owner && t < L) ? arow[static_cast<int64_t>(t) * p.a_sl] : ident;
-                    if (wrow) w_next = (row_owner && t < L) ? wrow[static_cast<int64_t>(t) * p.a_sl] : 0.f;
+                    if constexpr (WEIGHTED) w_next = (row_owner && t < L) ? wrow[static_cast<int64_t>(t) * p.a_sl] : 0.f;
                 }
-                build(log2_decay(v), wrow ? w : (conv ? 1.f : 1.f - v));
+                build(log2_decay(v), has_w ? w : (conv ? 1.f : 1.f - v));
                 // cs_sm[127] now holds log2 of the product of this tile's decays
                 if (p.log_decay_sum && bt == 0) logsum += cs_sm[QT - 1] * 0.6931471805599453f;
             }
@@ -1311,6 +1325,84 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 }  // namespace tc
 
 // ---------------------------------------------------------------------------------------------
+// fp32 forward on the CUDA cores, fed by TMA
+// ---------------------------------------------------------------------------------------------
+// The exact fp32 recurrence of the CUDA-core family (same function template, same arithmetic, bit-identical results)
+// with the x tiles brought in by TMA: a ring of three [128 steps x 64 channels] fp32 boxes per thread block and two
+// thread blocks per SM keep 192 KB of loads in flight per SM, where the register prefetch of the plain kernel
+// keeps 64 KB.  One thread issues the copies; a stage is refilled right after the tile's block-wide barrier, by which
+// time every thread has taken its values out of it.
+namespace tmafeed {
+
+constexpr int kStages = 3;
+constexpr int kChannels = kFmaCT * 4;                       // 64 channels per thread block (one TMA box)
+constexpr int kStageBytes = kFmaTile * kChannels * 4;       // 32 KB
+constexpr int kCtrlBytes = 64;                              // mbarriers, abort flag
+constexpr int kSmemBytes = kStages * kStageBytes + kCtrlBytes + 128;   // + slack to align the ring to 128 bytes
+static_assert(kChannels == tc::kBlockCols && kFmaTile == tc::QT, "the tensor map's box is [128 steps x 64 channels]");
+
+struct TmaFeed {
+    uint4 cur[kFmaSB];
+    const CUtensorMap *tm;
+    uint8_t *stages;
+    uint32_t bars;            // shared-space address of kStages mbarriers
+    volatile int *abort_flag;
+    int c0, hi, bi, n_tiles, tid, off;   // off: bytes from the start of a stage to this thread's first value
+
+    __device__ __forceinline__ void issue(int k) {   // one thread
+        const int s = k % kStages;
+        tc::mbar_expect_tx(bars + 8 * s, kStageBytes);
+        tc::tma_load_4d(tc::smem_u32(stages + s * kStageBytes), tm, bars + 8 * s, c0, hi, k * kFmaTile, bi);
+    }
+    __device__ __forceinline__ void init(const FusedParams &, const float *, bool, int, int) {
+        if (tid == 0) {
+            for (int s = 0; s < kStages; ++s) tc::mbar_init(bars + 8 * s, 1);
+            *abort_flag = 0;
+            tc::fence_barrier_init();
+            for (int k = 0; k < kStages && k < n_tiles; ++k) issue(k);
+        }
+    }
+    __device__ __forceinline__ void begin(int k, bool) {
+        const int s = k % kStages;
+        tc::mbar_wait(bars + 8 * s, (k / kStages) & 1, abort_flag, 40);   // bounded; steps and channels past the end arrive as zeros
+        const uint8_t *src = stages + s * kStageBytes + off;
+#pragma unroll
+        for (int i = 0; i < kFmaSB; ++i) cur[i] = *reinterpret_cast<const uint4 *>(src + i * kChannels * 4);
+    }
+    __device__ __forceinline__ void after_barrier(int k) {
+        if (tid == 0 && k + kStages < n_tiles && !*abort_flag) issue(k + kStages);
+    }
+    __device__ __forceinline__ void end() {}
+    __device__ __forceinline__ void finish() {
+        if (*abort_flag)   // a wait ran out: give copies still in flight time to land before shared memory is released
+            for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+};
+
+template <bool WEIGHTED>
+__global__ void __launch_bounds__(kFmaThreads, 2)
+ema_fwd_fma_tma_kernel(const __grid_constant__ CUtensorMap tm_x, const FusedParams p) {
+    extern __shared__ uint8_t dyn_smem[];
+    uint8_t *base = dyn_smem + ((128u - (tc::smem_u32(dyn_smem) & 127u)) & 127u);
+    TmaFeed feed;
+    feed.tm = &tm_x;
+    feed.stages = base;
+    feed.bars = tc::smem_u32(base + kStages * kStageBytes);
+    feed.abort_flag = reinterpret_cast<volatile int *>(base + kStages * kStageBytes + 8 * kStages);
+    feed.tid = threadIdx.x;
+    const int lc = threadIdx.x % kFmaCT, sub = threadIdx.x / kFmaCT;
+    feed.off = (sub * kFmaSB * kChannels + lc * 4) * 4;
+    const int64_t row = blockIdx.x / p.n_dtiles;
+    feed.c0 = static_cast<int>(blockIdx.x % p.n_dtiles) * kChannels;
+    feed.bi = static_cast<int>(row / p.h);
+    feed.hi = static_cast<int>(row % p.h);
+    feed.n_tiles = p.n_tiles;
+    ema_fwd_fma_body<float, 4, WEIGHTED>(p, feed);
+}
+
+}  // namespace tmafeed
+
+// ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
 namespace {
@@ -1335,8 +1427,9 @@ EncodeTiledFn encode_fn() {
 
 // bf16 tensor [b, L, h, d] with element strides (sb, sl, sh), box = [64 channels, 1, 128 steps, 1] (half a tile),
 // 128-byte swizzle; out-of-range parts of a box read as zero and are not written.
+// bf16 (the default): 64-channel boxes in the 128-byte swizzle the MMA descriptors expect; fp32: dense 64-channel boxes
 int make_tmap(CUtensorMap *tm, const void *base, int64_t b, int64_t L, int64_t h, int64_t d, int64_t sb,
-              int64_t sl, int64_t sh) {
+              int64_t sl, int64_t sh, bool f32 = false) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return EMA_ERR_CUDA;
     // cuTensorMapEncodeTiled is a driver call and wants a context current on this thread.  A thread that has
@@ -1349,12 +1442,14 @@ int make_tmap(CUtensorMap *tm, const void *base, int64_t b, int64_t L, int64_t h
     if (b == 1) sb = L * sl;
     const cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(h), static_cast<cuuint64_t>(L),
                                 static_cast<cuuint64_t>(b)};
-    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(sh) * 2, static_cast<cuuint64_t>(sl) * 2,
-                                   static_cast<cuuint64_t>(sb) * 2};
+    const cuuint64_t es = f32 ? 4 : 2;
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(sh) * es, static_cast<cuuint64_t>(sl) * es,
+                                   static_cast<cuuint64_t>(sb) * es};
     const cuuint32_t box[4] = {tc::kBlockCols, 1, tc::QT, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+    CUresult r = fn(tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    f32 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? EMA_OK : EMA_ERR_UNSUPPORTED;
 }
@@ -1469,10 +1564,10 @@ int launch_fused_fwd_tc(const FusedParams &fp, cudaStream_t stream) {
     // the sum of the log decays is accumulated per item by one CTA: no cutting when it is asked for
     rc = plan_grid(fp, p.n_items, fp.log_decay_sum == nullptr, stream, &grid, &p.split, &p.carry, &p.flags);
     if (rc) return rc;
-    cudaError_t e = cudaFuncSetAttribute(tc::ema_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         tc::kFwdSmemBytes);
+    auto kernel = (fp.in_weight || fp.out_weight) ? tc::ema_fwd_tc_kernel<true> : tc::ema_fwd_tc_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kFwdSmemBytes);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
-    tc::ema_fwd_tc_kernel<<<grid, tc::kThreads, tc::kFwdSmemBytes, stream>>>(tm_x, tm_y, p);
+    kernel<<<grid, tc::kThreads, tc::kFwdSmemBytes, stream>>>(tm_x, tm_y, p);
     return check_launch();
 }
 
@@ -1512,6 +1607,27 @@ int launch_fused_bwd_tc(const FusedParams &fp, cudaStream_t stream) {
                                          tc::kBwdSmemBytes);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     tc::ema_bwd_tc_kernel<<<grid, tc::kThreads, tc::kBwdSmemBytes, stream>>>(tm_x, tm_g, tm_o, p);
+    return check_launch();
+}
+
+// fp32 forward, CUDA cores fed by TMA.  Takes what the widest-vector CUDA-core kernel takes (d and the strides multiples of
+// 4 elements, 16-byte aligned base) when the whole sequence is scanned; EMA_ERR_UNSUPPORTED sends the caller to the
+// plain kernel.
+int launch_fused_fwd_fma_tma(const FusedParams &fp, cudaStream_t stream) {
+    if (fp.stop_below > 0.f) return EMA_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(fp.x) % 16 != 0 || fp.d % 4 != 0 || encode_fn() == nullptr) return EMA_ERR_UNSUPPORTED;
+    if ((fp.h > 1 && (fp.x_sh % 4 != 0 || fp.x_sh <= 0)) || (fp.L > 1 && (fp.x_sl % 4 != 0 || fp.x_sl <= 0)) ||
+        (fp.b > 1 && (fp.x_sb % 4 != 0 || fp.x_sb <= 0)))
+        return EMA_ERR_UNSUPPORTED;
+    CUtensorMap tm_x;
+    int rc = make_tmap(&tm_x, fp.x, fp.b, fp.L, fp.h, fp.d, fp.x_sb, fp.x_sl, fp.x_sh, true);
+    if (rc) return rc;
+    const bool weighted = fp.in_weight || fp.out_weight;
+    auto kernel = weighted ? tmafeed::ema_fwd_fma_tma_kernel<true> : tmafeed::ema_fwd_fma_tma_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tmafeed::kSmemBytes);
+    if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
+    const int64_t blocks = fp.b * fp.h * fp.n_dtiles;   // n_dtiles counts 64-channel tiles here
+    kernel<<<static_cast<unsigned>(blocks), kFmaThreads, tmafeed::kSmemBytes, stream>>>(tm_x, fp);
     return check_launch();
 }
 
