@@ -86,8 +86,8 @@ const char *ema_b200_error_string(int code);
 int ema_b200_device_status(int clear);
 
 /* Which kernels bf16 problems run on: 0 = tensor-core path wherever the layout allows it (default),
- * 1 = plain CUDA-core kernels only (also for fp32, whose forward otherwise uses the TMA-fed variant of the same
- * kernel).  fp32 problems always compute on the CUDA cores (exactness).  Meant for A/B
+ * 1 = plain CUDA-core kernels only (also for fp32, which otherwise uses the TMA-fed variants of the same
+ * kernels).  fp32 problems always compute on the CUDA cores (exactness).  Meant for A/B
  * measurements and tests; the environment variable EMA_B200_PATH=fma sets the same switch at load. */
 int ema_b200_set_path(int path);
 /* Whether the bf16 kernels may cut a work item across thread blocks when the items do not divide evenly among
@@ -95,7 +95,7 @@ int ema_b200_set_path(int path);
  * previous setting.  Results do not depend on it; meant for A/B measurements and tests. */
 int ema_b200_set_split(int on);
 /* Kernel family the last ema_b200_fwd / ema_b200_bwd call on this thread launched: 1 = tensor cores,
- * 0 = CUDA cores, 2 = CUDA cores with x brought in by TMA (fp32 forward on 16-byte aligned layouts; same
+ * 0 = CUDA cores, 2 = CUDA cores with x (and dy) brought in by TMA (fp32 on 16-byte aligned layouts; same
  * arithmetic and bit-identical results as 0), -1 = none yet.  Lets a test assert which path really ran. */
 int ema_b200_last_path(void);
 

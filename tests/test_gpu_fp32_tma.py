@@ -84,3 +84,34 @@ def test_weighted_forward_through_both_feeds(ema_lib):
     ema_lib.ema_b200_set_path(1)
     f = ops.ema_fwd(x, torch.log(a), prescaled_log=True, in_weight=w, out_weight=c, want_final=True)
     assert torch.equal(t["y"], f["y"]) and torch.equal(t["final_state"], f["final_state"])
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("per_head", [False, True])
+@pytest.mark.parametrize("prescaled", [False, True])
+def test_tma_fed_backward_is_bit_identical_to_the_plain_kernel(shape, per_head, prescaled, ema_lib):
+    from ema_b200 import ops
+    from helpers import oracle_fwd_bwd
+    b, L, h, d = shape
+    x, a, dy, np_in = make_inputs(60 + L + d, b, L, h, d, per_head=per_head, dtype=torch.float32)
+    dec = torch.log(a) if prescaled else a
+    dfin = torch.randn(b, h, d, device="cuda")
+    ema_lib.ema_b200_set_path(1)
+    f = ops.ema_fwd(x, dec, want_tile_states=True, prescaled_log=prescaled)
+    gp = ops.ema_bwd(x, dec, dy, f["tile_states"], dfinal_state=dfin, want_dinit=True, prescaled_log=prescaled)
+    torch.cuda.synchronize()
+    assert ema_lib.ema_b200_last_path() == 0
+    ema_lib.ema_b200_set_path(0)
+    gt = ops.ema_bwd(x, dec, dy, f["tile_states"], dfinal_state=dfin, want_dinit=True, prescaled_log=prescaled)
+    torch.cuda.synchronize()
+    assert ema_lib.ema_b200_last_path() == 2
+    for key in ("dx", "ddecay", "dinit_state"):
+        assert torch.equal(gt[key], gp[key]), key
+    if not prescaled:
+        # and against the oracle, plain problem
+        f2 = ops.ema_fwd(x, a, want_tile_states=True)
+        g2 = ops.ema_bwd(x, a, dy, f2["tile_states"])
+        _, dx_ref, da_ref = oracle_fwd_bwd(np_in)
+        assert np.abs(g2["dx"].cpu().numpy() - dx_ref).max() <= 1e-4
+        assert np.abs(g2["ddecay"].cpu().numpy() - da_ref).max() <= 1e-4 + 2e-5 * np.abs(da_ref).max()
+    assert ema_lib.ema_b200_device_status(0) == 0

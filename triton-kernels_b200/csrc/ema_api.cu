@@ -267,6 +267,12 @@ extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const floa
         done = rc == EMA_OK;
     }
     g_last_path = done ? 1 : 0;
+    if (!done && p->dtype == EMA_F32 && vec == 4 && tc_enabled()) {
+        rc = launch_fused_bwd_fma_tma(fp, st);
+        if (rc && rc != EMA_ERR_UNSUPPORTED) return rc;
+        done = rc == EMA_OK;
+        if (done) g_last_path = 2;
+    }
     if (!done) {
         rc = launch_fused_bwd_fma(fp, p->dtype, vec, st);
         if (rc) return rc;

@@ -172,6 +172,7 @@ int launch_fused_fwd_tc(const FusedParams &p, cudaStream_t stream);
 int launch_fused_bwd_tc(const FusedParams &p, cudaStream_t stream);
 // fp32 forward on the CUDA cores with x brought in by TMA; p.n_dtiles must count 64-channel tiles (vec 4)
 int launch_fused_fwd_fma_tma(const FusedParams &p, cudaStream_t stream);
+int launch_fused_bwd_fma_tma(const FusedParams &p, cudaStream_t stream);
 int read_tc_status(int clear);
 // bytes of scratch that let the tensor-core kernels cut work items across CTAs (0 = never needed)
 size_t tc_sync_bytes(int64_t b, int64_t h, int64_t d);

@@ -33,6 +33,7 @@
 #include "ema_common.cuh"
 #include "ema_tc_common.cuh"
 #include "ema_fwd_fma_kernel.cuh"
+#include "ema_bwd_fma_kernel.cuh"
 
 namespace ema {
 namespace tc {
@@ -1400,6 +1401,81 @@ ema_fwd_fma_tma_kernel(const __grid_constant__ CUtensorMap tm_x, const FusedPara
     ema_fwd_fma_body<float, 4, WEIGHTED>(p, feed);
 }
 
+// Backward: x and dy tiles of the same steps share a stage (64 KB); three stages and one thread block per SM (the
+// backward's registers allow no more) keep 192 KB in flight.  Tiles are walked from the last to the first.
+constexpr int kBwdStageBytes = 2 * kStageBytes;
+constexpr int kBwdSmemBytes = kStages * kBwdStageBytes + kCtrlBytes + 128;
+
+struct TmaFeedBwd {
+    uint4 xc[kFmaSB], gc[kFmaSB];
+    const CUtensorMap *tm_x, *tm_g;
+    uint8_t *stages;
+    uint32_t bars;
+    volatile int *abort_flag;
+    int c0, hi, bi, n_tiles, tid, off;
+
+    __device__ __forceinline__ void issue(int kk) {   // one thread; iteration kk handles tile n_tiles - 1 - kk
+        const int s = kk % kStages, t0 = (n_tiles - 1 - kk) * kFmaTile;
+        const uint32_t dst = tc::smem_u32(stages + s * kBwdStageBytes);
+        tc::mbar_expect_tx(bars + 8 * s, kBwdStageBytes);
+        tc::tma_load_4d(dst, tm_x, bars + 8 * s, c0, hi, t0, bi);
+        tc::tma_load_4d(dst + kStageBytes, tm_g, bars + 8 * s, c0, hi, t0, bi);
+    }
+    __device__ __forceinline__ void fetch(int kk) {
+        const int s = kk % kStages;
+        tc::mbar_wait(bars + 8 * s, (kk / kStages) & 1, abort_flag, 41);   // bounded; steps and channels past the end are zeros
+        const uint8_t *src = stages + s * kBwdStageBytes + off;
+#pragma unroll
+        for (int i = 0; i < kFmaSB; ++i) {
+            xc[i] = *reinterpret_cast<const uint4 *>(src + i * kChannels * 4);
+            gc[i] = *reinterpret_cast<const uint4 *>(src + kStageBytes + i * kChannels * 4);
+        }
+    }
+    __device__ __forceinline__ void init(const FusedParams &, const float *, const float *, bool, int, int, int) {
+        if (tid == 0) {
+            for (int s = 0; s < kStages; ++s) tc::mbar_init(bars + 8 * s, 1);
+            *abort_flag = 0;
+            tc::fence_barrier_init();
+            for (int kk = 0; kk < kStages && kk < n_tiles; ++kk) issue(kk);
+        }
+        __syncthreads();   // the barriers exist before anyone waits on them
+        fetch(0);
+    }
+    __device__ __forceinline__ void begin(int kk, int, bool) {
+        if (kk > 0) fetch(kk);
+    }
+    __device__ __forceinline__ void after_barrier(int kk) {
+        if (tid == 0 && kk + kStages < n_tiles && !*abort_flag) issue(kk + kStages);
+    }
+    __device__ __forceinline__ void end(int, bool) {}
+    __device__ __forceinline__ void finish() {
+        if (*abort_flag)
+            for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+};
+
+__global__ void __launch_bounds__(kFmaThreads, 1)
+ema_bwd_fma_tma_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_g,
+                       const FusedParams p) {
+    extern __shared__ uint8_t dyn_smem[];
+    uint8_t *base = dyn_smem + ((128u - (tc::smem_u32(dyn_smem) & 127u)) & 127u);
+    TmaFeedBwd feed;
+    feed.tm_x = &tm_x;
+    feed.tm_g = &tm_g;
+    feed.stages = base;
+    feed.bars = tc::smem_u32(base + kStages * kBwdStageBytes);
+    feed.abort_flag = reinterpret_cast<volatile int *>(base + kStages * kBwdStageBytes + 8 * kStages);
+    feed.tid = threadIdx.x;
+    const int lc = threadIdx.x % kFmaCT, sub = threadIdx.x / kFmaCT;
+    feed.off = (sub * kFmaSB * kChannels + lc * 4) * 4;
+    const int64_t row = blockIdx.x / p.n_dtiles;
+    feed.c0 = static_cast<int>(blockIdx.x % p.n_dtiles) * kChannels;
+    feed.bi = static_cast<int>(row / p.h);
+    feed.hi = static_cast<int>(row % p.h);
+    feed.n_tiles = p.n_tiles;
+    ema_bwd_fma_body<float, 4>(p, feed);
+}
+
 }  // namespace tmafeed
 
 // ---------------------------------------------------------------------------------------------
@@ -1610,14 +1686,14 @@ int launch_fused_bwd_tc(const FusedParams &fp, cudaStream_t stream) {
     return check_launch();
 }
 
+static bool tma_f32_ok(const void *base, int64_t d, int64_t sb, int64_t sl, int64_t sh, int64_t b, int64_t L, int64_t h);
+
 // fp32 forward, CUDA cores fed by TMA.  Takes what the widest-vector CUDA-core kernel takes (d and the strides multiples of
 // 4 elements, 16-byte aligned base) when the whole sequence is scanned; EMA_ERR_UNSUPPORTED sends the caller to the
 // plain kernel.
 int launch_fused_fwd_fma_tma(const FusedParams &fp, cudaStream_t stream) {
     if (fp.stop_below > 0.f) return EMA_ERR_UNSUPPORTED;
-    if (reinterpret_cast<uintptr_t>(fp.x) % 16 != 0 || fp.d % 4 != 0 || encode_fn() == nullptr) return EMA_ERR_UNSUPPORTED;
-    if ((fp.h > 1 && (fp.x_sh % 4 != 0 || fp.x_sh <= 0)) || (fp.L > 1 && (fp.x_sl % 4 != 0 || fp.x_sl <= 0)) ||
-        (fp.b > 1 && (fp.x_sb % 4 != 0 || fp.x_sb <= 0)))
+    if (encode_fn() == nullptr || !tma_f32_ok(fp.x, fp.d, fp.x_sb, fp.x_sl, fp.x_sh, fp.b, fp.L, fp.h))
         return EMA_ERR_UNSUPPORTED;
     CUtensorMap tm_x;
     int rc = make_tmap(&tm_x, fp.x, fp.b, fp.L, fp.h, fp.d, fp.x_sb, fp.x_sl, fp.x_sh, true);
@@ -1628,6 +1704,31 @@ int launch_fused_fwd_fma_tma(const FusedParams &fp, cudaStream_t stream) {
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     const int64_t blocks = fp.b * fp.h * fp.n_dtiles;   // n_dtiles counts 64-channel tiles here
     kernel<<<static_cast<unsigned>(blocks), kFmaThreads, tmafeed::kSmemBytes, stream>>>(tm_x, fp);
+    return check_launch();
+}
+
+static bool tma_f32_ok(const void *base, int64_t d, int64_t sb, int64_t sl, int64_t sh, int64_t b, int64_t L, int64_t h) {
+    if (reinterpret_cast<uintptr_t>(base) % 16 != 0 || d % 4 != 0) return false;
+    return !((h > 1 && (sh % 4 != 0 || sh <= 0)) || (L > 1 && (sl % 4 != 0 || sl <= 0)) || (b > 1 && (sb % 4 != 0 || sb <= 0)));
+}
+
+// fp32 backward, CUDA cores fed by TMA: same conditions as the forward, for x and dy.
+int launch_fused_bwd_fma_tma(const FusedParams &fp, cudaStream_t stream) {
+    if (fp.stop_below > 0.f || encode_fn() == nullptr) return EMA_ERR_UNSUPPORTED;
+    if (!tma_f32_ok(fp.x, fp.d, fp.x_sb, fp.x_sl, fp.x_sh, fp.b, fp.L, fp.h) ||
+        !tma_f32_ok(fp.dy, fp.d, fp.g_sb, fp.g_sl, fp.g_sh, fp.b, fp.L, fp.h))
+        return EMA_ERR_UNSUPPORTED;
+    CUtensorMap tm_x, tm_g;
+    int rc = make_tmap(&tm_x, fp.x, fp.b, fp.L, fp.h, fp.d, fp.x_sb, fp.x_sl, fp.x_sh, true);
+    if (rc) return rc;
+    rc = make_tmap(&tm_g, fp.dy, fp.b, fp.L, fp.h, fp.d, fp.g_sb, fp.g_sl, fp.g_sh, true);
+    if (rc) return rc;
+    cudaError_t e = cudaFuncSetAttribute(tmafeed::ema_bwd_fma_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         tmafeed::kBwdSmemBytes);
+    if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
+    const int64_t blocks = fp.b * fp.h * fp.n_dtiles;
+    tmafeed::ema_bwd_fma_tma_kernel<<<static_cast<unsigned>(blocks), kFmaThreads, tmafeed::kBwdSmemBytes, stream>>>(
+        tm_x, tm_g, fp);
     return check_launch();
 }
 
