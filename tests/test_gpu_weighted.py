@@ -99,3 +99,17 @@ def test_weights_need_a_per_step_decay(ema_lib):
         ops.ema_fwd(x, a[0, 0].contiguous(), in_weight=w)
     with pytest.raises(ValueError):
         ops.ema_fwd(x, a, in_weight=w[:, :10])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_output_weight_alone_keeps_the_conventions_input_weight(dtype, ema_lib):
+    """Without an input-weight tensor the input weight stays the convention's 1 - a: y = c * ema(x, a)."""
+    from ema_b200 import ops
+    x, a, _, c = _inputs(21, 3, 700, 2, 192, dtype)
+    plain = ops.ema_fwd(x, a)["y"].float()
+    got = ops.ema_fwd(x, a, out_weight=c)["y"].float()
+    want = c.unsqueeze(-1) * plain
+    if dtype == torch.float32:
+        assert torch.equal(got, want)
+    else:   # the plain result was rounded to bf16 before the multiplication, the weighted one after it
+        assert float((got - want).abs().max()) <= BF16_REL * float(want.abs().max())

@@ -60,8 +60,10 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
     using R = raw_t<T, VEC>;
     constexpr int WQ = WEIGHTED ? QT : 1;   // the weight tables exist only in the weighted kernel
     __shared__ float a_sm[2][QT];
-    __shared__ float w_sm[2][WQ];   // input weights of the tile
-    __shared__ float c_sm[2][WQ];   // output weights
+    // Weight tables of a tile.  Unlike the decays they are read after the tile's block-wide barrier too, while a faster
+    // thread may already be writing the next tile's entries: three buffers (tile k in buffer k % 3) keep the two apart.
+    __shared__ float w_sm[3][WQ];   // input weights
+    __shared__ float c_sm[3][WQ];   // output weights
     __shared__ float S_sm[2][NS][DT];
     __shared__ float P_sm[2][NS];
     __shared__ float h_sm[2][DT];
@@ -88,11 +90,17 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
         const float v = arow[static_cast<int64_t>(t) * p.a_sl];
         return conv ? expf(v) : v;
     };
-    // per-step weights share the decay's strides; a missing tensor means weight 1
+    // per-step weights share the decay's strides (weighted calls always have a per-step decay); a missing output
+    // weight is 1, a missing input weight the convention's (1 - a, or 1)
     const int64_t w_off = bi * p.a_sb + hi * p.a_sh;
     auto load_w = [&](const float *w, int t) -> float {
         if (!w) return 1.f;
         return t < L ? w[w_off + static_cast<int64_t>(t) * p.a_sl] : 0.f;
+    };
+    auto load_in_w = [&](int t) -> float {
+        if (p.in_weight) return load_w(p.in_weight, t);
+        if (t >= L) return 0.f;
+        return conv ? 1.f : 1.f - arow[static_cast<int64_t>(t) * p.a_sl];
     };
 
     float h[VEC];
@@ -106,7 +114,7 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
     if (tid < QT) a_sm[0][tid] = load_a(tid);
     if constexpr (WEIGHTED) {
         if (tid < QT) {
-            w_sm[0][tid] = load_w(p.in_weight, tid);
+            w_sm[0][tid] = load_in_w(tid);
             c_sm[0][tid] = load_w(p.out_weight, tid);
         }
     }
@@ -118,6 +126,7 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
     float run = 1.f, logsum = 0.f;
     for (int k = 0; k < p.n_tiles; ++k) {
         const int par = k & 1;
+        const int wb = WEIGHTED ? k % 3 : 0;   // buffer of the weight tables
         const int t0 = k * QT + sub * SB;
         const bool more = k + 1 < p.n_tiles;
         float a_pref = 1.f, w_pref = 0.f, c_pref = 0.f;
@@ -126,7 +135,7 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
             if (tid < QT) a_pref = load_a((k + 1) * QT + tid);
             if constexpr (WEIGHTED) {
                 if (tid < QT) {
-                    w_pref = load_w(p.in_weight, (k + 1) * QT + tid);
+                    w_pref = load_in_w((k + 1) * QT + tid);
                     c_pref = load_w(p.out_weight, (k + 1) * QT + tid);
                 }
             }
@@ -144,7 +153,7 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
         for (int s = 0; s < SB; ++s) {
             float xf[VEC];
             unpack<T, VEC>(cur[s], xf);
-            const float pw = WEIGHTED ? w_sm[par][(sub * SB + s) % WQ] : (conv ? 1.f : 1.f - a_r[s]);
+            const float pw = WEIGHTED ? w_sm[wb][(sub * SB + s) % WQ] : (conv ? 1.f : 1.f - a_r[s]);
 #pragma unroll
             for (int v = 0; v < VEC; ++v) st[v] = fmaf(a_r[s], st[v], pw * xf[v]);
             Pl *= a_r[s];
@@ -155,8 +164,8 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
         if (more && tid < QT) a_sm[par ^ 1][tid] = a_pref;
         if constexpr (WEIGHTED) {
             if (more && tid < QT) {
-                w_sm[par ^ 1][tid] = w_pref;
-                c_sm[par ^ 1][tid] = c_pref;
+                w_sm[(k + 1) % 3][tid] = w_pref;
+                c_sm[(k + 1) % 3][tid] = c_pref;
             }
         }
         __syncthreads();
@@ -193,14 +202,14 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
         for (int s = 0; s < SB; ++s) {
             float xf[VEC];
             unpack<T, VEC>(cur[s], xf);
-            const float pw = WEIGHTED ? w_sm[par][(sub * SB + s) % WQ] : (conv ? 1.f : 1.f - a_r[s]);
+            const float pw = WEIGHTED ? w_sm[wb][(sub * SB + s) % WQ] : (conv ? 1.f : 1.f - a_r[s]);
 #pragma unroll
             for (int v = 0; v < VEC; ++v) h[v] = fmaf(a_r[s], h[v], pw * xf[v]);
             const int t = t0 + s;
             if (c_ok && t < L) {
                 if constexpr (WEIGHTED) {
                     if (p.out) {
-                        const float cw = c_sm[par][(sub * SB + s) % WQ];
+                        const float cw = c_sm[wb][(sub * SB + s) % WQ];
                         float ys[VEC];
 #pragma unroll
                         for (int v = 0; v < VEC; ++v) ys[v] = cw * h[v];
