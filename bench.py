@@ -34,6 +34,9 @@ WORKLOADS = {
                b=16, L=8192, h=2, d=1024, chunk=256, per_head=True, fwd_only=False, lo=2.0, hi=6.0),
     "c2": dict(name="ema_fwd_b16_L8192_h2_d1024_bf16_perstep_decay_chunk128",
                b=16, L=8192, h=2, d=1024, chunk=128, per_head=False, fwd_only=True, lo=2.0, hi=6.0),
+    # the c2 tensors with the backward as well: the per-step decay path at a size a profiler can capture
+    "c2b": dict(name="ema_fwd_bwd_b16_L8192_h2_d1024_bf16_perstep_decay_chunk128",
+                b=16, L=8192, h=2, d=1024, chunk=128, per_head=False, fwd_only=False, lo=2.0, hi=6.0),
     "c4": dict(name="ema_fwd_bwd_b4_L65536_h8_d1024_bf16_perstep_decay_chunk512",
                b=4, L=65536, h=8, d=1024, chunk=512, per_head=False, fwd_only=False, lo=3.0, hi=8.0),
     # sequence parallel: every rank holds one contiguous 65536-step segment of b8 h4 d1024 sequences of length
