@@ -1602,6 +1602,8 @@ static int plan_grid(const FusedParams &fp, int n_items, bool allow_split, cudaS
     *flags = nullptr;
     // cutting pays when whole items would leave a noticeable share of the SM-rounds idle (256 items on 148 SMs: 13.5 %)
     const bool uneven = static_cast<int64_t>(rounds) * sms * 92 > static_cast<int64_t>(n_items) * 100;
+    // (with fewer items than SMs a cut cannot help: an item's tiles are a sequential chain, and the thread blocks that
+    // would share it only wait for one another - measured 30-40 % slower)
     if (!allow_split || !split_enabled() || n_items < sms || sms > kMaxSplitGrid || !uneven || !fp.sync_ws ||
         fp.sync_ws_bytes < tc_sync_bytes(fp.b, fp.h, fp.d))
         return EMA_OK;
