@@ -85,15 +85,38 @@ const char *ema_b200_error_string(int code);
  * forever: after a timeout they finish their loops without waiting and the call's results are void. */
 int ema_b200_device_status(int clear);
 
+/* Self-test of the bounded device-side waits (test support; no counterpart in the reference, whose kernels never
+ * wait on one another).  Launches one small thread block that waits - through the same wait functions the
+ * tensor-core kernels use, but with a limit of `polls` polls (1 .. 2^20; a thousand polls last a few milliseconds) -
+ * for something that never happens: mode 0, an mbarrier nobody arrives on; mode 1, an arrival counter nobody
+ * increments (`zero_word`: one 32-bit device word holding 0 that nothing writes).  The wait runs out, the kernel
+ * records it in the status word and returns; no copy or tensor memory is in flight, nothing traps or hangs.
+ * Afterwards ema_b200_device_status(1) returns EMA_ERR_TIMEOUT once and EMA_OK from then on, and the library keeps
+ * working. */
+int ema_b200_selftest_wait(int mode, int polls, const void *zero_word, void *stream);
+
 /* Which kernels bf16 problems run on: 0 = tensor-core path wherever the layout allows it (default),
  * 1 = plain CUDA-core kernels only (also for fp32, which otherwise uses the TMA-fed variants of the same
  * kernels).  fp32 problems always compute on the CUDA cores (exactness).  Meant for A/B
  * measurements and tests; the environment variable EMA_B200_PATH=fma sets the same switch at load. */
 int ema_b200_set_path(int path);
-/* Whether the bf16 kernels may cut a work item across thread blocks when the items do not divide evenly among
- * the SMs (1, the default; the environment variable EMA_B200_SPLIT=0 turns it off at load).  Returns the
- * previous setting.  Results do not depend on it; meant for A/B measurements and tests. */
+/* How the bf16 kernels spread a problem over the SMs (the environment variable EMA_B200_SPLIT sets the same at load):
+ *   0  every work item (scan row x 128 channels) stays on one thread block;
+ *   1  (default) items may be cut across thread blocks: when the items do not divide evenly among the SMs, a thread
+ *      block hands the carry of a cut item to the next one through the scratch; when there are fewer items than about
+ *      two thirds of the SMs (and at least four 128-step tiles), a first pass reduces every tile to its aggregate -
+ *      the reference's chunk-state stage, kernels/ema_kernels/ema_state_fwd.py:54, and in the backward its dstates
+ *      stage, kernels/ema_kernels_bwd/ema_scan_bwd.py:39 - and every piece of an item starts from the fold of the
+ *      aggregates before it (the reference's state passing, kernels/ema_kernels/ema_state_pass.py:100-120), so that no
+ *      thread block waits for another;
+ *   2  as 1, with the aggregate schedule for every problem that has at least two tiles (tests).
+ * Returns the previous setting.  Cutting with carries gives bit-identical results; the aggregate schedule agrees
+ * with them to within the rounding of the bf16 decay matrices.  Both need the scratch of
+ * ema_b200_fwd_workspace_bytes / ema_b200_bwd_workspace_bytes, whose value depends on this setting. */
 int ema_b200_set_split(int on);
+/* Schedule of the last tensor-core launch made by ema_b200_fwd / ema_b200_bwd on this thread: 0 whole items,
+ * 1 items cut with carries, 2 aggregates; -1 when the last call did not use the tensor-core kernels. */
+int ema_b200_last_schedule(void);
 /* Kernel family the last ema_b200_fwd / ema_b200_bwd call on this thread launched: 1 = tensor cores,
  * 0 = CUDA cores, 2 = CUDA cores with x (and dy) brought in by TMA (fp32 on 16-byte aligned layouts; same
  * arithmetic and bit-identical results as 0), -1 = none yet.  Lets a test assert which path really ran. */
@@ -127,13 +150,12 @@ size_t ema_b200_bwd_workspace_bytes(const ema_b200_problem *p);
  *   stop_below    0 to scan all L steps.  > 0: stop after the first tile at whose end the
  *                 product of decays since step 0 is below this value - used to re-scan only the
  *                 prefix an incoming carry can still influence (sequence-parallel fix-up).
- *   workspace     optional scratch of ema_b200_fwd_workspace_bytes(p) bytes (a few hundred KB, whatever
- *                 the problem size), 16-byte aligned.  With
- *                 it, and when the work items (scan row x 128 channels) do not divide evenly among
- *                 the SMs, the bf16 kernels cut items across thread blocks and pass the carries
- *                 through this scratch, so that every SM has work; without it each item stays on
- *                 one thread block.  The results are the same either way.  Two calls that may
- *                 overlap in time must not share a scratch. */
+ *   workspace     optional scratch of ema_b200_fwd_workspace_bytes(p) bytes, 16-byte aligned (a few
+ *                 hundred KB; for problems with few work items, see ema_b200_set_split, also 4 bytes
+ *                 per 128 elements of x for the per-tile aggregates).  With it the bf16 kernels cut
+ *                 work items (scan row x 128 channels) across thread blocks so that every SM has
+ *                 work; without it each item stays on one thread block.  Two calls that may overlap
+ *                 in time must not share a scratch. */
 size_t ema_b200_fwd_workspace_bytes(const ema_b200_problem *p);
 int ema_b200_fwd(const ema_b200_problem *p, const void *x, const float *decay, void *y,
                  float *chunk_states, float *tile_states, const float *init_state, float *final_state,
@@ -166,6 +188,19 @@ int ema_b200_bwd(const ema_b200_problem *p, const void *x, const float *decay, c
                  const float *tile_states, void *dx, float *ddecay, const float *dfinal_state,
                  float *dinit_state, float stop_below, void *workspace, size_t workspace_bytes,
                  void *stream);
+
+/* ---- sequence-parallel carry fold ------------------------------------------------------------
+ * (The reference is single-GPU; the recurrence folded here is its chunk-level carry,
+ * kernels/ema_kernels/ema_state_pass.py:100-120, h <- exp(cs_last) h + S, applied to whole segments.)
+ *
+ * records: `world` records in rank order, each [F (rows*d floats) | logP (rows floats)]: the state a
+ * rank's segment ends in when scanned from zero and the sum of its log decays - what the ranks
+ * all-gather (final_state and log_decay_sum of ema_b200_fwd written into one buffer).
+ *   reverse == 0: out[rows, d] = state entering segment `rank`   (fold of records 0 .. rank-1)
+ *   reverse != 0: out[rows, d] = adjoint entering segment `rank` from the right (fold of records
+ *                 world-1 .. rank+1, F being the dinit_state of ema_b200_bwd)                      */
+int ema_b200_fold_records(const float *records, int world, int rank, int64_t rows, int64_t d, int reverse,
+                          float *out, void *stream);
 
 /* ---- backward without a workspace ---------------------------------------------------------
  * (No counterpart in the reference: its backward allocates its temporaries with torch.empty.)

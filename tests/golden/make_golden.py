@@ -15,6 +15,11 @@ Two sources of truth are recorded, both executed from the reference's own files:
   state-passing kernel is pinned to BLOCK_SIZE=64, the block size its host wrapper sizes the
   partial-sum buffer for (kernels/ema_kernels_bwd/ema_state_passing_bwd_dstates.py:134-142).
 
+* the heads-style entry point ema_chunk_scan_combined (kernels/ema_combined.py:100, forward :12-57) for state
+  size 1, again through the interpreted Triton kernels, each autotuner pinned to its first configuration.  Its
+  cumulative-sum kernel hard-codes dA = -dt (kernels/ema_chunk_state.py:95), so only A = -1 is comparable with
+  the sequential definition; the fixtures record that in `meta_A_is_minus_one`.
+
 Inputs come from numpy's frozen RandomState streams (golden_inputs.py); the north-star fixtures
 store only a and the outputs, and the tests rebuild x and dy from the recorded seed.
 """
@@ -126,6 +131,46 @@ def main():
               "dx:", np.abs(cdx.numpy() - rec["loop_dX"]).max(),
               "out:", np.abs(o.numpy() - rec["loop_out"]).max())
 
+    def heads_case(name, seed, b, L, h, p, g, chunk, full, with_seq_idx=False):
+        """out and final_states of the reference's heads-style entry point for state size 1 and A = -1."""
+        import kernels.ema_combined as ref_combined
+        import kernels.ema_chunk_state as m1, kernels.ema_state_passing as m2, kernels.ema_bmm as m3, kernels.ema_chunk_scan as m4
+        for mod in (m1, m2, m3, m4):
+            for attr in dir(mod):
+                k = getattr(mod, attr)
+                if isinstance(getattr(k, "configs", None), list) and k.configs:
+                    k.configs = k.configs[:1]
+        rs = np.random.RandomState(seed)
+        f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32)
+        rec = dict(x=f32(rs.standard_normal((b, L, h, p))), A=-np.ones(h, np.float32),
+                   B=f32(rs.random_sample((b, L, g, 1))))
+        if full:
+            rec.update(dt=f32(0.3 * rs.standard_normal((b, L, h)) - 1.0), C=f32(0.5 + rs.random_sample((b, L, g, 1))),
+                       D=f32(rs.standard_normal((h, p))), z=f32(rs.standard_normal((b, L, h, p))),
+                       dt_bias=f32(0.1 * rs.standard_normal(h)), initial_states=f32(rs.standard_normal((b, h, p, 1))))
+            kw = dict(dt_softplus=True, dt_limit=(0.001, 2.0))
+        else:
+            rec.update(dt=f32(0.01 + 0.2 * rs.random_sample((b, L, h))), C=np.ones((b, L, g, 1), np.float32))
+            kw = {}
+        if with_seq_idx:
+            sid = np.zeros((b, L), np.int32)
+            sid[0, L // 3:] = 1
+            sid[0, chunk:] += 1          # a restart exactly on a chunk boundary
+            sid[1, L - 7:] = 5
+            rec["seq_idx"] = sid
+        t = {k: torch.tensor(v) for k, v in rec.items()}
+        with torch.no_grad():
+            out, fin = ref_combined.ema_chunk_scan_combined(
+                t["x"], t["dt"], t["A"], t["B"], t["C"], chunk, D=t.get("D"), z=t.get("z"), dt_bias=t.get("dt_bias"),
+                initial_states=t.get("initial_states"), seq_idx=t.get("seq_idx"), return_final_states=True, **kw)
+        rec.update(out=out.numpy(), final_states=fin.numpy(), meta=np.array([seed, b, L, h, p, g, chunk, int(full)]),
+                   meta_A_is_minus_one=np.array([1]))
+        np.savez(os.path.join(args.out, name + ".npz"), **rec)
+        print(name, "done", float(np.abs(rec["out"]).max()))
+
+    heads_case("heads_plain", 21, 2, 96, 2, 16, 1, 32, full=False)
+    heads_case("heads_full", 22, 2, 100, 4, 16, 2, 32, full=True)
+    heads_case("heads_seqidx", 23, 2, 90, 2, 16, 1, 32, full=False, with_seq_idx=True)
     north_star_case("northstar_c1", 1235, 2, 256, 2, 64, 2.0, 6.0, per_head=False)
     north_star_case("northstar_perhead", 1237, 2, 192, 3, 32, 2.0, 6.0, per_head=True)
     north_star_case("northstar_ragged", 1241, 1, 77, 2, 24, 3.0, 8.0, per_head=False)

@@ -1,35 +1,48 @@
 """The heads-style entry point ema_chunk_scan_combined (drop-in for kernels/ema_combined.py:100 of the
-reference) in the EMA special case, state size 1: against a sequential fp64 loop, values and gradients."""
+reference) in the EMA special case, state size 1: against fixtures recorded from the reference's own entry point
+(its Triton kernels under the CPU interpreter, tests/golden/heads_*.npz) and against the sequential fp64 loop of
+oracle/ema_heads_loop.py, values and gradients."""
+import os
+
+import numpy as np
 import pytest
 import torch
-import torch.nn.functional as F
 
 from helpers import BF16_REL, FP32_ATOL
+from oracle.ema_heads_loop import heads_loop_torch
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["heads_plain", "heads_full", "heads_seqidx"])
+@pytest.mark.parametrize("grad", [False, True])
+def test_heads_style_matches_the_reference_fixture(name, grad, ema_lib, golden_dir):
+    """out and final_states equal what the reference's ema_chunk_scan_combined returned on the same inputs (A = -1:
+    the reference ignores A, kernels/ema_chunk_state.py:95); both the fused inference route (no gradients) and the
+    autograd route."""
+    from kernels.ema_combined import ema_chunk_scan_combined
+    g = np.load(os.path.join(golden_dir, name + ".npz"))
+    assert int(g["meta_A_is_minus_one"][0]) == 1
+    chunk, full = int(g["meta"][6]), bool(g["meta"][7])
+    t = {k: torch.tensor(g[k]).cuda() for k in g.files if k not in ("out", "final_states", "meta", "meta_A_is_minus_one")}
+    if grad:
+        t["x"].requires_grad_(True)
+    kw = dict(dt_softplus=True, dt_limit=(0.001, 2.0)) if full else {}
+    with torch.enable_grad() if grad else torch.no_grad():
+        out, fin = ema_chunk_scan_combined(t["x"], t["dt"], t["A"], t["B"], t["C"], chunk, D=t.get("D"), z=t.get("z"),
+                                           dt_bias=t.get("dt_bias"), initial_states=t.get("initial_states"),
+                                           seq_idx=t.get("seq_idx"), return_final_states=True, **kw)
+    for got, ref, what in ((out, g["out"], "out"), (fin, g["final_states"], "final_states")):
+        err = float(np.abs(got.detach().float().cpu().numpy() - ref).max())
+        tol = FP32_ATOL + 2e-5 * float(np.abs(ref).max())
+        assert err <= tol, f"{name} {what}: {err:.3e} > {tol:.3e}"
+    assert ema_lib.ema_b200_device_status(1) == 0
 
 
 def _loop(x, dt, A, B, C, D, z, dt_bias, init, softplus, limit, seq_idx=None):
-    """fp64 sequential definition (the recurrence of the reference's chunked kernels, ema_combined.py:12-66)."""
-    b, L, h, p = x.shape
-    rep = h // B.shape[2]
-    d = dt if dt_bias is None else dt + dt_bias
-    if softplus:
-        d = torch.where(d <= 20.0, F.softplus(d), d)
-    d = torch.clamp(d, min=limit[0], max=limit[1])
-    Bh = B[..., 0].repeat_interleave(rep, dim=2)
-    Ch = C[..., 0].repeat_interleave(rep, dim=2)
-    s = torch.zeros((b, h, p), dtype=x.dtype) if init is None else init[..., 0]
-    ys = []
-    for t in range(L):
-        if seq_idx is not None and t > 0:   # a new sequence starts from a zero state
-            s = s * (seq_idx[:, t] == seq_idx[:, t - 1]).to(s.dtype).view(b, 1, 1)
-        s = torch.exp(d[:, t] * A).unsqueeze(-1) * s + (d[:, t] * Bh[:, t]).unsqueeze(-1) * x[:, t]
-        ys.append(Ch[:, t].unsqueeze(-1) * s)
-    y = torch.stack(ys, dim=1)
-    if D is not None:
-        y = y + x * (D.unsqueeze(-1) if D.dim() == 1 else D)
-    if z is not None:
-        y = y * F.silu(z)
-    return y, s.unsqueeze(-1)
+    """The sequential fp64 definition (oracle/ema_heads_loop.py, pinned against fixtures recorded from the
+    reference's own entry point), on torch leaves so that autograd gives the gradients."""
+    return heads_loop_torch(x, dt, A, B, C, D=D, z=z, dt_bias=dt_bias, initial_states=init, dt_softplus=softplus,
+                            dt_limit=limit, seq_idx=seq_idx)
 
 
 def _make(seed, b, L, h, p, g, dtype, full):

@@ -110,3 +110,25 @@ def test_edge_shapes():
         assert y.shape == x.shape and dx.shape == x.shape and da.shape == a.shape
     x, a, dy = gen_inputs(3, 1, 1, 1, 4, 2.0, 6.0)
     assert np.allclose(eo.fwd(x, a), (1 - a)[..., None] * x)
+
+
+@pytest.mark.parametrize("name", ["heads_plain", "heads_full", "heads_seqidx"])
+def test_heads_loop_matches_the_reference_entry_point(name, golden_dir):
+    """oracle/ema_heads_loop.py (numpy, and its torch twin used for gradients) against out / final_states recorded
+    from the reference's ema_chunk_scan_combined (kernels/ema_combined.py:100) under the Triton interpreter."""
+    import torch
+    from oracle.ema_heads_loop import heads_loop, heads_loop_torch
+    g = np.load(os.path.join(golden_dir, name + ".npz"))
+    full = bool(g["meta"][7])
+    opt = lambda k: g[k] if k in g.files else None
+    kw = dict(dt_softplus=True, dt_limit=(0.001, 2.0)) if full else {}
+    out, fin = heads_loop(g["x"], g["dt"], g["A"], g["B"], g["C"], D=opt("D"), z=opt("z"), dt_bias=opt("dt_bias"),
+                          initial_states=opt("initial_states"), seq_idx=opt("seq_idx"), **kw)
+    scale = float(np.abs(g["out"]).max())
+    assert np.abs(out - g["out"]).max() <= 1e-5 * max(scale, 1.0)
+    assert np.abs(fin - g["final_states"]).max() <= 1e-5 * max(float(np.abs(g["final_states"]).max()), 1.0)
+    tt = lambda k: None if opt(k) is None else torch.tensor(g[k]).double() if g[k].dtype != np.int32 else torch.tensor(g[k])
+    out_t, fin_t = heads_loop_torch(tt("x"), tt("dt"), tt("A"), tt("B"), tt("C"), D=tt("D"), z=tt("z"),
+                                    dt_bias=tt("dt_bias"), initial_states=tt("initial_states"), seq_idx=tt("seq_idx"), **kw)
+    assert np.abs(out_t.numpy() - out).max() <= 1e-9 * max(scale, 1.0)
+    assert np.abs(fin_t.numpy() - fin).max() <= 1e-9 * max(scale, 1.0)

@@ -1,6 +1,7 @@
 // C-ABI entry points of the fused path: argument checks, kernel selection, launches.
 #include "ema_common.cuh"
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -38,14 +39,16 @@ int pick_vec(const ema_b200_problem *p, const void *x, const void *out, const vo
 
 // Kernel family for bf16 problems: 0 = tensor cores where the layout allows (default), 1 = CUDA cores
 // only.  Set by ema_b200_set_path or, once, by the environment variable EMA_B200_PATH=fma.
-int g_path = -1;
+std::atomic<int> g_path{-1};
 thread_local int g_last_path = -1;  // kernel family of the last fused launch on this thread: 1 tensor cores, 0 CUDA cores
 bool tc_enabled() {
-    if (g_path < 0) {
+    int v = g_path.load(std::memory_order_relaxed);
+    if (v < 0) {
         const char *e = std::getenv("EMA_B200_PATH");
-        g_path = (e && std::strcmp(e, "fma") == 0) ? 1 : 0;
+        v = (e && std::strcmp(e, "fma") == 0) ? 1 : 0;
+        g_path.store(v, std::memory_order_relaxed);
     }
-    return g_path == 0;
+    return v == 0;
 }
 
 void fill_params(FusedParams &fp, const ema_b200_problem *p, int vec) {
@@ -92,11 +95,19 @@ extern "C" const char *ema_b200_error_string(int code) {
 extern "C" int ema_b200_device_status(int clear) { return read_tc_status(clear); }
 extern "C" int ema_b200_set_split(int on) { return tc_set_split(on); }
 
+extern "C" int ema_b200_selftest_wait(int mode, int polls, const void *zero_word, void *stream) {
+    if ((mode != 0 && mode != 1) || polls <= 0 || polls > (1 << 20)) return EMA_ERR_BADARG;
+    if (mode == 1 && (!zero_word || !aligned(zero_word, 4))) return EMA_ERR_BADARG;
+    return launch_selftest_wait(mode, static_cast<unsigned>(polls), static_cast<const unsigned *>(zero_word),
+                                static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int ema_b200_last_path(void) { return g_last_path; }
+extern "C" int ema_b200_last_schedule(void) { return g_last_path == 1 ? tc_last_schedule() : -1; }
 
 extern "C" int ema_b200_set_path(int path) {
     if (path != 0 && path != 1) return EMA_ERR_BADARG;
-    g_path = path;
+    g_path.store(path, std::memory_order_relaxed);
     return EMA_OK;
 }
 
@@ -124,7 +135,7 @@ static size_t bwd_partial_bytes(const ema_b200_problem *p) {
 }
 
 static size_t sync_bytes(const ema_b200_problem *p) {
-    return p->dtype == EMA_BF16 ? tc_sync_bytes(p->b, p->h, p->d) : 0;
+    return p->dtype == EMA_BF16 ? tc_sync_bytes(p->b * p->h, p->L, p->d) : 0;
 }
 
 extern "C" size_t ema_b200_bwd_workspace_bytes(const ema_b200_problem *p) {

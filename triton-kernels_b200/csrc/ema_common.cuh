@@ -174,8 +174,15 @@ int launch_fused_bwd_tc(const FusedParams &p, cudaStream_t stream);
 int launch_fused_fwd_fma_tma(const FusedParams &p, cudaStream_t stream);
 int launch_fused_bwd_fma_tma(const FusedParams &p, cudaStream_t stream);
 int read_tc_status(int clear);
-// bytes of scratch that let the tensor-core kernels cut work items across CTAs (0 = never needed)
-size_t tc_sync_bytes(int64_t b, int64_t h, int64_t d);
+int launch_selftest_wait(int mode, unsigned polls, const unsigned *scratch, cudaStream_t stream);
+// bytes of scratch that let the tensor-core kernels cut work items across CTAs: carries handed between thread
+// blocks, plus per-tile aggregates for problems with few work items (rows = b * h scan rows)
+size_t tc_sync_bytes(int64_t rows, int64_t L, int64_t d);
+bool tc_wants_aggregates(int64_t rows, int64_t L, int64_t d);
 int tc_set_split(int on);   // returns the previous setting
+int tc_last_schedule();     // schedule of this thread's last tensor-core launch: 0 whole items, 1 carries, 2 aggregates
+// per-tile aggregates (ema_tile_agg.cu): one buffer's size, and the pass that fills it from x (adjoint = 0) or dy
+size_t tile_aggregate_bytes(int64_t rows, int64_t L, int64_t d);
+int launch_tile_aggregates(const FusedParams &fp, int adjoint, float *buf, cudaStream_t stream);
 
 }  // namespace ema

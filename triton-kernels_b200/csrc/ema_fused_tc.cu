@@ -27,6 +27,7 @@
 // carry ready (a ring of 4 so that the warp on the serial carry chain can run ahead of the others), and
 // stage staged.  Every wait is bounded (ema_tc_common.cuh): after a timeout the roles run their loops to
 // the end without waiting, the CTA tears down normally and the host sees EMA_ERR_TIMEOUT.
+#include <atomic>
 #include <cstdlib>
 #include <cuda_fp16.h>
 
@@ -314,6 +315,9 @@ struct TcParams {
     int split;
     float *carry;
     unsigned *flags;
+    // aggregate schedule (split == 2): per-tile aggregates [rows, n_tiles, d] and decay products [rows, n_tiles] made
+    // by tile_aggregate_kernel; a piece that starts inside an item folds the aggregates of the tiles before it
+    const float *agg_vec, *agg_fac;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -326,6 +330,10 @@ struct TcParams {
 // for FIRST and on the piece that waits for somebody LAST, so that a carry is published a whole range ahead of
 // its use and no wait depends on another wait; the wait itself is bounded like every other wait of the kernel.
 // ---------------------------------------------------------------------------------------------
+// split = 2 (few work items): the same contiguous ranges, now of any length, but nothing is handed from CTA to CTA.
+// A separate pass (tile_aggregate_kernel) has reduced every tile to its aggregate, and a piece that starts inside an
+// item computes the state (adjoint) entering it by folding the aggregates of the tiles before (after) it - the
+// reference's chunk-state / state-passing / chunk-scan split, with the serial carry done where it is needed.
 struct Piece {
     int64_t item;
     int k0, k1;   // tiles [k0, k1) of the item
@@ -365,10 +373,24 @@ struct Sched {
         return pc;
     }
 };
+// State entering tile k0 of a row's channel c: h <- P_j h + S_j over the tiles j < k0 (vec, fac: this row's aggregates).
+// Kept out of line: it runs once per piece, and the epilogue's hot loop must stay small.
+__device__ __noinline__ float fold_state_before(const float *vec, const float *fac, int64_t d, int k0, float h) {
+#pragma unroll 4
+    for (int j = 0; j < k0; ++j) h = fmaf(fac[j], h, vec[static_cast<int64_t>(j) * d]);
+    return h;
+}
+// Adjoint entering tile k1 - 1 from the right: g <- G_j + F_j g over the tiles j = n_tiles - 1 .. k1.
+__device__ __noinline__ float fold_adjoint_after(const float *vec, const float *fac, int64_t d, int k1, int n_tiles, float g) {
+#pragma unroll 4
+    for (int j = n_tiles - 1; j >= k1; --j) g = fmaf(fac[j], g, vec[static_cast<int64_t>(j) * d]);
+    return g;
+}
 constexpr int kCarryFloats = 2 * DT;   // per cut: the carries of up to two channel tiles
 // Bounded wait for a carry: one arrival per 64-channel half of every channel tile of the item.
-__device__ __forceinline__ bool wait_carry(const unsigned *flag, unsigned need, volatile int *abort_flag, int site) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+__device__ __forceinline__ bool wait_carry(const unsigned *flag, unsigned need, volatile int *abort_flag, int site,
+                                           uint32_t limit = kWaitLimit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         unsigned v;
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
         if (v >= need) return true;
@@ -412,7 +434,11 @@ static_assert(kFwdSmemBytes <= 227 * 1024, "forward shared memory exceeds the pe
 // WEIGHTED: per-step input weights inside the decay matrix and output weights on the rows of what is written, as its
 // own instantiation: in the plain kernel even a never-taken branch for them costs 40 % of the per-step speed (the
 // five roles' code competes for the instruction cache).
-template <bool WEIGHTED>
+// AGG: the aggregate schedule (split = 2), also its own instantiation.  The state entering every tile is then the
+// fold of the per-tile aggregates, h_{k+1} = P_k h_k + S_k, carried in a register by the thread that owns the
+// channel - the same fp32 chain wherever the pieces are cut, so the results do not depend on the grid - and the last
+// row of the product is no longer on a serial chain.
+template <bool WEIGHTED, bool AGG>
 __global__ void __launch_bounds__(kThreads, 1)
 ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                   const TcParams p) {
@@ -446,7 +472,8 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
         for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiWarps); }
         for (int i = 0; i < kFwdMatBufs; ++i) { mbar_init(bar(B_MAT_FULL + i), kBuildWarps); mbar_init(bar(B_MAT_EMPTY + i), 1); }
-        for (int i = 0; i < kFwdHRing; ++i) mbar_init(bar(B_H + i), 2);       // one arrival per channel half
+        // carry ready: one arrival per channel half (row 127's two threads), or per loader warp with aggregates
+        for (int i = 0; i < kFwdHRing; ++i) mbar_init(bar(B_H + i), AGG ? 4 : 2);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tm_x);
@@ -585,17 +612,18 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         const bool loader = half == 0;   // 128 threads that move per-channel vectors: thread m <-> channel m
         uint32_t it = 0, mt = 0;
         int cur_head = -1;
+        float h_reg[2] = {0.f, 0.f};   // AGG: the state entering the current tile, channel m of each sub-tile (loaders)
         for (int pi = 0; pi < sched.n; ++pi) {
             const Piece pc = sched.get<true>(pi);
             const int dt0 = item_dt0(pc.item), nsub = item_nsub(pc.item);
             const int64_t row = item_row(pc.item);
             const int hi = static_cast<int>(row % p.h);
-            const bool publish = pc.k1 < p.n_tiles;   // the item continues in another CTA: hand it the state
+            const bool publish = !AGG && pc.k1 < p.n_tiles;   // the item continues in another CTA: hand it the state
             // a piece that ends inside an item hands its state to the next CTA (cut blockIdx.x + 1); a piece that starts
             // inside an item takes it from the previous one (cut blockIdx.x); kCarryFloats floats per cut
             float *carry_out = p.carry + static_cast<int64_t>(blockIdx.x + 1) * kCarryFloats;
             if (loader) {
-                if (pc.k0 > 0) {   // second part of a cut item: the state comes from the CTA that made the first part
+                if (!AGG && pc.k0 > 0) {   // second part of a cut item: the state comes from the CTA that made the first part
                     if (lane == 0) wait_carry(p.flags + blockIdx.x, 2u * nsub, abort_flag, 22);
                     __syncwarp();
                 }
@@ -603,17 +631,21 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     const int c0u = (dt0 + u) * DT;
                     const bool ok = c0u + m < p.d;
                     float v;
-                    if (pc.k0 > 0) {
-                        v = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x) * kCarryFloats + u * DT + m);
-                    } else {
+                    if (AGG || pc.k0 == 0) {
                         v = (p.init_state && ok) ? p.init_state[row * p.d + c0u + m] : 0.f;
-                        if (p.chunk_states && ok) p.chunk_states[(row * p.n_chunks) * p.d + c0u + m] = v;
+                        if (pc.k0 == 0 && p.chunk_states && ok) p.chunk_states[(row * p.n_chunks) * p.d + c0u + m] = v;
+                        if (AGG && pc.k0 > 0 && ok)
+                            v = fold_state_before(p.agg_vec + row * p.n_tiles * p.d + c0u + m,
+                                                  p.agg_fac + row * p.n_tiles, p.d, pc.k0, v);
+                    } else {
+                        v = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x) * kCarryFloats + u * DT + m);
                     }
                     h_sm[((it + u) & (kFwdHRing - 1)) * DT + m] = v;
+                    h_reg[u] = v;
                 }
             }
             bar_sync(1, kEpiThreads);  // once per piece: the previous one is finished everywhere, the state is in place
-            if (m == QT - 1)
+            if (AGG ? (loader && lane == 0) : (m == QT - 1))
                 for (int u = 0; u < nsub; ++u) mbar_arrive(bar(B_H + ((it + u) & (kFwdHRing - 1))));
             for (int k = pc.k0; k < pc.k1; ++k)
             for (int u = 0; u < nsub; ++u, ++it) {
@@ -628,9 +660,22 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     const int tw = k * QT + m;
                     out_w = tw < L ? p.out_weight[(row / p.h) * p.a_sb + static_cast<int64_t>(tw) * p.a_sl + hi * p.a_sh] : 0.f;
                 }
+                // AGG: this tile's aggregate, fetched ahead of the wait that hides its latency
+                float agg_s = 0.f, agg_p = 0.f;
+                if (AGG && loader && k + 1 < pc.k1) {
+                    agg_p = p.agg_fac[row * p.n_tiles + k];
+                    if (ch_ok) agg_s = p.agg_vec[(row * p.n_tiles + k) * p.d + c0 + m];
+                }
                 if (lane == 0) mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 5);  // one poller per warp
                 __syncwarp();
                 tc_fence_after_sync();
+                if (AGG && loader && k + 1 < pc.k1) {   // the state entering this channel tile's next tile
+                    const float hn = fmaf(agg_p, h_reg[u], agg_s);
+                    h_reg[u] = hn;
+                    h_sm[((it + nsub) & (kFwdHRing - 1)) * DT + m] = hn;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(B_H + ((it + nsub) & (kFwdHRing - 1))));
+                }
                 const float E = e_sm[((mt - 1) & (kRing - 1)) * QT + m];
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * DT + half * 64;
                 if (lane == 0) mbar_wait(bar(B_H + slot), hph, abort_flag, 6);
@@ -659,7 +704,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         y[c + 2] = fmaf(E, hv.z, y[c + 2]);
                         y[c + 3] = fmaf(E, hv.w, y[c + 3]);
                     }
-                    if (m == QT - 1 && k + 1 < pc.k1) {  // the last row is the state entering this channel tile's next tile
+                    if (!AGG && m == QT - 1 && k + 1 < pc.k1) {  // the last row is the state entering this channel tile's next tile
                         float *hout = h_sm + ((it + nsub) & (kFwdHRing - 1)) * DT + cb;
 #pragma unroll
                         for (int c = 0; c < 32; c += 4)
@@ -834,6 +879,8 @@ struct TcBwdParams {
     int split;
     float *carry;
     unsigned *flags;
+    // aggregate schedule (split == 2): adjoint aggregates [rows, n_tiles, d] and products [rows, n_tiles]
+    const float *agg_vec, *agg_fac;
 };
 
 constexpr int kBwdStages = 2;
@@ -874,6 +921,9 @@ struct BwdSmem {
 constexpr int kBwdSmemBytes = BwdSmem::total;   // no alignment slack: see the kernel
 static_assert(kBwdSmemBytes <= 227 * 1024, "backward shared memory exceeds the per-CTA limit");
 
+// AGG: the aggregate schedule (split = 2) as its own instantiation: the adjoint entering every tile is the fold of
+// the per-tile adjoint aggregates, g_{k-1} = G_k + F_k g_k, carried in a register by the thread that owns the channel.
+template <bool AGG>
 __global__ void __launch_bounds__(kThreads, 1)
 ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_g,
                   const __grid_constant__ CUtensorMap tm_o, const TcBwdParams p) {
@@ -914,8 +964,9 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         for (int i = 0; i < 2; ++i) { mbar_init(bar(B_ACC_FULL + i), 1); mbar_init(bar(B_ACC_EMPTY + i), kEpiWarps); }
         mbar_init(bar(B_MAT_FULL), kBuildWarps);
         mbar_init(bar(B_MAT_EMPTY), 1);
-        // carry ready: the two halves of the adjoint row and the four warps that fetch the saved state
-        for (int i = 0; i < kBwdCRing; ++i) mbar_init(bar(B_G + i), 6);
+        // carry ready: the two halves of the adjoint row and the four warps that fetch the saved state (with
+        // aggregates those four warps bring the adjoint as well)
+        for (int i = 0; i < kBwdCRing; ++i) mbar_init(bar(B_G + i), AGG ? 4 : 6);
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tmap(&tm_x);
@@ -1062,12 +1113,13 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const int dt0 = item_dt0(pc.item), nsub = item_nsub(pc.item);
             const int64_t row = item_row(pc.item);
             const int hi = static_cast<int>(row % p.h);
-            const bool publish = pc.k0 > 0;   // the item continues to the left in another CTA: hand it the adjoint
+            const bool publish = !AGG && pc.k0 > 0;   // the item continues to the left in another CTA: hand it the adjoint
             // cut blockIdx.x is this CTA's left edge (it publishes there), cut blockIdx.x + 1 its right edge (it reads there)
             float *carry_out = p.carry + static_cast<int64_t>(blockIdx.x) * kCarryFloats;
             float hs_next = 0.f;
+            float g_reg[2] = {0.f, 0.f};   // AGG: the adjoint entering the current tile, channel m of each sub-tile (loaders)
             if (loader) {
-                if (pc.k1 < p.n_tiles) {   // left part of a cut item: the adjoint comes from the CTA that made the right part
+                if (!AGG && pc.k1 < p.n_tiles) {   // left part of a cut item: the adjoint comes from the CTA that made the right part
                     if (lane == 0) wait_carry(p.flags + blockIdx.x + 1, 2u * nsub, abort_flag, 23);
                     __syncwarp();
                 }
@@ -1078,16 +1130,21 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     hs_sm[slot0 * DT + m] =
                         ok ? p.tile_states[(row * p.n_tiles + (pc.k1 - 1)) * p.d + c0u + m] : 0.f;
                     float gv;
-                    if (pc.k1 < p.n_tiles)
+                    if (!AGG && pc.k1 < p.n_tiles) {
                         gv = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x + 1) * kCarryFloats + u * DT + m);
-                    else
+                    } else {
                         gv = (p.dfinal_state && ok) ? p.dfinal_state[row * p.d + c0u + m] : 0.f;
+                        if (AGG && pc.k1 < p.n_tiles && ok)
+                            gv = fold_adjoint_after(p.agg_vec + row * p.n_tiles * p.d + c0u + m,
+                                                    p.agg_fac + row * p.n_tiles, p.d, pc.k1, p.n_tiles, gv);
+                    }
                     g_sm[slot0 * DT + m] = gv;
+                    g_reg[u] = gv;
                 }
             }
             bar_sync(1, kEpiThreads);
             for (int u = 0; u < nsub; ++u) {
-                if (m == 0) mbar_arrive(bar(B_G + (it + u) % kBwdCRing));
+                if (!AGG && m == 0) mbar_arrive(bar(B_G + (it + u) % kBwdCRing));
                 if (loader && lane == 0) mbar_arrive(bar(B_G + (it + u) % kBwdCRing));
             }
             for (int k = pc.k1 - 1; k >= pc.k0; --k)
@@ -1108,6 +1165,12 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 if (u == 0 && (per_step || hi != cur_head)) { cur_head = hi; ++mt; }
                 // prefetch the saved state of the next tile to the left while this one is being finished
                 if (loader && k > pc.k0) hs_next = ch_ok ? ts_item[static_cast<int64_t>(k - 1) * p.d] : 0.f;
+                // AGG: this tile's adjoint aggregate, for the adjoint the tile on the left receives
+                float agg_g = 0.f, agg_f = 0.f;
+                if (AGG && loader && k > pc.k0) {
+                    agg_f = p.agg_fac[row * p.n_tiles + k];
+                    if (ch_ok) agg_g = p.agg_vec[(row * p.n_tiles + k) * p.d + c0 + m];
+                }
                 if (lane == 0) mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 15);
                 __syncwarp();
                 tc_fence_after_sync();
@@ -1155,7 +1218,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         const float2 hi2 = __ffma2_rn(F2, make_float2(gv.z, gv.w), make_float2(lam[c + 2], lam[c + 3]));
                         lam[c] = lo.x; lam[c + 1] = lo.y; lam[c + 2] = hi2.x; lam[c + 3] = hi2.y;
                     }
-                    if (m == 0) {
+                    if (m == 0 && !(AGG && k > pc.k0)) {
                         if (k > pc.k0) {  // row 0 of the adjoint is what the tile on the left receives
                             float *gout = g_sm + nslot * DT + cb;
 #pragma unroll
@@ -1171,7 +1234,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                                 __threadfence();
                                 atomicAdd(p.flags + blockIdx.x, 1u);
                             }
-                        } else if (p.dinit_state) {
+                        } else if (p.dinit_state && pc.k0 == 0) {
                             float *di = p.dinit_state + row * p.d + c0 + cb;
 #pragma unroll
                             for (int c = 0; c < 32; ++c)
@@ -1199,6 +1262,11 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     }
                 }
                 if (loader && k > pc.k0) {  // the saved state the tile on the left will need
+                    if (AGG) {   // and the adjoint entering it
+                        const float gn = fmaf(agg_f, g_reg[u], agg_g);
+                        g_reg[u] = gn;
+                        g_sm[nslot * DT + m] = gn;
+                    }
                     hs_sm[nslot * DT + m] = hs_next;
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar(B_G + nslot));
@@ -1321,6 +1389,31 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Self-test of the bounded waits: one small thread block waits, with a short limit, for something that never
+// happens - an mbarrier nobody arrives on (mode 0) or a global arrival counter nobody increments (mode 1) - through
+// the very wait functions the kernels above use.  The wait runs out, records 0x100 | site in the status word and
+// returns; nothing else is in flight (no copies, no tensor memory), so the kernel simply ends.
+// ---------------------------------------------------------------------------------------------
+__global__ void selftest_wait_kernel(int mode, uint32_t limit, const unsigned *never_set) {
+    __shared__ __align__(8) uint64_t bar_storage;
+    __shared__ int abort_flag_sm;
+    volatile int *abort_flag = &abort_flag_sm;
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(smem_u32(&bar_storage), 1);
+        fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (mode == 0) mbar_wait_limit(smem_u32(&bar_storage), 0, abort_flag, 0x7e, limit);
+        else wait_carry(never_set, 1u, abort_flag, 0x7f, limit);
+    }
+    __syncthreads();
+    // every other thread sees the abort flag the way the roles of the real kernels do
+    if (threadIdx.x == 1 && !*abort_flag) atomicCAS(&g_tc_status, 0, 0x3ff);
 }
 
 }  // namespace tc
@@ -1493,17 +1586,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// looked up once; the initialisation of a function-local static is safe when several host threads arrive together
 EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    static const EncodeTiledFn fn = [] {
         void *ptr = nullptr;
         cudaDriverEntryPointQueryResult qres;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
             qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
+            return reinterpret_cast<EncodeTiledFn>(ptr);
+        return static_cast<EncodeTiledFn>(nullptr);
+    }();
     return fn;
 }
 
@@ -1536,14 +1628,19 @@ int make_tmap(CUtensorMap *tm, const void *base, int64_t b, int64_t L, int64_t h
     return r == CUDA_SUCCESS ? EMA_OK : EMA_ERR_UNSUPPORTED;
 }
 
+// SM count of the CURRENT device, cached per device (a process may drive GPUs of different sizes)
 int sm_count() {
-    static int n = 0;
-    if (n == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;
+    constexpr int kMaxDev = 64;
+    static std::atomic<int> cache[kMaxDev];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev >= 0 && dev < kMaxDev) {
+        const int c = cache[dev].load(std::memory_order_relaxed);
+        if (c > 0) return c;
     }
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    if (dev >= 0 && dev < kMaxDev) cache[dev].store(n, std::memory_order_relaxed);
     return n;
 }
 
@@ -1563,20 +1660,24 @@ bool tc_tensor_ok(const void *base, int64_t d, int64_t sb, int64_t sl, int64_t s
 // ranges, for up to kMaxSplitGrid thread blocks (one per SM).  Its size does not depend on the problem.
 constexpr int kMaxSplitGrid = 512;
 static size_t sync_flag_bytes() { return static_cast<size_t>(kMaxSplitGrid + 1) * 4 / 256 * 256 + 256; }
-size_t tc_sync_bytes(int64_t, int64_t, int64_t) {
+static size_t carry_bytes() {
     return sync_flag_bytes() + static_cast<size_t>(kMaxSplitGrid + 1) * tc::kCarryFloats * sizeof(float);
 }
-static int g_split = -1;   // -1: not read yet; 0 / 1
-static bool split_enabled() {
-    if (g_split < 0) {
+// 0: whole items only; 1: cut items when that fills the GPU better (default); 2: as 1, and use the aggregate
+// schedule for every problem it can take, however small (tests)
+static std::atomic<int> g_split{-1};
+static int split_setting() {
+    int v = g_split.load(std::memory_order_relaxed);
+    if (v < 0) {
         const char *e = getenv("EMA_B200_SPLIT");
-        g_split = (e && e[0] == '0') ? 0 : 1;
+        v = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 1;
+        g_split.store(v, std::memory_order_relaxed);
     }
-    return g_split != 0;
+    return v;
 }
 int tc_set_split(int on) {
-    const int before = split_enabled() ? 1 : 0;
-    g_split = on ? 1 : 0;
+    const int before = split_setting();
+    g_split.store(on < 0 ? 0 : (on > 2 ? 2 : on), std::memory_order_relaxed);
     return before;
 }
 // SMs the split schedule leaves free for small kernels of other streams (a collective that overlaps the scan):
@@ -1590,30 +1691,92 @@ static int spare_sms() {
     }();
     return n;
 }
-// Decides the grid.  Whole items per CTA when they divide evenly (or when there is no scratch); otherwise one
-// CTA per SM, each with a contiguous range of tiles (tc::Sched).  Clears the arrival counters on the stream.
-static int plan_grid(const FusedParams &fp, int n_items, bool allow_split, cudaStream_t stream, int *grid, int *split,
-                     float **carry, unsigned **flags) {
+// Few work items: with one item per thread block fewer than this share (percent) of the SMs would have work.  Then the
+// items are cut into pieces that start from folded per-tile aggregates (one more pass over x, or dy, to make them).
+static int few_items_percent() {
+    static const int n = [] {
+        const char *e = getenv("EMA_B200_AGG_BELOW");
+        const int v = e ? atoi(e) : 65;
+        return v < 0 ? 0 : (v > 100 ? 100 : v);
+    }();
+    return n;
+}
+// Would the aggregate schedule be used for a problem of this size (given scratch)?  rows = scan rows.
+bool tc_wants_aggregates(int64_t rows, int64_t L, int64_t d) {
+    const int setting = split_setting();
+    if (setting == 0 || rows <= 0 || L <= 0 || d <= 0) return false;
     const int sms = sm_count();
+    const int64_t n_tiles = (L + tc::QT - 1) / tc::QT, n_dtiles = (d + tc::DT - 1) / tc::DT;
+    if (n_tiles < 2 || sms > kMaxSplitGrid) return false;
+    if (setting == 2) return true;
+    return n_tiles >= 4 && rows * n_dtiles * 100 < static_cast<int64_t>(sms) * few_items_percent();
+}
+// scratch of the tensor-core kernels for one direction: the carries of the split schedule, and one buffer of
+// per-tile aggregates when the problem is one the aggregate schedule would take
+size_t tc_sync_bytes(int64_t rows, int64_t L, int64_t d) {
+    return carry_bytes() + (tc_wants_aggregates(rows, L, d) ? tile_aggregate_bytes(rows, L, d) : 0);
+}
+
+static thread_local int g_last_schedule = -1;
+int tc_last_schedule() { return g_last_schedule; }
+
+// How a launch is laid out: the grid, the schedule, and how channel tiles are grouped into work items.
+struct Plan {
+    int grid, split, sub, n_groups, n_items;
+    float *carry;
+    unsigned *flags;
+    float *agg;
+};
+// Decides the schedule.  Aggregates (split 2) when there are few work items and the caller gave scratch for them;
+// otherwise whole items per CTA when they divide evenly (or when there is no scratch), else one CTA per SM, each with a
+// contiguous range of tiles (tc::Sched, split 1; clears the arrival counters on the stream).
+static int make_plan(const FusedParams &fp, bool allow_carry_split, bool allow_aggregates, cudaStream_t stream, Plan *pl) {
+    const int sms = sm_count();
+    const int64_t rows = fp.b * fp.h;
+    const int n_tiles = static_cast<int>((fp.L + tc::QT - 1) / tc::QT);
+    const int n_dtiles = static_cast<int>((fp.d + tc::DT - 1) / tc::DT);
+    const bool per_step = fp.decay_mode == EMA_DECAY_PER_STEP;
+    pl->carry = nullptr; pl->flags = nullptr; pl->agg = nullptr; pl->split = 0;
+    const bool have_carry_ws = fp.sync_ws && fp.sync_ws_bytes >= carry_bytes();
+    if (allow_aggregates && tc_wants_aggregates(rows, fp.L, fp.d) &&
+        fp.sync_ws && fp.sync_ws_bytes >= carry_bytes() + tile_aggregate_bytes(rows, fp.L, fp.d)) {
+        // tiles are dealt evenly whatever the item count, so a per-step decay always shares one matrix between two
+        // channel tiles
+        pl->sub = (per_step && n_dtiles > 1) ? 2 : 1;
+        pl->n_groups = (n_dtiles + pl->sub - 1) / pl->sub;
+        pl->n_items = static_cast<int>(rows * pl->n_groups);
+        const int64_t units = static_cast<int64_t>(pl->n_items) * n_tiles;
+        const int want = sms - spare_sms();
+        pl->grid = static_cast<int>(units < want ? units : want);
+        pl->split = 2;
+        pl->agg = reinterpret_cast<float *>(static_cast<uint8_t *>(fp.sync_ws) + carry_bytes());
+        return EMA_OK;
+    }
+    // With a per-step decay every tile needs its own matrix and the builders set the pace: let one matrix serve two
+    // channel tiles of the row, unless halving the number of work items would leave noticeably more SMs without one.
+    {
+        const int64_t single = rows * n_dtiles, paired = rows * ((n_dtiles + 1) / 2);
+        const int64_t busy_single = single < sms ? single : sms, busy_paired = paired < sms ? paired : sms;
+        pl->sub = (per_step && n_dtiles > 1 && busy_paired * 100 >= busy_single * 85) ? 2 : 1;
+    }
+    pl->n_groups = (n_dtiles + pl->sub - 1) / pl->sub;
+    pl->n_items = static_cast<int>(rows * pl->n_groups);
+    const int n_items = pl->n_items;
     const int rounds = (n_items + sms - 1) / sms;
-    *grid = (n_items + rounds - 1) / rounds;
-    *split = 0;
-    *carry = nullptr;
-    *flags = nullptr;
+    pl->grid = (n_items + rounds - 1) / rounds;
     // cutting pays when whole items would leave a noticeable share of the SM-rounds idle (256 items on 148 SMs: 13.5 %)
     const bool uneven = static_cast<int64_t>(rounds) * sms * 92 > static_cast<int64_t>(n_items) * 100;
-    // (with fewer items than SMs a cut cannot help: an item's tiles are a sequential chain, and the thread blocks that
-    // would share it only wait for one another - measured 30-40 % slower)
-    if (!allow_split || !split_enabled() || n_items < sms || sms > kMaxSplitGrid || !uneven || !fp.sync_ws ||
-        fp.sync_ws_bytes < tc_sync_bytes(fp.b, fp.h, fp.d))
+    // (with fewer items than SMs a cut that hands carries on cannot help: an item's tiles are a sequential chain, and
+    // the thread blocks that would share it only wait for one another - measured 30-40 % slower)
+    if (!allow_carry_split || split_setting() == 0 || n_items < sms || sms > kMaxSplitGrid || !uneven || !have_carry_ws)
         return EMA_OK;
     const size_t fb = sync_flag_bytes();
     cudaError_t e = cudaMemsetAsync(fp.sync_ws, 0, fb, stream);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
-    *flags = static_cast<unsigned *>(fp.sync_ws);
-    *carry = reinterpret_cast<float *>(static_cast<uint8_t *>(fp.sync_ws) + fb);
-    *grid = sms - spare_sms();
-    *split = 1;
+    pl->flags = static_cast<unsigned *>(fp.sync_ws);
+    pl->carry = reinterpret_cast<float *>(static_cast<uint8_t *>(fp.sync_ws) + fb);
+    pl->grid = sms - spare_sms();
+    pl->split = 1;
     return EMA_OK;
 }
 
@@ -1633,22 +1796,26 @@ int launch_fused_fwd_tc(const FusedParams &fp, cudaStream_t stream) {
     p.decay_mode = fp.decay_mode; p.convention = fp.convention; p.chunk = fp.chunk;
     p.n_tiles = static_cast<int>((fp.L + tc::QT - 1) / tc::QT);
     p.n_dtiles = static_cast<int>((fp.d + tc::DT - 1) / tc::DT);
-    // With a per-step decay every tile needs its own matrix and the builders set the pace: let one matrix serve two
-    // channel tiles of the row, unless halving the number of work items would leave noticeably more SMs without one.
-    {
-        const int64_t rows = fp.b * fp.h, sms = sm_count();
-        const int64_t single = rows * p.n_dtiles, paired = rows * ((p.n_dtiles + 1) / 2);
-        const int64_t busy_single = single < sms ? single : sms, busy_paired = paired < sms ? paired : sms;
-        p.sub = (fp.decay_mode == EMA_DECAY_PER_STEP && p.n_dtiles > 1 && busy_paired * 100 >= busy_single * 85) ? 2 : 1;
-    }
-    p.n_groups = (p.n_dtiles + p.sub - 1) / p.sub;
-    p.n_items = static_cast<int>(fp.b * fp.h * p.n_groups);
     p.n_chunks = fp.n_chunks;
-    int grid = 0;
-    // the sum of the log decays is accumulated per item by one CTA: no cutting when it is asked for
-    rc = plan_grid(fp, p.n_items, fp.log_decay_sum == nullptr, stream, &grid, &p.split, &p.carry, &p.flags);
+    // the sum of the log decays is accumulated per item by one CTA: no cutting when it is asked for; the weighted
+    // scan has no aggregate pass
+    Plan pl;
+    const bool weighted = fp.in_weight || fp.out_weight;
+    rc = make_plan(fp, fp.log_decay_sum == nullptr, fp.log_decay_sum == nullptr && !weighted, stream, &pl);
     if (rc) return rc;
-    auto kernel = (fp.in_weight || fp.out_weight) ? tc::ema_fwd_tc_kernel<true> : tc::ema_fwd_tc_kernel<false>;
+    p.sub = pl.sub; p.n_groups = pl.n_groups; p.n_items = pl.n_items;
+    p.split = pl.split; p.carry = pl.carry; p.flags = pl.flags;
+    p.agg_vec = p.agg_fac = nullptr;
+    if (pl.split == 2) {
+        rc = launch_tile_aggregates(fp, 0, pl.agg, stream);
+        if (rc) return rc;
+        p.agg_vec = pl.agg;
+        p.agg_fac = pl.agg + fp.b * fp.h * p.n_tiles * fp.d;
+    }
+    const int grid = pl.grid;
+    g_last_schedule = pl.split;
+    auto kernel = weighted ? tc::ema_fwd_tc_kernel<true, false>
+                           : (pl.split == 2 ? tc::ema_fwd_tc_kernel<false, true> : tc::ema_fwd_tc_kernel<false, false>);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kFwdSmemBytes);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     kernel<<<grid, tc::kThreads, tc::kFwdSmemBytes, stream>>>(tm_x, tm_y, p);
@@ -1674,23 +1841,26 @@ int launch_fused_bwd_tc(const FusedParams &fp, cudaStream_t stream) {
     p.decay_mode = fp.decay_mode; p.convention = fp.convention;
     p.n_tiles = static_cast<int>((fp.L + tc::QT - 1) / tc::QT);
     p.n_dtiles = static_cast<int>((fp.d + tc::DT - 1) / tc::DT);
-    {   // same pairing rule as the forward kernel
-        const int64_t rows = fp.b * fp.h, sms = sm_count();
-        const int64_t single = rows * p.n_dtiles, paired = rows * ((p.n_dtiles + 1) / 2);
-        const int64_t busy_single = single < sms ? single : sms, busy_paired = paired < sms ? paired : sms;
-        p.sub = (fp.decay_mode == EMA_DECAY_PER_STEP && p.n_dtiles > 1 && busy_paired * 100 >= busy_single * 85) ? 2 : 1;
-    }
-    p.n_groups = (p.n_dtiles + p.sub - 1) / p.sub;
-    p.n_items = static_cast<int>(fp.b * fp.h * p.n_groups);
     p.n_dt64 = static_cast<int>((fp.d + 63) / 64);
     p.head_partial_offset = kHeadPartialOffset(fp.b * fp.h);
-    int grid = 0;
-    rc = plan_grid(fp, p.n_items, true, stream, &grid, &p.split, &p.carry, &p.flags);
+    Plan pl;
+    rc = make_plan(fp, true, true, stream, &pl);
     if (rc) return rc;
-    cudaError_t e = cudaFuncSetAttribute(tc::ema_bwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         tc::kBwdSmemBytes);
+    p.sub = pl.sub; p.n_groups = pl.n_groups; p.n_items = pl.n_items;
+    p.split = pl.split; p.carry = pl.carry; p.flags = pl.flags;
+    p.agg_vec = p.agg_fac = nullptr;
+    if (pl.split == 2) {
+        rc = launch_tile_aggregates(fp, 1, pl.agg, stream);
+        if (rc) return rc;
+        p.agg_vec = pl.agg;
+        p.agg_fac = pl.agg + fp.b * fp.h * p.n_tiles * fp.d;
+    }
+    const int grid = pl.grid;
+    g_last_schedule = pl.split;
+    auto kernel = pl.split == 2 ? tc::ema_bwd_tc_kernel<true> : tc::ema_bwd_tc_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kBwdSmemBytes);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
-    tc::ema_bwd_tc_kernel<<<grid, tc::kThreads, tc::kBwdSmemBytes, stream>>>(tm_x, tm_g, tm_o, p);
+    kernel<<<grid, tc::kThreads, tc::kBwdSmemBytes, stream>>>(tm_x, tm_g, tm_o, p);
     return check_launch();
 }
 
@@ -1744,6 +1914,13 @@ int launch_fused_bwd_fma_tma(const FusedParams &fp, cudaStream_t stream) {
     const int64_t blocks = fp.b * fp.h * fp.n_dtiles;
     tmafeed::ema_bwd_fma_tma_kernel<<<static_cast<unsigned>(blocks), kFmaThreads, tmafeed::kBwdSmemBytes, stream>>>(
         tm_x, tm_g, fp);
+    return check_launch();
+}
+
+// Launches the bounded-wait self-test (see tc::selftest_wait_kernel); `scratch` is one zeroed 32-bit word in device
+// memory that nothing ever writes (mode 1 only).
+int launch_selftest_wait(int mode, unsigned polls, const unsigned *scratch, cudaStream_t stream) {
+    tc::selftest_wait_kernel<<<1, 32, 0, stream>>>(mode, polls, scratch);
     return check_launch();
 }
 

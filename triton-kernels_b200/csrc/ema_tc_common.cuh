@@ -41,14 +41,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  `abort_flag` lives in shared memory; `site` identifies the wait in the status word.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site,
+                                                uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
     }
     *abort_flag = 1;
     atomicCAS(&g_tc_status, 0, 0x100 | (site & 0xff));
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int site) {
+    return mbar_wait_limit(bar, parity, abort_flag, site, kWaitLimit);
 }
 
 __device__ __forceinline__ void fence_barrier_init() {

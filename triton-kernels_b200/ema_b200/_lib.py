@@ -52,8 +52,10 @@ def lib():
         "ema_b200_last_cuda_error": (ci, []),
         "ema_b200_error_string": (ctypes.c_char_p, [ci]),
         "ema_b200_device_status": (ci, [ci]),
+        "ema_b200_selftest_wait": (ci, [ci, ci, vp, vp]),
         "ema_b200_set_path": (ci, [ci]),
         "ema_b200_last_path": (ci, []),
+        "ema_b200_last_schedule": (ci, []),
         "ema_b200_set_split": (ci, [ci]),
         "ema_b200_tile_steps": (ci, [pp]),
         "ema_b200_tile_states_bytes": (sz, [pp]),
@@ -62,6 +64,7 @@ def lib():
         "ema_b200_fwd": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp, sz, vp]),
         "ema_b200_fwd_weighted": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp, sz, vp]),
         "ema_b200_bwd": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp, sz, vp]),
+        "ema_b200_fold_records": (ci, [vp, ci, ci, i64, i64, ci, vp, vp]),
         "ema_b200_static_scratch_limit": (sz, []),
         "ema_b200_bwd_static_scratch": (ci, [pp, vp, vp, vp, vp, vp, vp, vp]),
         "ema_b200_chunk_cumsum": (ci, [vp, i64, i64, vp, i64, i64, ci, vp]),

@@ -6,9 +6,10 @@ Two modes, neither of which exists in the reference project (it is single-GPU):
   data-path collective.  Only a time-invariant decay a[h] needs one all-reduce of h floats for its
   gradient.
 * sequence parallel - rank g holds the g-th contiguous segment of the sequence.  Every rank scans
-  its segment from a zero state, the ranks all-gather the per-row final state F[b,h,d] and the
-  summed log-decay logP[b,h] (kept in the log domain: the product of 65536 decays underflows), each
-  rank folds its predecessors into its incoming carry, and a fix-up pass re-scans only the prefix of
+  its segment from a zero state, the ranks all-gather one record each - the per-row final state
+  F[b,h,d] followed by the summed log-decay logP[b,h] (kept in the log domain: the product of 65536
+  decays underflows), written by the scan kernel straight into the send buffer - each rank folds
+  its predecessors into its incoming carry (one small kernel), and a fix-up pass re-scans only the prefix of
   the segment that the carry can still influence.  The backward mirrors it right to left with the
   adjoint carry.  Remote data always arrives in local memory through the collective before a kernel
   reads it.
@@ -22,6 +23,17 @@ import torch.distributed as dist
 from . import ops as _cuda_ops
 
 STOP_BELOW = 1e-12  # a carry attenuated below this no longer changes an fp32 result
+
+# Timing hook for benchmarks: set to a list and the sequence-parallel function appends (label, CUDA event) at its
+# stage boundaries (local scan / exchange and fold / re-scan), recorded on the current stream.  None: no events.
+trace = None
+
+
+def _mark(label, t):
+    if trace is not None and t.is_cuda:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record(torch.cuda.current_stream(t.device))
+        trace.append((label, ev))
 
 
 # ---- row sharding -----------------------------------------------------------------------------
@@ -94,43 +106,83 @@ def fold_adjoints(dinits, log_sums, after):
     return carry
 
 
-def _all_gather(t, group):
+def _gather_records(rec, group):
+    """[world, n] from every rank's flat record [n] (one collective)."""
     world = dist.get_world_size(group)
-    out = [torch.empty_like(t) for _ in range(world)]
-    dist.all_gather(out, t.contiguous(), group=group)
-    return out
+    out = torch.empty((world * rec.numel(),), dtype=rec.dtype, device=rec.device)
+    dist.all_gather_into_tensor(out, rec, group=group)
+    return out.view(world, rec.numel())
+
+
+def _fold(backend, records, rank, b, h, d, reverse):
+    """Folds the gathered records [world, b*h*d + b*h] into the carry entering segment `rank`: one kernel when the
+    backend has one (CUDA), otherwise the torch loops above (the CPU stand-in of the tests)."""
+    rows = b * h
+    if hasattr(backend, "fold_records"):
+        return backend.fold_records(records, rank, rows, d, reverse=reverse).view(b, h, d)
+    vecs = [r[:rows * d].view(b, h, d) for r in records]
+    logs = [r[rows * d:].view(b, h) for r in records]
+    return fold_adjoints(vecs, logs, rank) if reverse else fold_carries(vecs, logs, rank)
 
 
 class _SeqParallelEma(torch.autograd.Function):
+    """Local scan from a zero state, ONE all-gather of [final state | summed log decay] per direction, fold, and a
+    re-scan of the part of the segment the incoming carry can still change."""
+
     @staticmethod
     def forward(ctx, x, a, group, backend, stop_below):
         rank, world = dist.get_rank(group), dist.get_world_size(group)
-        r = backend.ema_fwd(x, a, want_tile_states=True, want_final=True, want_log_decay_sum=True)
-        finals = _all_gather(r["final_state"], group)
-        log_sums = _all_gather(r["log_decay_sum"], group)
+        b, L, h, d = x.shape
+        rows = b * h
+        # the record this rank contributes: the kernel writes both parts straight into it
+        rec = torch.empty((rows * d + rows,), dtype=torch.float32, device=x.device)
+        fin, lds = rec[:rows * d].view(b, h, d), rec[rows * d:].view(b, h)
+        _mark("fwd_begin", x)
+        r = backend.ema_fwd(x, a, want_tile_states=True, want_final=True, want_log_decay_sum=True, final_out=fin,
+                            log_decay_sum_out=lds)
+        if r["final_state"].data_ptr() != fin.data_ptr():   # a backend that allocates its own outputs
+            fin.copy_(r["final_state"])
+            lds.copy_(r["log_decay_sum"])
         y, ts = r["y"], r["tile_states"]
-        carry_in = None
-        if rank > 0:
-            carry_in = fold_carries(finals, log_sums, rank)
-            backend.ema_fwd(x, a, init_state=carry_in, stop_below=stop_below, out=y, tile_states=ts)
-        ctx.save_for_backward(x, a, ts, torch.stack(log_sums))
+        _mark("fwd_local", x)
+        if world > 1:
+            records = _gather_records(rec, group)
+            carry_in = _fold(backend, records, rank, b, h, d, reverse=False) if rank > 0 else None
+            _mark("fwd_exchange", x)
+            if rank > 0:
+                backend.ema_fwd(x, a, init_state=carry_in, stop_below=stop_below, out=y, tile_states=ts)
+        _mark("fwd_end", x)
+        ctx.save_for_backward(x, a, ts, lds)
         ctx.group, ctx.backend, ctx.stop_below = group, backend, stop_below
         ctx.rank, ctx.world = rank, world
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, a, ts, log_sums = ctx.saved_tensors
+        x, a, ts, lds = ctx.saved_tensors
         backend, group = ctx.backend, ctx.group
-        r = backend.ema_bwd(x, a, dy, ts, want_dinit=True)
-        dinits = _all_gather(r["dinit_state"], group)
-        if ctx.rank < ctx.world - 1:
-            dfinal = fold_adjoints(dinits, list(log_sums), ctx.rank)
-            r = backend.ema_bwd(x, a, dy, ts, dfinal_state=dfinal, stop_below=ctx.stop_below, dx=r["dx"],
-                                workspace=r["workspace"], ddecay=r["ddecay"])
+        b, L, h, d = x.shape
+        rows = b * h
+        rec = torch.empty((rows * d + rows,), dtype=torch.float32, device=x.device)
+        dinit = rec[:rows * d].view(b, h, d)
+        rec[rows * d:].copy_(lds.reshape(-1))
+        _mark("bwd_begin", x)
+        r = backend.ema_bwd(x, a, dy, ts, want_dinit=True, dinit_out=dinit)
+        if r["dinit_state"].data_ptr() != dinit.data_ptr():
+            dinit.copy_(r["dinit_state"])
+        _mark("bwd_local", x)
+        if ctx.world > 1:
+            records = _gather_records(rec, group)
+            last = ctx.rank == ctx.world - 1
+            dfinal = None if last else _fold(backend, records, ctx.rank, b, h, d, reverse=True)
+            _mark("bwd_exchange", x)
+            if not last:
+                r = backend.ema_bwd(x, a, dy, ts, dfinal_state=dfinal, stop_below=ctx.stop_below, dx=r["dx"],
+                                    workspace=r["workspace"], ddecay=r["ddecay"])
         da = r["ddecay"]
-        if a.dim() == 1:
+        if a.dim() == 1 and ctx.world > 1:
             dist.all_reduce(da, group=group)
+        _mark("bwd_end", x)
         return r["dx"], da, None, None, None
 
 

@@ -49,6 +49,12 @@ def _check_inputs(x, decay):
     return x, decay
 
 
+def _check_device_status(dev):
+    """Reads and clears the device status word (synchronises `dev`); raises if a bounded wait ran out."""
+    with torch.cuda.device(dev):
+        check("ema_b200_device_status", lib().ema_b200_device_status(1))
+
+
 def n_tiles_of(x, decay, convention=CONV_NORTH_STAR):
     """(tile_steps, n_tiles) the library uses for this problem."""
     p = _problem(x, decay, x, convention=convention)
@@ -60,7 +66,8 @@ def n_tiles_of(x, decay, convention=CONV_NORTH_STAR):
 
 def ema_fwd(x, decay, *, chunk=0, prescaled_log=False, init_state=None, want_chunk_states=False,
             want_tile_states=False, want_final=False, want_log_decay_sum=False, stop_below=0.0,
-            out=None, tile_states=None, workspace=None, in_weight=None, out_weight=None):
+            out=None, tile_states=None, workspace=None, in_weight=None, out_weight=None, final_out=None,
+            log_decay_sum_out=None, check_status=False):
     """Forward scan.  Returns a dict with 'y' and the requested extras.
 
     x[b,L,h,d] (fp32|bf16, last dim contiguous), decay a[b,L,h] or a[h] (fp32).
@@ -70,6 +77,10 @@ def ema_fwd(x, decay, *, chunk=0, prescaled_log=False, init_state=None, want_chu
     over all SMs; pass it back in to avoid the allocation, never to two calls that may overlap.
     `in_weight` / `out_weight` (fp32 [b,L,h], per-step decay only) fold per-step weights into the same pass:
     s_t = a_t s_{t-1} + in_weight_t x_t, y_t = out_weight_t s_t; the returned states are the s themselves.
+    `final_out` (fp32 [b,h,d]) / `log_decay_sum_out` (fp32 [b,h]), both contiguous, receive the final state and the
+    summed log decay in place (e.g. two views of one buffer that is then sent to other ranks).
+    `check_status=True` reads the device status word after the call (this synchronises the device) and raises
+    EmaB200Error(EMA_ERR_TIMEOUT) if a bounded device-side wait ran out.
     """
     x, decay = _check_inputs(x, decay)
     dev = require_cuda(x, decay, init_state, out, tile_states, in_weight, out_weight)
@@ -103,11 +114,15 @@ def ema_fwd(x, decay, *, chunk=0, prescaled_log=False, init_state=None, want_chu
         nt = (L + tsteps - 1) // tsteps if tsteps > 0 else 0
         ts = tile_states if tile_states is not None else torch.empty((b * h, nt, d), dtype=torch.float32, device=dev)
         res["tile_states"] = ts
-    if want_final:
-        fin = torch.empty((b, h, d), dtype=torch.float32, device=dev)
+    if want_final or final_out is not None:
+        fin = final_out if final_out is not None else torch.empty((b, h, d), dtype=torch.float32, device=dev)
+        if tuple(fin.shape) != (b, h, d) or fin.dtype != torch.float32 or not fin.is_contiguous():
+            raise ValueError("final_out must be contiguous fp32 [b, h, d]")
         res["final_state"] = fin
-    if want_log_decay_sum:
-        lds = torch.zeros((b, h), dtype=torch.float32, device=dev)
+    if want_log_decay_sum or log_decay_sum_out is not None:
+        lds = log_decay_sum_out if log_decay_sum_out is not None else torch.zeros((b, h), dtype=torch.float32, device=dev)
+        if tuple(lds.shape) != (b, h) or lds.dtype != torch.float32 or not lds.is_contiguous():
+            raise ValueError("log_decay_sum_out must be contiguous fp32 [b, h]")
         res["log_decay_sum"] = lds
     if init_state is not None:
         if tuple(init_state.shape) != (b, h, d) or init_state.dtype != torch.float32:
@@ -128,11 +143,13 @@ def ema_fwd(x, decay, *, chunk=0, prescaled_log=False, init_state=None, want_chu
                                  ptr(fin), ptr(lds), ctypes.c_float(stop_below), ptr(workspace), ws_size,
                                  stream_ptr(dev))
     check("ema_b200_fwd_weighted" if weighted else "ema_b200_fwd", rc)
+    if check_status:
+        _check_device_status(dev)
     return res
 
 
 def ema_bwd(x, decay, dy, tile_states, *, prescaled_log=False, dfinal_state=None, want_dinit=False,
-            stop_below=0.0, dx=None, workspace=None, ddecay=None):
+            stop_below=0.0, dx=None, workspace=None, ddecay=None, dinit_out=None, check_status=False):
     """Backward scan.  Returns a dict with 'dx', 'ddecay' (shaped like decay) and optionally 'dinit_state'.
 
     `dx`, `workspace`, `ddecay` let a caller re-scan a suffix in place (sequence-parallel fix-up):
@@ -156,7 +173,11 @@ def ema_bwd(x, decay, dy, tile_states, *, prescaled_log=False, dfinal_state=None
     nbytes = L_.ema_b200_bwd_workspace_bytes(ctypes.byref(p))
     if workspace is None:
         workspace = torch.empty(((nbytes + 3) // 4,), dtype=torch.float32, device=dev)
-    dinit = torch.empty((b, h, d), dtype=torch.float32, device=dev) if want_dinit else None
+    dinit = None
+    if want_dinit or dinit_out is not None:
+        dinit = dinit_out if dinit_out is not None else torch.empty((b, h, d), dtype=torch.float32, device=dev)
+        if tuple(dinit.shape) != (b, h, d) or dinit.dtype != torch.float32 or not dinit.is_contiguous():
+            raise ValueError("dinit_out must be contiguous fp32 [b, h, d]")
     if dfinal_state is not None:
         if tuple(dfinal_state.shape) != (b, h, d) or dfinal_state.dtype != torch.float32:
             raise ValueError("dfinal_state must be fp32 [b, h, d]")
@@ -166,10 +187,28 @@ def ema_bwd(x, decay, dy, tile_states, *, prescaled_log=False, dfinal_state=None
                              ptr(ddecay), ptr(dfinal_state), ptr(dinit), ctypes.c_float(stop_below),
                              ptr(workspace), ctypes.c_size_t(workspace.numel() * 4), stream_ptr(dev))
     check("ema_b200_bwd", rc)
+    if check_status:
+        _check_device_status(dev)
     res = {"dx": dx, "ddecay": ddecay, "workspace": workspace}
-    if want_dinit:
+    if dinit is not None:
         res["dinit_state"] = dinit
     return res
+
+
+def fold_records(records, rank, rows, d, reverse=False, out=None):
+    """State (reverse=False) or adjoint (reverse=True) entering segment `rank`, folded from the gathered
+    per-rank records [world, rows*d + rows] = [zero-state final (or dinit) | summed log decay]."""
+    dev = require_cuda(records, out)
+    if records.dtype != torch.float32 or records.dim() != 2 or records.shape[1] != rows * d + rows or \
+            not records.is_contiguous():
+        raise ValueError("records must be contiguous fp32 [world, rows*d + rows]")
+    if out is None:
+        out = torch.empty((rows, d), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib().ema_b200_fold_records(ptr(records), int(records.shape[0]), int(rank), rows, d,
+                                         1 if reverse else 0, ptr(out), stream_ptr(dev))
+    check("ema_b200_fold_records", rc)
+    return out
 
 
 def ema_bwd_static_scratch(x, decay, dy, tile_states, dx, ddecay, *, prescaled_log=False):
