@@ -647,8 +647,13 @@ def run_gpu(args):
         e2e_step()
         pipe.wait()
         torch.cuda.synchronize()
-        if not torch.equal(hy, y.cpu()) or not torch.equal(hdx, dx.cpu()):
-            raise RuntimeError("host pipeline result differs from the device-resident result")
+        # Against the device-resident result.  The pipeline's batch slices are problems with few work items, which the
+        # kernels cut into pieces that start from per-tile aggregates, while the whole batch runs item by item: the two
+        # agree to within the rounding of the bf16 decay matrices, not bit for bit.
+        e2e_err = max(float((hy.float() - y.cpu().float()).abs().max() / y.float().abs().max()),
+                      float((hdx.float() - dx.cpu().float()).abs().max() / dx.float().abs().max()))
+        if not e2e_err <= 2e-2:
+            raise RuntimeError(f"host pipeline result differs from the device-resident result ({e2e_err:.3e})")
         if world > 1:
             dist.barrier()
         s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -670,6 +675,7 @@ def run_gpu(args):
                "api": "ema_b200.HostPipeline.run(sync=False) per step + wait(): pinned host x, dy, a -> y, dx, da; "
                       "8 batch slices, H2D / kernels / D2H on three streams, consecutive steps overlap",
                "gpu_launches_per_step": pipe.n_launches, "numa_node": numa_node,
+               "max_rel_diff_vs_device_resident": e2e_err,
                "host_link_gbs_each_way_all_ranks": each_way * world / (e2e_ms * 1e-3) / 1e9,
                "limit": "host-to-device and device-to-host copies (PCIe and host memory), not the kernels: all ranks "
                         "of the node share one host, so with N > 1 the aggregate copy rate each way "

@@ -189,6 +189,23 @@ int ema_b200_bwd(const ema_b200_problem *p, const void *x, const float *decay, c
                  float *dinit_state, float stop_below, void *workspace, size_t workspace_bytes,
                  void *stream);
 
+/* Backward of ema_b200_fwd_weighted, in one pass over x and dy: with lambda_t = out_weight_t dy_t + a_{t+1} lambda_{t+1}
+ *     dx_t = in_weight_t lambda_t,                d decay_t      = sum_d lambda_t s_{t-1}   (times a_t for a log decay),
+ *     d in_weight_t = sum_d lambda_t x_t,          d out_weight_t = sum_d dy_t s_t .
+ * With gradients the reference's heads-style entry point (kernels/ema_combined.py:100; its own backward is a stub,
+ * :89-92) thus needs no elementwise pass over x, dy or the result around the scan: the gradients of dt, A, B, C follow
+ * from these three [b, L, h] tensors by the chain rule on [b, L, h]-sized data.
+ *   in_weight / out_weight  as in the forward (null: the convention's input weight / 1); per-step decay only
+ *   din_weight, dout_weight fp32 [b, L, h] with the decay's strides; required when the weight is given, else null
+ *   tile_states             the states s saved by the weighted forward
+ *   workspace               ema_b200_bwd_weighted_workspace_bytes(p) bytes, 16-byte aligned
+ * Runs on the CUDA cores for both element types (fp32 state, exact fp32 arithmetic). */
+size_t ema_b200_bwd_weighted_workspace_bytes(const ema_b200_problem *p);
+int ema_b200_bwd_weighted(const ema_b200_problem *p, const void *x, const float *decay, const float *in_weight,
+                          const float *out_weight, const void *dy, const float *tile_states, void *dx, float *ddecay,
+                          float *din_weight, float *dout_weight, const float *dfinal_state, float *dinit_state,
+                          void *workspace, size_t workspace_bytes, void *stream);
+
 /* ---- sequence-parallel carry fold ------------------------------------------------------------
  * (The reference is single-GPU; the recurrence folded here is its chunk-level carry,
  * kernels/ema_kernels/ema_state_pass.py:100-120, h <- exp(cs_last) h + S, applied to whole segments.)
@@ -250,10 +267,16 @@ int ema_b200_chunk_scan(const void *X, const float *cs, const float *h, void *ou
 /* _ema_chunk_scan_bwd_dstates, kernels/ema_kernels_bwd/ema_scan_bwd.py:132 (kernel :39). */
 int ema_b200_bwd_dstates(const float *cs, const void *dout, float *dh, int dtype, int64_t B,
                          int64_t L, int64_t T, int Q, void *stream);
-/* _ema_state_passing_bwd, kernels/ema_kernels_bwd/ema_state_passing_bwd_dstates.py:103 (kernel :20). */
+/* _ema_state_passing_bwd, kernels/ema_kernels_bwd/ema_state_passing_bwd_dstates.py:103 (kernel :20).
+ * workspace (optional, ema_b200_state_passing_bwd_workspace_bytes(B, C, T) bytes, 4-byte aligned): per-warp
+ * partial dot products [B, C, ceil(T/128)], the counterpart of the partial-sum buffer the reference's wrapper
+ * allocates (:134-142).  With it (and T a multiple of 4, 16-byte aligned tensors) a batch row is spread over T / 128
+ * thread blocks with 128-bit accesses and the partials are summed in a fixed order by a second kernel; without it
+ * one thread block walks a whole row (T <= 16384). */
+size_t ema_b200_state_passing_bwd_workspace_bytes(int64_t B, int64_t C, int64_t T);
 int ema_b200_state_passing_bwd(const float *h, const float *cs_last, int64_t cl_sb, int64_t cl_sc,
                                const float *dh, float *dS, float *ddA_last, int64_t B, int64_t C,
-                               int64_t T, void *stream);
+                               int64_t T, void *workspace, size_t workspace_bytes, void *stream);
 /* _chunk_scan_chunk_state_bwd_dx, kernels/ema_kernels_bwd/ema_chunk_scan_chunk_state_bwd_dx.py:208 (kernel :69). */
 int ema_b200_bwd_dx(const float *cs, const void *dout, const float *dS, void *dx, int dtype,
                     int64_t B, int64_t L, int64_t T, int Q, void *stream);

@@ -100,4 +100,7 @@ def test_stage_entry_points_reject_bad_sizes(ema_lib):
     assert ema_lib.ema_b200_chunk_cumsum(ok, 1, 1, ok, 0, 8, 4, None) == -1
     assert ema_lib.ema_b200_chunk_state(ok, ok, ok, 0, 1, 8, 4, 0, None) == -1
     assert ema_lib.ema_b200_chunk_scan(ok, ok, ok, None, 0, 1, 8, 4, 4, None) == -1
-    assert ema_lib.ema_b200_state_passing_bwd(ok, ok, 1, 1, ok, ok, ok, 1, 2, 1 << 20, None) == -3
+    # without a workspace one thread block walks a whole row: refused beyond 16384 channels
+    assert ema_lib.ema_b200_state_passing_bwd(ok, ok, 1, 1, ok, ok, ok, 1, 2, 1 << 20, None, 0, None) == -3
+    assert ema_lib.ema_b200_state_passing_bwd_workspace_bytes(2, 3, 1024) == 2 * 3 * 8 * 4
+    assert ema_lib.ema_b200_state_passing_bwd_workspace_bytes(2, 3, 1023) == 0

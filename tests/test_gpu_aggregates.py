@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import BF16_REL, assert_close_bf16, make_inputs, oracle_fwd_bwd
+from helpers import BF16_REL, assert_close_bf16, assert_close_da_head, make_inputs, oracle_fwd_bwd
 from oracle import ema_oracle as eo
 
 pytestmark = pytest.mark.gpu
@@ -48,12 +48,17 @@ def test_pieces_started_from_aggregates_match_the_oracle(shape, per_head, forced
     y_ref, dx_ref, da_ref = oracle_fwd_bwd(np_in)
     assert_close_bf16(f["y"], y_ref, "y")
     assert_close_bf16(g["dx"], dx_ref, "dx")
-    assert_close_bf16(g["ddecay"], da_ref, "da")
+    if per_head:
+        assert_close_da_head(g["ddecay"], da_ref, np_in, y_ref, dx_ref)
+    else:
+        assert_close_bf16(g["ddecay"], da_ref, "da")
     # the whole-item schedule of the same kernels
     lib.ema_b200_set_split(0)
     f0, g0, sf0, _ = _run(x, a, dy, lib)
     lib.ema_b200_set_split(2)
     assert sf0 == (1, 0)
+    if per_head:   # the decay gradient of the whole-item schedule meets the same bound
+        assert_close_da_head(g0["ddecay"], da_ref, np_in, y_ref, dx_ref, "da (whole items)")
     for got, ref, what in ((f["y"], f0["y"], "y"), (g["dx"], g0["dx"], "dx"), (f["final_state"], f0["final_state"], "final"),
                            (f["tile_states"], f0["tile_states"], "tile states"), (g["dinit_state"], g0["dinit_state"], "dinit")):
         ref = ref.float()
@@ -124,7 +129,7 @@ def test_few_items_take_the_aggregate_schedule_by_default(ema_lib):
     y_ref, dx_ref, da_ref = oracle_fwd_bwd(np_in)
     assert_close_bf16(f["y"], y_ref, "y")
     assert_close_bf16(g["dx"], dx_ref, "dx")
-    assert_close_bf16(g["ddecay"], da_ref, "da")
+    assert_close_da_head(g["ddecay"], da_ref, np_in, y_ref, dx_ref)
     # many items: the schedule is not used (256 items), nor when the summed log decay is asked for
     x2, a2, _, _ = make_inputs(13, 16, 512, 2, 1024, per_head=True, dtype=torch.bfloat16)
     ops.ema_fwd(x2, a2)

@@ -184,6 +184,13 @@ def test_empty_and_bad_arguments():
     E = _ema()
     y = E.ema_fwd(torch.zeros(2, 0, 2, 8, device="cuda"), torch.zeros(2, 0, 2, device="cuda"), want_final=True)
     assert y["y"].shape == (2, 0, 2, 8) and torch.all(y["final_state"] == 0)
+    # no channels: the decay gradient is an empty sum for every step (a caller's buffer must not keep its old contents)
+    for dtype in (torch.float32, torch.bfloat16):
+        x0 = torch.zeros(2, 5, 2, 0, device="cuda", dtype=dtype)
+        a0 = torch.full((2, 5, 2), 0.9, device="cuda")
+        ts0 = E.ema_fwd(x0, a0, want_tile_states=True)["tile_states"]
+        r0 = E.ema_bwd(x0, a0, x0, ts0, ddecay=torch.full_like(a0, float("nan")))
+        assert r0["dx"].shape == (2, 5, 2, 0) and bool((r0["ddecay"] == 0).all())
     with pytest.raises(ValueError):
         E.ema_fwd(torch.zeros(2, 4, 2, 8, device="cuda"), torch.zeros(2, 4, 3, device="cuda"))
     with pytest.raises(TypeError):

@@ -47,11 +47,23 @@ def test_tensor_core_and_cuda_core_paths_agree(seed, ema_lib):
             got, ref = outs[0][i], outs[1][i]
             if got is None:
                 continue
-            # a per-head decay gradient is one number per head, the sum of b*L*d terms of either sign: its error is
-            # relative to the size of the terms, not of their sum
-            tol = 0.15 if (name == "da" and per_head) else 1.25 * BF16_REL
+            tol = 1.25 * BF16_REL
             scale = max(float(ref.abs().max()), 1e-3)
             err = float((got - ref).abs().max()) / scale
+            if name == "da" and per_head:
+                # A per-head decay gradient is one number per head, the sum of b*L*d terms lambda * z of either sign
+                # (z = y_prev - x, or a * y_prev for the log convention) that largely cancel: allow one bf16 rounding
+                # (2^-8) of every term with independent signs on top of the relative tolerance.  The terms are rebuilt
+                # from the CUDA-core path's own y and dx.
+                y1, dx1 = outs[1][0].double(), outs[1][2].double()
+                a4 = a.double().view(1, 1, h, 1)
+                lam = dx1 if conv else dx1 / torch.where(a4 == 1.0, torch.ones_like(a4), 1.0 - a4)
+                first = init.double().unsqueeze(1) if init is not None else torch.zeros_like(y1[:, :1])
+                y_prev = torch.cat([first, y1[:, :-1]], dim=1)
+                z = a4 * y_prev if conv else y_prev - x.double()
+                norm = (lam * z).pow(2).sum(dim=(0, 1, 3)).sqrt()
+                bad = (got.double() - ref.double()).abs() > tol * ref.double().abs() + 2.0 ** -8 * norm + 1e-3
+                err = float("inf") if bool(bad.any()) else 0.0
             if not bool(torch.isfinite(got).all()) or err > tol:
                 failures.append((dict(b=b, L=L, h=h, d=d, per_head=per_head, conv=conv, strided=strided, lohi=(lo, hi),
                                       init=init is not None, dfin=dfin is not None, chunk=chunk), name, err))

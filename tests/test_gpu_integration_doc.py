@@ -1,7 +1,8 @@
-"""The binding stubs printed in INTEGRATION.md are executed as they stand (only the library path is filled in) and
-their results compared with the package's own entry points."""
+"""The binding stubs a maintainer of the reference would add (triton-kernels_b200/examples/reference_binding_stub.py, the
+file the integration notes quote) are imported as they stand and their results compared with the package's own entry
+points."""
+import importlib.util
 import os
-import re
 
 import pytest
 import torch
@@ -12,15 +13,12 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def _stub_namespace(ema_lib):
-    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
-    blocks = re.findall(r"```python\n(.*?)```", text, flags=re.S)
-    stubs = [b for b in blocks if "_lib" in b and "def " in b]
-    assert len(stubs) >= 2, "expected the forward stub and the weighted-forward stub"
-    ns = {}
-    for src in stubs:
-        src = src.replace('ctypes.CDLL("libema_b200.so")', f'ctypes.CDLL({ema_lib._name!r})')
-        exec(compile(src, "INTEGRATION.md", "exec"), ns)
-    return ns
+    path = os.path.join(ROOT, "triton-kernels_b200", "examples", "reference_binding_stub.py")
+    os.environ.setdefault("EMA_B200_LIB", ema_lib._name)
+    spec = importlib.util.spec_from_file_location("reference_binding_stub", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return vars(mod)
 
 
 def test_forward_stub(ema_lib):

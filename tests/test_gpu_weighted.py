@@ -113,3 +113,81 @@ def test_output_weight_alone_keeps_the_conventions_input_weight(dtype, ema_lib):
         assert torch.equal(got, want)
     else:   # the plain result was rounded to bf16 before the multiplication, the weighted one after it
         assert float((got - want).abs().max()) <= BF16_REL * float(want.abs().max())
+
+
+# ---- weighted backward ---------------------------------------------------------------------------------------------
+def _loop_with_grads(x, dec, w, c, dy, log_conv, init, dfin):
+    """The weighted recurrence as a float64 torch loop (the sequential definition of the reference's loops,
+    kernels/tests/ema_bwd/_ema_full_bwd.py:24-34, with per-step input and output weights), differentiated by autograd."""
+    leaves = {k: (None if v is None else v.detach().double().cpu().requires_grad_(True))
+              for k, v in dict(x=x, dec=dec, w=w, c=c, init=init).items()}
+    xx, dd = leaves["x"], leaves["dec"]
+    b, L, h, d = xx.shape
+    a = torch.exp(dd) if log_conv else dd
+    win = leaves["w"] if w is not None else (torch.ones_like(a) if log_conv else 1.0 - a)
+    s = torch.zeros(b, h, d, dtype=torch.float64) if init is None else leaves["init"]
+    ys = []
+    for t in range(L):
+        s = a[:, t].unsqueeze(-1) * s + win[:, t].unsqueeze(-1) * xx[:, t]
+        ys.append(s if c is None else leaves["c"][:, t].unsqueeze(-1) * s)
+    y = torch.stack(ys, dim=1)
+    loss = (y * dy.double().cpu()).sum()
+    if dfin is not None:
+        loss = loss + (s * dfin.double().cpu()).sum()
+    loss.backward()
+    return {k: (None if v is None else v.grad) for k, v in leaves.items()}
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("which", ["both", "in", "out"])
+@pytest.mark.parametrize("log_conv", [False, True])
+@pytest.mark.parametrize("shape", [(2, 300, 2, 64), (1, 261, 3, 100), (3, 130, 2, 256)])
+def test_weighted_backward_matches_autograd_of_the_loop(shape, log_conv, which, dtype, ema_lib):
+    from ema_b200 import ops
+    b, L, h, d = shape
+    x, a, w, c = _inputs(40 + L, b, L, h, d, dtype)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    dy = torch.randn((b, L, h, d), generator=g, device="cuda").to(dtype)
+    init = torch.randn((b, h, d), generator=g, device="cuda")
+    dfin = torch.randn((b, h, d), generator=g, device="cuda")
+    dec = torch.log(a) if log_conv else a
+    w_ = w if which in ("both", "in") else None
+    c_ = c if which in ("both", "out") else None
+    f = ops.ema_fwd(x, dec, prescaled_log=log_conv, init_state=init, want_tile_states=True, in_weight=w_, out_weight=c_)
+    r = ops.ema_bwd_weighted(x, dec, dy, f["tile_states"], in_weight=w_, out_weight=c_, prescaled_log=log_conv,
+                             dfinal_state=dfin, want_dinit=True)
+    torch.cuda.synchronize()
+    ref = _loop_with_grads(x.float(), dec, w_, c_, dy.float(), log_conv, init, dfin)
+
+    def close(got, want, what):
+        got, want = got.float().cpu(), want.float()
+        scale = max(float(want.abs().max()), 1e-6)
+        err = float((got - want).abs().max())
+        tol = BF16_REL * scale if dtype == torch.bfloat16 else 1e-4 + 2e-5 * scale
+        assert err <= tol, f"{what}: {err:.3e} > {tol:.3e} (scale {scale:.3e})"
+
+    close(r["dx"], ref["x"], "dx")
+    close(r["ddecay"], ref["dec"], "ddecay")
+    close(r["dinit_state"], ref["init"], "dinit")
+    if w_ is not None:
+        close(r["din_weight"], ref["w"], "din_weight")
+    else:
+        assert "din_weight" not in r
+    if c_ is not None:
+        close(r["dout_weight"], ref["c"], "dout_weight")
+    assert ema_lib.ema_b200_device_status(1) == 0
+
+
+def test_weighted_backward_argument_checks(ema_lib):
+    from ema_b200 import ops
+    x, a, w, c = _inputs(3, 1, 64, 2, 32, torch.float32)
+    ts = ops.ema_fwd(x, a, want_tile_states=True, in_weight=w)["tile_states"]
+    with pytest.raises(ValueError):
+        ops.ema_bwd_weighted(x, a[0, 0].contiguous(), x, ts, in_weight=w)          # per-head decay
+    with pytest.raises(ValueError):
+        ops.ema_bwd_weighted(x, a, x, ts, in_weight=w[:, :10])                     # weight of the wrong shape
+    # no channels: every per-step gradient is an empty sum
+    x0 = torch.zeros(1, 5, 2, 0, device="cuda")
+    a0 = torch.full((1, 5, 2), 0.9, device="cuda")
+    r = ops.ema_bwd_weighted(x0, a0, x0, torch.zeros(2, 1, 0, device="cuda"), in_weight=a0, out_weight=a0)
+    assert bool((r["ddecay"] == 0).all()) and bool((r["din_weight"] == 0).all()) and bool((r["dout_weight"] == 0).all())

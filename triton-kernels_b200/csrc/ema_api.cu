@@ -248,6 +248,14 @@ extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const floa
             // ddecay[h] may be strided: clear element by element through a 2-D memset
             e = cudaMemset2DAsync(ddecay, static_cast<size_t>(p->a_sh > 0 ? p->a_sh : 1) * 4, 0, 4,
                                   static_cast<size_t>(p->h), st);
+        } else if (p->decay_mode == EMA_DECAY_PER_STEP && ddecay && p->L > 0) {
+            // no channels: the gradient of every step's decay is an empty sum (the reduction kernel writes zeros)
+            FusedParams fz;
+            fill_params(fz, p, 1);
+            fz.n_dtiles = 0;
+            fz.da_partial = static_cast<float *>(workspace);
+            const int rz = launch_da_reduce(fz, ddecay, kFmaTile, st);
+            if (rz) return rz;
         }
         if (e == cudaSuccess && dinit_state && p->d > 0) {
             e = dfinal_state ? cudaMemcpyAsync(dinit_state, dfinal_state, rows * p->d * 4, cudaMemcpyDeviceToDevice, st)
@@ -289,4 +297,64 @@ extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const floa
         if (rc) return rc;
     }
     return launch_da_reduce(fp, ddecay, kFmaTile, st);
+}
+
+
+// ---- weighted backward ----------------------------------------------------------------------------------------
+extern "C" size_t ema_b200_bwd_weighted_workspace_bytes(const ema_b200_problem *p) {
+    if (check_problem(p) != EMA_OK || p->decay_mode != EMA_DECAY_PER_STEP) return 0;
+    return 3 * bwd_partial_bytes(p);
+}
+
+extern "C" int ema_b200_bwd_weighted(const ema_b200_problem *p, const void *x, const float *decay,
+                                     const float *in_weight, const float *out_weight, const void *dy,
+                                     const float *tile_states, void *dx, float *ddecay, float *din_weight,
+                                     float *dout_weight, const float *dfinal_state, float *dinit_state,
+                                     void *workspace, size_t workspace_bytes, void *stream) {
+    int rc = check_problem(p);
+    if (rc) return rc;
+    if (p->decay_mode != EMA_DECAY_PER_STEP) return EMA_ERR_UNSUPPORTED;
+    const bool empty = p->b * p->h == 0 || p->L == 0 || p->d == 0;
+    if (!empty && (!x || !decay || !dy || !dx || !ddecay || !tile_states)) return EMA_ERR_BADARG;
+    if ((in_weight && !din_weight) || (out_weight && !dout_weight)) return EMA_ERR_BADARG;
+    const size_t es = p->dtype == EMA_F32 ? 4 : 2;
+    if (!aligned(x, es) || !aligned(dy, es) || !aligned(dx, es) || !aligned(decay, 4) || !aligned(ddecay, 4) ||
+        !aligned(in_weight, 4) || !aligned(out_weight, 4) || !aligned(din_weight, 4) || !aligned(dout_weight, 4))
+        return EMA_ERR_ALIGN;
+    if (!workspace || workspace_bytes < ema_b200_bwd_weighted_workspace_bytes(p)) return EMA_ERR_WORKSPACE;
+    if (!aligned(workspace, 16)) return EMA_ERR_ALIGN;
+    auto st = static_cast<cudaStream_t>(stream);
+    const int64_t rows = p->b * p->h;
+    if (rows == 0 || p->L == 0) return EMA_OK;
+    const int vec = p->d > 0 ? pick_vec(p, x, dx, dy) : 1;
+    FusedParams fp;
+    fill_params(fp, p, vec);
+    fp.x = x; fp.decay = decay; fp.dy = dy; fp.out = dx;
+    fp.in_weight = in_weight; fp.out_weight = out_weight;
+    fp.tile_states = const_cast<float *>(tile_states);
+    fp.dfinal_state = dfinal_state; fp.dinit_state = dinit_state;
+    fp.da_partial = static_cast<float *>(workspace);
+    fp.weighted_partial_stride = static_cast<int64_t>(bwd_partial_bytes(p) / sizeof(float));
+    if (rows * fp.n_dtiles >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;
+    if (p->d == 0) {
+        fp.n_dtiles = 0;   // no channels: every gradient of a per-step quantity is an empty sum
+    } else {
+        g_last_path = 0;
+        rc = launch_fused_bwd_fma_weighted(fp, p->dtype, vec, st);
+        if (rc) return rc;
+    }
+    // three fixed-order reductions over the channel tiles: decay, input weight, output weight
+    rc = launch_da_reduce(fp, ddecay, kFmaTile, st);
+    if (rc) return rc;
+    FusedParams fq = fp;
+    if (din_weight) {
+        fq.da_partial = fp.da_partial + fp.weighted_partial_stride;
+        rc = launch_da_reduce(fq, din_weight, kFmaTile, st);
+        if (rc) return rc;
+    }
+    if (dout_weight) {
+        fq.da_partial = fp.da_partial + 2 * fp.weighted_partial_stride;
+        rc = launch_da_reduce(fq, dout_weight, kFmaTile, st);
+    }
+    return rc;
 }

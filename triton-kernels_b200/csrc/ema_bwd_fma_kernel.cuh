@@ -86,12 +86,22 @@ __device__ __forceinline__ float reduce8_over16(const float (&acc)[8], int lc) {
 //   after_barrier(kk)  after the tile's block-wide barrier: every thread has consumed the tile's staging, if any
 //   end(k, more)       bottom of the iteration
 //   finish()           after the loop
-template <typename T, int VEC, typename FEED>
+//
+// WEIGHTED (per-step decay only): the forward was  s_t = a_t s_{t-1} + w_t x_t,  y_t = c_t s_t  with per-step weights
+// w = in_weight (or the convention's 1 - a | 1 when null) and c = out_weight (or 1).  Then
+//     lambda_t = c_t dy_t + a_{t+1} lambda_{t+1},   dx_t = w_t lambda_t,
+//     d decay_t = sum_d lambda_t s_{t-1}  (times a_t for a log decay; minus sum_d lambda_t x_t when w is the convention's 1 - a),
+//     d in_weight_t = sum_d lambda_t x_t,   d out_weight_t = sum_d dy_t s_t,
+// all in the one pass: three partial sums per step instead of one (partial regions p.weighted_partial_stride apart).
+template <typename T, int VEC, typename FEED, bool WEIGHTED = false>
 __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &feed) {
     constexpr int CT = kFmaCT, SB = kFmaSB, NS = kFmaNS, QT = kFmaTile, DT = CT * VEC;
     static_assert(SB == 8 && CT == 16, "reduce8_over16 assumes 8 steps x 16 lanes");
     using R = raw_t<T, VEC>;
+    constexpr int WQ = WEIGHTED ? QT : 1;   // the weight tables exist only in the weighted kernel
     __shared__ float a_sm[2][QT + 1];
+    __shared__ float w_sm[2][WQ];   // input weights of the tile
+    __shared__ float c_sm[2][WQ];   // output weights of the tile
     __shared__ float Sf_sm[2][NS][DT];
     __shared__ float Rr_sm[2][NS][DT];
     __shared__ float Pf_sm[2][NS];
@@ -122,6 +132,18 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
         const float v = arow[static_cast<int64_t>(t) * p.a_sl];
         return conv ? expf(v) : v;
     };
+    // per-step weights share the decay's strides; a missing output weight is 1, a missing input weight the convention's
+    const int64_t w_off = bi * p.a_sb + hi * p.a_sh;
+    const bool explicit_w = WEIGHTED && p.in_weight != nullptr;
+    auto load_in_w = [&](int t) -> float {
+        if (t >= L) return 0.f;
+        if (p.in_weight) return p.in_weight[w_off + static_cast<int64_t>(t) * p.a_sl];
+        return conv ? 1.f : 1.f - arow[static_cast<int64_t>(t) * p.a_sl];
+    };
+    auto load_out_w = [&](int t) -> float {
+        if (!p.out_weight) return 1.f;
+        return t < L ? p.out_weight[w_off + static_cast<int64_t>(t) * p.a_sl] : 0.f;
+    };
     auto load_state = [&](int k, float (&hs)[VEC]) {
         const float *ts = p.tile_states + (row * n_tiles + k) * p.d + c0;
 #pragma unroll
@@ -140,6 +162,9 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
     {
         const int k = n_tiles - 1;
         if (tid <= QT) a_sm[0][tid] = load_a(k * QT + tid);
+        if constexpr (WEIGHTED) {
+            if (tid < QT) { w_sm[0][tid] = load_in_w(k * QT + tid); c_sm[0][tid] = load_out_w(k * QT + tid); }
+        }
     }
     feed.init(p, xrow, grow, c_ok, sub, L, n_tiles);
     R (&xc)[SB] = feed.xc;
@@ -154,16 +179,25 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
         const int par = kk & 1;
         const int t0 = k * QT + sub * SB;
         const bool more = k > 0;
-        float a_pref = 1.f;
+        float a_pref = 1.f, w_pref = 0.f, c_pref = 0.f;
         feed.begin(kk, k, more);
         if (more) {
             if (tid < QT) a_pref = load_a((k - 1) * QT + tid);
+            if constexpr (WEIGHTED) {
+                if (tid < QT) { w_pref = load_in_w((k - 1) * QT + tid); c_pref = load_out_w((k - 1) * QT + tid); }
+            }
             load_state(k - 1, hs_next);
         }
 
         float a_r[SB + 1];
 #pragma unroll
         for (int s = 0; s <= SB; ++s) a_r[s] = a_sm[par][sub * SB + s];
+        // the tile's weights go to registers before the barrier: the table of the other parity is rewritten after it
+        float w_r[WEIGHTED ? SB : 1], c_r[WEIGHTED ? SB : 1];
+        if constexpr (WEIGHTED) {
+#pragma unroll
+            for (int s = 0; s < SB; ++s) { w_r[s] = w_sm[par][sub * SB + s]; c_r[s] = c_sm[par][sub * SB + s]; }
+        }
         // the gradient entering the state after step L-1 rides on dy_{L-1}
         const int s_last = (L - 1) - t0;
 
@@ -176,7 +210,7 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
         for (int s = 0; s < SB; ++s) {
             float xf[VEC];
             unpack<T, VEC>(xc[s], xf);
-            const float pw = conv ? 1.f : 1.f - a_r[s];
+            const float pw = WEIGHTED ? w_r[s] : (conv ? 1.f : 1.f - a_r[s]);
 #pragma unroll
             for (int v = 0; v < VEC; ++v) st[v] = fmaf(a_r[s], st[v], pw * xf[v]);
             Pf *= a_r[s];
@@ -185,6 +219,10 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
         for (int s = SB - 1; s >= 0; --s) {
             float gf[VEC];
             unpack<T, VEC>(gc[s], gf);
+            if constexpr (WEIGHTED) {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) gf[v] *= c_r[s];
+            }
             if (s == s_last) {
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) gf[v] += dfin[v];
@@ -202,6 +240,9 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
         if (more) {
             if (tid < QT) a_sm[par ^ 1][tid] = a_pref;
             if (tid == QT) a_sm[par ^ 1][QT] = a_sm[par][0];  // a of the first step of this tile
+            if constexpr (WEIGHTED) {
+                if (tid < QT) { w_sm[par ^ 1][tid] = w_pref; c_sm[par ^ 1][tid] = c_pref; }
+            }
         }
         __syncthreads();
         feed.after_barrier(kk);
@@ -227,7 +268,7 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
         for (int s = 0; s < SB; ++s) {
             float xf[VEC];
             unpack<T, VEC>(xc[s], xf);
-            const float pw = conv ? 1.f : 1.f - a_r[s];
+            const float pw = WEIGHTED ? w_r[s] : (conv ? 1.f : 1.f - a_r[s]);
 #pragma unroll
             for (int v = 0; v < VEC; ++v) {
                 yprev[s][v] = h[v];
@@ -235,26 +276,40 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
             }
         }
         float acc[SB];
+        float acc_w[WEIGHTED ? SB : 1], acc_c[WEIGHTED ? SB : 1];
 #pragma unroll
         for (int s = SB - 1; s >= 0; --s) {
             float gf[VEC], xf[VEC], dxf[VEC];
             unpack<T, VEC>(gc[s], gf);
             unpack<T, VEC>(xc[s], xf);
+            const float pw = WEIGHTED ? w_r[s] : (conv ? 1.f : 1.f - a_r[s]);
+            float c_acc = 0.f, w_acc = 0.f;
+            if constexpr (WEIGHTED) {
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) {
+                    c_acc = fmaf(gf[v], fmaf(a_r[s], yprev[s][v], pw * xf[v]), c_acc);   // dy_t . s_t
+                    gf[v] *= c_r[s];
+                }
+            }
             if (s == s_last) {
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) gf[v] += dfin[v];
             }
-            const float pw = conv ? 1.f : 1.f - a_r[s];
             float a_acc = 0.f;
 #pragma unroll
             for (int v = 0; v < VEC; ++v) {
                 g[v] = fmaf(a_r[s + 1], g[v], gf[v]);  // lambda_t
                 dxf[v] = pw * g[v];
-                a_acc = conv ? fmaf(g[v], yprev[s][v], a_acc)
-                             : fmaf(g[v], yprev[s][v] - xf[v], a_acc);
+                a_acc = (conv || explicit_w) ? fmaf(g[v], yprev[s][v], a_acc)
+                                             : fmaf(g[v], yprev[s][v] - xf[v], a_acc);
+                if constexpr (WEIGHTED) w_acc = fmaf(g[v], xf[v], w_acc);
             }
             const int t = t0 + s;
             acc[s] = (t < L) ? (conv ? a_r[s] * a_acc : a_acc) : 0.f;
+            if constexpr (WEIGHTED) {
+                acc_w[s] = (t < L) ? w_acc : 0.f;
+                acc_c[s] = (t < L) ? c_acc : 0.f;
+            }
             if (c_ok && t < L)
                 st_stream<T, VEC>(orow + static_cast<int64_t>(t) * p.o_sl, pack<T, VEC>(dxf));
         }
@@ -270,8 +325,16 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
         // decay gradient: partial over this CTA's channels
         if (per_step) {
             const float tot = reduce8_over16(acc, lc);
-            if ((lc & 1) == 0)
-                p.da_partial[blk * (static_cast<int64_t>(n_tiles) * QT) + t0 + (lc >> 1)] = tot;
+            const int64_t slot = blk * (static_cast<int64_t>(n_tiles) * QT) + t0 + (lc >> 1);
+            if ((lc & 1) == 0) p.da_partial[slot] = tot;
+            if constexpr (WEIGHTED) {
+                const float tot_w = reduce8_over16(acc_w, lc);
+                const float tot_c = reduce8_over16(acc_c, lc);
+                if ((lc & 1) == 0) {
+                    p.da_partial[p.weighted_partial_stride + slot] = tot_w;
+                    p.da_partial[2 * p.weighted_partial_stride + slot] = tot_c;
+                }
+            }
         } else {
             float tot = 0.f;
 #pragma unroll

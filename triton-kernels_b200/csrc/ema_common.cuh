@@ -27,6 +27,7 @@ struct FusedParams {
     const float *dfinal_state;
     float *dinit_state;
     float *da_partial;
+    int64_t weighted_partial_stride;   // weighted backward: floats between the partial sums of decay, in_weight, out_weight
     int64_t b, L, h, d;
     int64_t x_sb, x_sl, x_sh;
     int64_t o_sb, o_sl, o_sh;
@@ -164,6 +165,7 @@ __host__ __device__ inline int64_t kHeadPartialOffset(int64_t rows) { return ((r
 
 int launch_fused_fwd_fma(const FusedParams &p, int dtype, int vec, cudaStream_t stream);
 int launch_fused_bwd_fma(const FusedParams &p, int dtype, int vec, cudaStream_t stream);
+int launch_fused_bwd_fma_weighted(const FusedParams &p, int dtype, int vec, cudaStream_t stream);
 int launch_da_reduce(const FusedParams &p, float *ddecay, int tile_steps, cudaStream_t stream);
 
 // tensor-core path (bf16): eligibility of one [b,L,h,d] tensor for TMA, launches, device status word

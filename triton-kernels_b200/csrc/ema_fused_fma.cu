@@ -35,6 +35,12 @@ __global__ void __launch_bounds__(kFmaThreads) ema_bwd_fma_kernel(const FusedPar
     ema_bwd_fma_body<T, VEC>(p, feed);
 }
 
+template <typename T, int VEC>
+__global__ void __launch_bounds__(kFmaThreads) ema_bwd_fma_weighted_kernel(const FusedParams p) {
+    RegisterFeedBwd<T, VEC, false> feed;
+    ema_bwd_fma_body<T, VEC, RegisterFeedBwd<T, VEC, false>, true>(p, feed);
+}
+
 // ------------------------------------------------------------------------------------------------
 // decay-gradient reductions (fixed order, no atomics)
 // ------------------------------------------------------------------------------------------------
@@ -108,11 +114,24 @@ int launch_fused_bwd_fma(const FusedParams &p, int dtype, int vec, cudaStream_t 
                     : launch_bwd<__nv_bfloat16, 1, true>(p, stream);
 }
 
+int launch_fused_bwd_fma_weighted(const FusedParams &p, int dtype, int vec, cudaStream_t stream) {
+    const unsigned blocks = static_cast<unsigned>(p.b * p.h * p.n_dtiles);
+    if (dtype == EMA_F32) {
+        if (vec == 4) ema_bwd_fma_weighted_kernel<float, 4><<<blocks, kFmaThreads, 0, stream>>>(p);
+        else ema_bwd_fma_weighted_kernel<float, 1><<<blocks, kFmaThreads, 0, stream>>>(p);
+    } else {
+        if (vec == 4) ema_bwd_fma_weighted_kernel<__nv_bfloat16, 4><<<blocks, kFmaThreads, 0, stream>>>(p);
+        else ema_bwd_fma_weighted_kernel<__nv_bfloat16, 1><<<blocks, kFmaThreads, 0, stream>>>(p);
+    }
+    return check_launch();
+}
+
 int launch_da_reduce(const FusedParams &p, float *ddecay, int tile_steps, cudaStream_t stream) {
     const int64_t rows = p.b * p.h;
     if (p.decay_mode == EMA_DECAY_PER_STEP) {
         const int64_t n = rows * p.L;
         const int64_t L_pad = static_cast<int64_t>(p.n_tiles) * tile_steps;
+        if ((n + 255) / 256 >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;   // beyond one grid dimension
         da_reduce_steps_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(
             p.da_partial, ddecay, rows, p.h, p.L, L_pad, p.n_dtiles, p.a_sb, p.a_sl, p.a_sh);
     } else {

@@ -289,12 +289,283 @@ __global__ void bwd_dacs_kernel(const T *__restrict__ X, const float *__restrict
     for (int q = threadIdx.x; q < Q; q += blockDim.x) out[bc * Q + q] = acc[q];
 }
 
+// ------------------------------------------------------------------------------------------------
+// 128-bit variants.  Taken when T is a multiple of the vector width (4 fp32 or 8 bf16 channels) and the tensors are
+// 16-byte aligned; the scalar kernels above remain for every other shape.  Same sums in a different order.
+// ------------------------------------------------------------------------------------------------
+template <typename T> struct Vec16 { static constexpr int n = 16 / static_cast<int>(sizeof(T)); };
+
+template <typename T>
+__device__ __forceinline__ void load16(const T *p, float (&f)[Vec16<T>::n]) {
+    const uint4 r = __ldg(reinterpret_cast<const uint4 *>(p));
+    unpack<T, Vec16<T>::n>(r, f);
+}
+template <typename T>
+__device__ __forceinline__ void store16(T *p, const float (&f)[Vec16<T>::n]) {
+    *reinterpret_cast<uint4 *>(p) = pack<T, Vec16<T>::n>(f);
+}
+
+// Weighted column sums of one chunk: out[b,c,:] = sum_q w_q rows[b, cQ+q, :].
+//   KIND 0 (chunk state)  w_q = exp(min(cs_last - cs_q, 0))      KIND 1 (dstates)  w_q = exp(cs_q)
+// 256 threads: warp g takes steps g, g+8, ..., lane l takes VEC channels; four 16-byte loads in flight per thread,
+// a fixed-order sum over the eight warps at the end.  Dynamic shared memory: w[Q] + red[8][32 VEC].
+template <typename T, int KIND>
+__global__ void __launch_bounds__(256) weighted_colsum_kernel(const T *__restrict__ rows, const float *__restrict__ cs,
+                                                              float *__restrict__ out, int64_t L, int64_t Tn, int Q,
+                                                              int64_t C) {
+    constexpr int VEC = Vec16<T>::n;
+    constexpr int CH = 32 * VEC;
+    extern __shared__ float sm[];
+    float *w = sm;
+    float *red = sm + Q;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t bc = blockIdx.x;
+    const int64_t b = bc / C, c = bc % C;
+    const int lim = chunk_limit(L, Q, c);
+    const float *csr = cs + bc * Q;
+    const float last = csr[lim - 1];
+    for (int q = tid; q < Q; q += 256)
+        w[q] = q < lim ? (KIND == 0 ? expf(fminf(last - csr[q], 0.f)) : expf(csr[q])) : 0.f;
+    __syncthreads();
+    const int64_t ch = static_cast<int64_t>(blockIdx.y) * CH + lane * VEC;
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+    if (ch < Tn) {
+        const T *base = rows + (b * L + c * Q) * Tn + ch;
+        for (int q0 = warp; q0 < lim; q0 += 32) {
+            float f[4][VEC];
+            float wq[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int q = q0 + 8 * i;
+                const bool ok = q < lim;
+                load16<T>(base + static_cast<int64_t>(ok ? q : lim - 1) * Tn, f[i]);   // rows past the end count with weight 0
+                wq[i] = ok ? w[q] : 0.f;
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) acc[e] = fmaf(wq[i], f[i][e], acc[e]);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) red[warp * CH + lane * VEC + e] = acc[e];
+    __syncthreads();
+    const int64_t co = static_cast<int64_t>(blockIdx.y) * CH + tid;
+    if (tid < CH && co < Tn) {
+        float s = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) s += red[g * CH + tid];
+        out[bc * Tn + co] = s;
+    }
+    if (CH > 256) {   // bf16: 256 channels per block, second half of the channels
+        const int t2 = tid + 256;
+        const int64_t co2 = static_cast<int64_t>(blockIdx.y) * CH + t2;
+        if (t2 < CH && co2 < Tn) {
+            float s = 0.f;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) s += red[g * CH + t2];
+            out[bc * Tn + co2] = s;
+        }
+    }
+}
+
+// The chunk scan and its mirror, a thread per VEC channels walking the chunk with the O(Q) recurrence; the per-step
+// factors are worked out once per block into shared memory (dynamic, Q floats), four steps' loads are in flight.
+//   REVERSE = false: y_m = f_m y_{m-1} + x_m from the chunk-start state,  f_m = exp(min(cs_m - cs_{m-1}, 0)), cs_{-1} = 0
+//   REVERSE = true : g_m = f_m g_{m+1} + dy_m from dS_c,                  f_m = exp(min(cs_{m+1} - cs_m, 0)), cs past the end = cs[Q-1]
+template <typename T, bool REVERSE>
+__global__ void __launch_bounds__(128) chunk_recurrence_vec_kernel(const T *__restrict__ in, const float *__restrict__ cs,
+                                                                   const float *__restrict__ start, T *__restrict__ out,
+                                                                   int64_t L, int64_t Tn, int Q, int64_t C) {
+    constexpr int VEC = Vec16<T>::n;
+    extern __shared__ float fac[];
+    const int64_t bc = blockIdx.x;
+    const int64_t b = bc / C, c = bc % C;
+    const int lim = chunk_limit(L, Q, c);
+    const float *csr = cs + bc * Q;
+    for (int m = threadIdx.x; m < lim; m += blockDim.x) {
+        if (!REVERSE) fac[m] = expf(fminf(csr[m] - (m > 0 ? csr[m - 1] : 0.f), 0.f));
+        else fac[m] = expf(fminf((m + 1 < lim ? csr[m + 1] : csr[Q - 1]) - csr[m], 0.f));
+    }
+    __syncthreads();
+    const int64_t ch = (static_cast<int64_t>(blockIdx.y) * blockDim.x + threadIdx.x) * VEC;
+    if (ch >= Tn) return;
+    float s[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; e += 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(start + bc * Tn + ch + e);
+        s[e] = v.x; s[e + 1] = v.y; s[e + 2] = v.z; s[e + 3] = v.w;
+    }
+    const int64_t base = (b * L + c * Q) * Tn + ch;
+    for (int j0 = 0; j0 < lim; j0 += 4) {
+        float f[4][VEC];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int j = j0 + i < lim ? j0 + i : lim - 1;
+            const int m = REVERSE ? lim - 1 - j : j;
+            load16<T>(in + base + static_cast<int64_t>(m) * Tn, f[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (j0 + i < lim) {
+                const int m = REVERSE ? lim - 1 - (j0 + i) : j0 + i;
+                const float fm = fac[m];
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) s[e] = fmaf(fm, s[e], f[i][e]);
+                store16<T>(out + base + static_cast<int64_t>(m) * Tn, s);
+            }
+        }
+    }
+}
+
+// Forward carry over the chunks, four channels per thread (128-bit loads and stores, coalesced across the warp) with
+// the next kDepth chunk states already in flight: the chain itself is one FMA per chunk.
+constexpr int kPassDepth = 8;
+__global__ void __launch_bounds__(32) state_passing_fwd_vec_kernel(const float4 *__restrict__ S, const float *__restrict__ cl,
+                                                                   int64_t cl_sb, int64_t cl_sc, float4 *__restrict__ out,
+                                                                   float4 *__restrict__ fin, int64_t C, int64_t T4) {
+    const int64_t b = blockIdx.x;
+    const int64_t t4 = static_cast<int64_t>(blockIdx.y) * blockDim.x + threadIdx.x;
+    if (t4 >= T4) return;
+    const float4 *src = S + b * C * T4 + t4;
+    float4 *dst = out + b * C * T4 + t4;
+    const float *clb = cl + b * cl_sb;
+    float4 buf[kPassDepth];
+    float sc[kPassDepth];
+#pragma unroll
+    for (int i = 0; i < kPassDepth; ++i) {
+        if (i < C) { buf[i] = __ldg(src + i * T4); sc[i] = expf(clb[i * cl_sc]); }
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int64_t c0 = 0; c0 < C; c0 += kPassDepth) {
+#pragma unroll
+        for (int i = 0; i < kPassDepth; ++i) {
+            const int64_t c = c0 + i;
+            if (c < C) {
+                dst[c * T4] = acc;
+                acc.x = fmaf(sc[i], acc.x, buf[i].x); acc.y = fmaf(sc[i], acc.y, buf[i].y);
+                acc.z = fmaf(sc[i], acc.z, buf[i].z); acc.w = fmaf(sc[i], acc.w, buf[i].w);
+                if (c + kPassDepth < C) { buf[i] = __ldg(src + (c + kPassDepth) * T4); sc[i] = expf(clb[(c + kPassDepth) * cl_sc]); }
+            }
+        }
+    }
+    fin[b * T4 + t4] = acc;
+}
+
+// Reverse carry of the adjoint, one warp per 128 channels of a batch row (so a row is spread over T / 128 thread
+// blocks).  Every warp writes the dot product <h_c, dS_c> over ITS channels to partial[b, c, warp]; a second kernel
+// sums the partials in a fixed order and applies exp(cs_last).
+constexpr int kPassBwdDepth = 4;
+__global__ void __launch_bounds__(32) state_passing_bwd_vec_kernel(const float4 *__restrict__ h, const float *__restrict__ cl,
+                                                                   int64_t cl_sb, int64_t cl_sc, const float4 *__restrict__ dh,
+                                                                   float4 *__restrict__ dS, float *__restrict__ partial,
+                                                                   int64_t C, int64_t T4, int n_warps) {
+    const int64_t b = blockIdx.x;
+    const int wi = blockIdx.y;
+    const int lane = threadIdx.x;
+    const int64_t t4 = static_cast<int64_t>(wi) * 32 + lane;
+    const bool ok = t4 < T4;
+    const int64_t off = b * C * T4 + (ok ? t4 : 0);
+    const float *clb = cl + b * cl_sb;
+    float4 hb[kPassBwdDepth], db[kPassBwdDepth];
+    float sc[kPassBwdDepth];
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int i = 0; i < kPassBwdDepth; ++i) {
+        const int64_t c = C - 1 - i;
+        if (c >= 0) {
+            hb[i] = ok ? __ldg(h + off + c * T4) : zero;
+            db[i] = ok ? __ldg(dh + off + c * T4) : zero;
+            sc[i] = expf(clb[c * cl_sc]);
+        }
+    }
+    float4 g = zero;
+    for (int64_t c0 = C - 1; c0 >= 0; c0 -= kPassBwdDepth) {
+#pragma unroll
+        for (int i = 0; i < kPassBwdDepth; ++i) {
+            const int64_t c = c0 - i;
+            if (c >= 0) {
+                if (ok) dS[off + c * T4] = g;
+                float part = hb[i].x * g.x + hb[i].y * g.y + hb[i].z * g.z + hb[i].w * g.w;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(kFull, part, o);
+                if (lane == 0) partial[(b * C + c) * n_warps + wi] = part;
+                if (c > 0) {
+                    g.x = fmaf(sc[i], g.x, db[i].x); g.y = fmaf(sc[i], g.y, db[i].y);
+                    g.z = fmaf(sc[i], g.z, db[i].z); g.w = fmaf(sc[i], g.w, db[i].w);
+                }
+                const int64_t cn = c - kPassBwdDepth;
+                if (cn >= 0) {
+                    hb[i] = ok ? __ldg(h + off + cn * T4) : zero;
+                    db[i] = ok ? __ldg(dh + off + cn * T4) : zero;
+                    sc[i] = expf(clb[cn * cl_sc]);
+                }
+            }
+        }
+    }
+}
+// ddA_last[b, c] = exp(cs_last[b, c]) * sum_w partial[b, c, w] for c > 0, and 0 for the first chunk
+__global__ void state_passing_bwd_sum_kernel(const float *__restrict__ partial, const float *__restrict__ cl, int64_t cl_sb,
+                                             int64_t cl_sc, float *__restrict__ ddA, int64_t B, int64_t C, int n_warps) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= B * C) return;
+    const int64_t b = i / C, c = i % C;
+    float s = 0.f;
+    for (int w = 0; w < n_warps; ++w) s += partial[i * n_warps + w];
+    ddA[i] = c > 0 ? s * expf(cl[b * cl_sb + c * cl_sc]) : 0.f;
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 inline unsigned cdiv(int64_t a, int64_t b) { return static_cast<unsigned>((a + b - 1) / b); }
 
 }  // namespace
 }  // namespace ema
 
 using namespace ema;
+
+// ---- launchers of the 128-bit variants ------------------------------------------------------------------------
+static bool colsum_vec_ok(const void *rows, int dtype, int64_t T, int Q) {
+    const int vec = dtype == EMA_F32 ? 4 : 8;
+    return (dtype == EMA_F32 || dtype == EMA_BF16) && T % vec == 0 && aligned16(rows) && Q <= 8192 &&
+           (T + 32 * vec - 1) / (32 * vec) <= 65535;
+}
+template <int KIND>
+static int launch_colsum_vec(const void *rows, const float *cs, float *out, int dtype, int64_t B, int64_t L, int64_t T,
+                             int Q, int64_t C, cudaStream_t st) {
+    const int vec = dtype == EMA_F32 ? 4 : 8;
+    const size_t smem = (static_cast<size_t>(Q) + 8 * 32 * vec) * sizeof(float);
+    dim3 grid(static_cast<unsigned>(B * C), static_cast<unsigned>((T + 32 * vec - 1) / (32 * vec)));
+    if (dtype == EMA_F32)
+        weighted_colsum_kernel<float, KIND><<<grid, 256, smem, st>>>(static_cast<const float *>(rows), cs, out, L, T, Q, C);
+    else
+        weighted_colsum_kernel<__nv_bfloat16, KIND><<<grid, 256, smem, st>>>(static_cast<const __nv_bfloat16 *>(rows), cs,
+                                                                              out, L, T, Q, C);
+    return check_launch();
+}
+static bool recurrence_vec_ok(const void *in, const void *out, const float *start, int dtype, int64_t T, int Q) {
+    const int vec = dtype == EMA_F32 ? 4 : 8;
+    return (dtype == EMA_F32 || dtype == EMA_BF16) && T % vec == 0 && aligned16(in) && aligned16(out) && aligned16(start) &&
+           Q <= 8192 && (T / vec + 127) / 128 <= 65535;
+}
+template <bool REVERSE>
+static int launch_recurrence_vec(const void *in, const float *cs, const float *start, void *out, int dtype, int64_t B,
+                                 int64_t L, int64_t T, int Q, int64_t C, cudaStream_t st) {
+    const int vec = dtype == EMA_F32 ? 4 : 8;
+    const int64_t groups = T / vec;
+    const int threads = groups >= 128 ? 128 : static_cast<int>((groups + 31) / 32 * 32);
+    dim3 grid(static_cast<unsigned>(B * C), static_cast<unsigned>((groups + threads - 1) / threads));
+    const size_t smem = static_cast<size_t>(Q) * sizeof(float);
+    if (dtype == EMA_F32)
+        chunk_recurrence_vec_kernel<float, REVERSE><<<grid, threads, smem, st>>>(
+            static_cast<const float *>(in), cs, start, static_cast<float *>(out), L, T, Q, C);
+    else
+        chunk_recurrence_vec_kernel<__nv_bfloat16, REVERSE><<<grid, threads, smem, st>>>(
+            static_cast<const __nv_bfloat16 *>(in), cs, start, static_cast<__nv_bfloat16 *>(out), L, T, Q, C);
+    return check_launch();
+}
 
 #define EMA_REQUIRE(cond, code) \
     do {                        \
@@ -329,8 +600,9 @@ extern "C" int ema_b200_chunk_state(const void *X, const float *cs, float *S, in
     int rc = stage_dims_ok(B, L, T, Q);
     if (rc) return rc;
     const int64_t C = (L + Q - 1) / Q;
-    dim3 grid(static_cast<unsigned>(B * C), cdiv(T, 128));
     auto st = static_cast<cudaStream_t>(stream);
+    if (colsum_vec_ok(X, dtype, T, Q)) return launch_colsum_vec<0>(X, cs, S, dtype, B, L, T, Q, C, st);
+    dim3 grid(static_cast<unsigned>(B * C), cdiv(T, 128));
     EMA_STAGE_DISPATCH(dtype,
         (chunk_state_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float *>(X), cs, S, L, T, Q, C)),
         (chunk_state_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16 *>(X), cs, S, L, T, Q, C)))
@@ -342,6 +614,13 @@ extern "C" int ema_b200_state_passing_fwd(const float *S, const float *cs_last, 
                                           int64_t C, int64_t T, void *stream) {
     EMA_REQUIRE(S && cs_last && out && final_states, EMA_ERR_BADARG);
     EMA_REQUIRE(B > 0 && C > 0 && T > 0, EMA_ERR_BADARG);
+    if (T % 4 == 0 && aligned16(S) && aligned16(out) && aligned16(final_states) && T / 4 <= 65535ll * 32) {
+        dim3 grid(static_cast<unsigned>(B), cdiv(T / 4, 32));
+        state_passing_fwd_vec_kernel<<<grid, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+            reinterpret_cast<const float4 *>(S), cs_last, cl_sb, cl_sc, reinterpret_cast<float4 *>(out),
+            reinterpret_cast<float4 *>(final_states), C, T / 4);
+        return check_launch();
+    }
     dim3 grid(static_cast<unsigned>(B), cdiv(T, 128));
     state_passing_fwd_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
         S, cs_last, cl_sb, cl_sc, out, final_states, C, T);
@@ -354,8 +633,9 @@ extern "C" int ema_b200_chunk_scan(const void *X, const float *cs, const float *
     int rc = stage_dims_ok(B, L, T, Q);
     if (rc) return rc;
     const int64_t C = (L + Q - 1) / Q;
-    dim3 grid(static_cast<unsigned>(B * C), cdiv(T, 128));
     auto st = static_cast<cudaStream_t>(stream);
+    if (recurrence_vec_ok(X, out, h, dtype, T, Q)) return launch_recurrence_vec<false>(X, cs, h, out, dtype, B, L, T, Q, C, st);
+    dim3 grid(static_cast<unsigned>(B * C), cdiv(T, 128));
     EMA_STAGE_DISPATCH(dtype,
         (chunk_scan_kernel<float><<<grid, 128, 0, st>>>(static_cast<const float *>(X), cs, h, static_cast<float *>(out), L, T, Q, C)),
         (chunk_scan_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16 *>(X), cs, h, static_cast<__nv_bfloat16 *>(out), L, T, Q, C)))
@@ -368,19 +648,40 @@ extern "C" int ema_b200_bwd_dstates(const float *cs, const void *dout, float *dh
     int rc = stage_dims_ok(B, L, T, Q);
     if (rc) return rc;
     const int64_t C = (L + Q - 1) / Q;
-    dim3 grid(static_cast<unsigned>(B * C), cdiv(T, 128));
     auto st = static_cast<cudaStream_t>(stream);
+    if (colsum_vec_ok(dout, dtype, T, Q)) return launch_colsum_vec<1>(dout, cs, dh, dtype, B, L, T, Q, C, st);
+    dim3 grid(static_cast<unsigned>(B * C), cdiv(T, 128));
     EMA_STAGE_DISPATCH(dtype,
         (bwd_dstates_kernel<float><<<grid, 128, 0, st>>>(cs, static_cast<const float *>(dout), dh, L, T, Q, C)),
         (bwd_dstates_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(cs, static_cast<const __nv_bfloat16 *>(dout), dh, L, T, Q, C)))
     return check_launch();
 }
 
+extern "C" size_t ema_b200_state_passing_bwd_workspace_bytes(int64_t B, int64_t C, int64_t T) {
+    if (B <= 0 || C <= 0 || T <= 0 || T % 4 != 0) return 0;
+    return static_cast<size_t>(B) * C * ((T / 4 + 31) / 32) * sizeof(float);
+}
+
 extern "C" int ema_b200_state_passing_bwd(const float *h, const float *cs_last, int64_t cl_sb,
                                           int64_t cl_sc, const float *dh, float *dS, float *ddA_last,
-                                          int64_t B, int64_t C, int64_t T, void *stream) {
+                                          int64_t B, int64_t C, int64_t T, void *workspace, size_t workspace_bytes,
+                                          void *stream) {
     EMA_REQUIRE(h && cs_last && dh && dS && ddA_last, EMA_ERR_BADARG);
     EMA_REQUIRE(B > 0 && C > 0 && T > 0, EMA_ERR_BADARG);
+    const size_t need = ema_b200_state_passing_bwd_workspace_bytes(B, C, T);
+    if (workspace && need > 0 && workspace_bytes >= need && aligned16(h) && aligned16(dh) && aligned16(dS) &&
+        (reinterpret_cast<uintptr_t>(workspace) & 3u) == 0 && (T / 4 + 31) / 32 <= 65535 && B * C < (1ll << 31) * 128) {
+        const int n_warps = static_cast<int>((T / 4 + 31) / 32);
+        auto st = static_cast<cudaStream_t>(stream);
+        dim3 grid(static_cast<unsigned>(B), static_cast<unsigned>(n_warps));
+        state_passing_bwd_vec_kernel<<<grid, 32, 0, st>>>(reinterpret_cast<const float4 *>(h), cs_last, cl_sb, cl_sc,
+                                                          reinterpret_cast<const float4 *>(dh),
+                                                          reinterpret_cast<float4 *>(dS), static_cast<float *>(workspace),
+                                                          C, T / 4, n_warps);
+        state_passing_bwd_sum_kernel<<<cdiv(B * C, 128), 128, 0, st>>>(static_cast<const float *>(workspace), cs_last,
+                                                                       cl_sb, cl_sc, ddA_last, B, C, n_warps);
+        return check_launch();
+    }
     EMA_REQUIRE(T <= 16 * 1024, EMA_ERR_UNSUPPORTED);
     int threads = static_cast<int>(((T + 15) / 16 + 31) / 32 * 32);
     if (threads < 32) threads = 32;
@@ -395,8 +696,9 @@ extern "C" int ema_b200_bwd_dx(const float *cs, const void *dout, const float *d
     int rc = stage_dims_ok(B, L, T, Q);
     if (rc) return rc;
     const int64_t C = (L + Q - 1) / Q;
-    dim3 grid(static_cast<unsigned>(B * C), cdiv(T, 128));
     auto st = static_cast<cudaStream_t>(stream);
+    if (recurrence_vec_ok(dout, dx, dS, dtype, T, Q)) return launch_recurrence_vec<true>(dout, cs, dS, dx, dtype, B, L, T, Q, C, st);
+    dim3 grid(static_cast<unsigned>(B * C), cdiv(T, 128));
     EMA_STAGE_DISPATCH(dtype,
         (bwd_dx_kernel<float><<<grid, 128, 0, st>>>(cs, static_cast<const float *>(dout), dS, static_cast<float *>(dx), L, T, Q, C)),
         (bwd_dx_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(cs, static_cast<const __nv_bfloat16 *>(dout), dS, static_cast<__nv_bfloat16 *>(dx), L, T, Q, C)))

@@ -65,6 +65,8 @@ def lib():
         "ema_b200_fwd_weighted": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp, sz, vp]),
         "ema_b200_bwd": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, cf, vp, sz, vp]),
         "ema_b200_fold_records": (ci, [vp, ci, ci, i64, i64, ci, vp, vp]),
+        "ema_b200_bwd_weighted_workspace_bytes": (sz, [pp]),
+        "ema_b200_bwd_weighted": (ci, [pp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
         "ema_b200_static_scratch_limit": (sz, []),
         "ema_b200_bwd_static_scratch": (ci, [pp, vp, vp, vp, vp, vp, vp, vp]),
         "ema_b200_chunk_cumsum": (ci, [vp, i64, i64, vp, i64, i64, ci, vp]),
@@ -72,7 +74,8 @@ def lib():
         "ema_b200_state_passing_fwd": (ci, [vp, vp, i64, i64, vp, vp, i64, i64, i64, vp]),
         "ema_b200_chunk_scan": (ci, [vp, vp, vp, vp, ci, i64, i64, i64, ci, vp]),
         "ema_b200_bwd_dstates": (ci, [vp, vp, vp, ci, i64, i64, i64, ci, vp]),
-        "ema_b200_state_passing_bwd": (ci, [vp, vp, i64, i64, vp, vp, vp, i64, i64, i64, vp]),
+        "ema_b200_state_passing_bwd_workspace_bytes": (sz, [i64, i64, i64]),
+        "ema_b200_state_passing_bwd": (ci, [vp, vp, i64, i64, vp, vp, vp, i64, i64, i64, vp, sz, vp]),
         "ema_b200_bwd_dx": (ci, [vp, vp, vp, vp, ci, i64, i64, i64, ci, vp]),
         "ema_b200_bwd_db": (ci, [vp, vp, vp, vp, ci, ci, i64, i64, i64, ci, vp]),
         "ema_b200_bwd_dc": (ci, [vp, vp, vp, vp, ci, i64, i64, i64, ci, vp]),

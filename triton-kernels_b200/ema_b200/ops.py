@@ -5,12 +5,53 @@ x[b, l, h, p] with one decay per (b, l, h) or per head): x[b, L, h, d], decay a[
 The reference's folded layout X[B, L, T] with A[B, L] is the same thing with h = 1.
 """
 import ctypes
+import json
+import os
 
 import torch
 
 from . import _lib
 from ._lib import (CONV_NORTH_STAR, CONV_PRESCALED_LOG, DECAY_PER_HEAD, DECAY_PER_STEP, Problem,
                    check, dtype_code, lib, ptr, require_cuda, stream_ptr)
+
+
+class _traced:
+    """Optional tracing of a library call, off by default.  EMA_B200_NVTX=1 wraps the call in an NVTX range (visible in
+    a profiler's timeline); EMA_B200_TRACE=<file> appends one JSON line per call - op, shape, dtype, decay mode, kernel
+    family and schedule, milliseconds between two CUDA events around the call, and the GB/s and tokens/s that follow
+    from the algorithmic bytes (x read + y written forward; x, dy read + dx written backward).  Tracing a call
+    synchronises the device, so it is a debugging aid, not for timed runs."""
+
+    def __init__(self, op, x, decay, passes):
+        self.op, self.x, self.decay, self.passes = op, x, decay, passes
+        self.nvtx = os.environ.get("EMA_B200_NVTX") == "1"
+        self.path = os.environ.get("EMA_B200_TRACE")
+
+    def __enter__(self):
+        if self.nvtx:
+            torch.cuda.nvtx.range_push(f"ema_b200.{self.op} {tuple(self.x.shape)}")
+        if self.path:
+            self.e0, self.e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            self.e0.record(torch.cuda.current_stream(self.x.device))
+        return self
+
+    def __exit__(self, *exc):
+        if self.path and exc[0] is None:
+            self.e1.record(torch.cuda.current_stream(self.x.device))
+            self.e1.synchronize()
+            ms = self.e0.elapsed_time(self.e1)
+            b, L, h, d = self.x.shape
+            nbytes = self.passes * self.x.numel() * self.x.element_size() + self.decay.numel() * 4
+            rec = {"op": self.op, "shape": [b, L, h, d], "dtype": str(self.x.dtype).replace("torch.", ""),
+                   "decay": "per_head" if self.decay.dim() == 1 else "per_step", "path": lib().ema_b200_last_path(),
+                   "schedule": lib().ema_b200_last_schedule(), "ms": ms,
+                   "algorithmic_GBps": nbytes / (ms * 1e-3) / 1e9 if ms > 0 else None,
+                   "tokens_per_s": b * L / (ms * 1e-3) if ms > 0 else None}
+            with open(self.path, "a") as f:
+                f.write(json.dumps(rec) + "\n")
+        if self.nvtx:
+            torch.cuda.nvtx.range_pop()
+        return False
 
 
 def _problem(x, decay, out, dy=None, convention=CONV_NORTH_STAR, chunk=0):
@@ -133,7 +174,7 @@ def ema_fwd(x, decay, *, chunk=0, prescaled_log=False, init_state=None, want_chu
         workspace = torch.empty(((ws_bytes + 3) // 4,), dtype=torch.float32, device=dev)
     res["fwd_workspace"] = workspace
     ws_size = ctypes.c_size_t(0 if workspace is None else workspace.numel() * 4)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _traced("ema_fwd", x, decay, 2):
         if weighted:
             rc = L_.ema_b200_fwd_weighted(ctypes.byref(p), ptr(x), ptr(decay), ptr(in_weight), ptr(out_weight), ptr(y),
                                           ptr(cs), ptr(ts), ptr(init_state), ptr(fin), ptr(lds),
@@ -182,7 +223,7 @@ def ema_bwd(x, decay, dy, tile_states, *, prescaled_log=False, dfinal_state=None
         if tuple(dfinal_state.shape) != (b, h, d) or dfinal_state.dtype != torch.float32:
             raise ValueError("dfinal_state must be fp32 [b, h, d]")
         dfinal_state = dfinal_state.contiguous()
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _traced("ema_bwd", x, decay, 3):
         rc = L_.ema_b200_bwd(ctypes.byref(p), ptr(x), ptr(decay), ptr(dy), ptr(tile_states), ptr(dx),
                              ptr(ddecay), ptr(dfinal_state), ptr(dinit), ctypes.c_float(stop_below),
                              ptr(workspace), ctypes.c_size_t(workspace.numel() * 4), stream_ptr(dev))
@@ -190,6 +231,60 @@ def ema_bwd(x, decay, dy, tile_states, *, prescaled_log=False, dfinal_state=None
     if check_status:
         _check_device_status(dev)
     res = {"dx": dx, "ddecay": ddecay, "workspace": workspace}
+    if dinit is not None:
+        res["dinit_state"] = dinit
+    return res
+
+
+def ema_bwd_weighted(x, decay, dy, tile_states, *, in_weight=None, out_weight=None, prescaled_log=False,
+                     dfinal_state=None, want_dinit=False):
+    """Backward of the weighted forward scan (ema_fwd with in_weight / out_weight), one pass over x and dy.
+
+    Returns a dict with 'dx', 'ddecay' and, for the weights that were given, 'din_weight' / 'dout_weight' (fp32
+    [b, L, h]); optionally 'dinit_state'.  Per-step decay only; `tile_states` are the ones the weighted forward saved.
+    """
+    x, decay = _check_inputs(x, decay)
+    if decay.dim() != 3:
+        raise ValueError("per-step weights need a per-step decay [b, L, h]")
+    if dy.shape != x.shape or dy.dtype != x.dtype:
+        raise ValueError("dy must match x in shape and dtype")
+    if dy.stride(-1) != 1 and dy.shape[-1] > 1:
+        dy = dy.contiguous()
+    decay = decay.contiguous()
+    dev = require_cuda(x, decay, dy, tile_states, dfinal_state, in_weight, out_weight)
+    b, L, h, d = x.shape
+
+    def _as_weight(w, name):
+        if w is None:
+            return None
+        if tuple(w.shape) != (b, L, h) or w.dtype != torch.float32:
+            raise ValueError(f"{name} must be fp32 [b, L, h]")
+        return w.contiguous()
+    in_weight, out_weight = _as_weight(in_weight, "in_weight"), _as_weight(out_weight, "out_weight")
+    conv = CONV_PRESCALED_LOG if prescaled_log else CONV_NORTH_STAR
+    dx = torch.empty((b, L, h, d), dtype=x.dtype, device=dev)
+    ddecay = torch.empty_like(decay)
+    dw = torch.empty_like(decay) if in_weight is not None else None
+    dc = torch.empty_like(decay) if out_weight is not None else None
+    p = _problem(x, decay, dx, dy=dy, convention=conv)
+    L_ = lib()
+    nbytes = L_.ema_b200_bwd_weighted_workspace_bytes(ctypes.byref(p))
+    workspace = torch.empty(((nbytes + 3) // 4,), dtype=torch.float32, device=dev)
+    dinit = torch.empty((b, h, d), dtype=torch.float32, device=dev) if want_dinit else None
+    if dfinal_state is not None:
+        if tuple(dfinal_state.shape) != (b, h, d) or dfinal_state.dtype != torch.float32:
+            raise ValueError("dfinal_state must be fp32 [b, h, d]")
+        dfinal_state = dfinal_state.contiguous()
+    with torch.cuda.device(dev), _traced("ema_bwd_weighted", x, decay, 3):
+        rc = L_.ema_b200_bwd_weighted(ctypes.byref(p), ptr(x), ptr(decay), ptr(in_weight), ptr(out_weight), ptr(dy),
+                                      ptr(tile_states), ptr(dx), ptr(ddecay), ptr(dw), ptr(dc), ptr(dfinal_state),
+                                      ptr(dinit), ptr(workspace), ctypes.c_size_t(workspace.numel() * 4), stream_ptr(dev))
+    check("ema_b200_bwd_weighted", rc)
+    res = {"dx": dx, "ddecay": ddecay}
+    if dw is not None:
+        res["din_weight"] = dw
+    if dc is not None:
+        res["dout_weight"] = dc
     if dinit is not None:
         res["dinit_state"] = dinit
     return res

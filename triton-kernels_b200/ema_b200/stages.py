@@ -4,6 +4,7 @@ X, dout: [B, L, T] contiguous (fp32 | bf16);  A: [B, L];  cs: [B, C, Q] fp32;  p
 [B, C, T] fp32.  Each function allocates its output like the reference wrapper it stands in for and
 makes one C-ABI call on the current stream of the input's device.
 """
+import ctypes
 import math
 
 import torch
@@ -98,10 +99,13 @@ def state_passing_bwd(states, cs_last, dout, dstates_dtype=None):
         cs_last = cs_last.float()
     dS = torch.empty(B, C, T, device=dev, dtype=torch.float32)
     ddA = torch.empty(B, C, device=dev, dtype=torch.float32)
+    # partial dot products per 128 channels (the reference's wrapper allocates the same kind of buffer)
+    ws_bytes = lib().ema_b200_state_passing_bwd_workspace_bytes(B, C, T)
+    ws = torch.empty((ws_bytes + 3) // 4, device=dev, dtype=torch.float32) if ws_bytes else None
     with torch.cuda.device(dev):
         rc = lib().ema_b200_state_passing_bwd(ptr(_f32c(states)), ptr(cs_last), cs_last.stride(0),
                                               cs_last.stride(1), ptr(_f32c(dout)), ptr(dS), ptr(ddA), B, C, T,
-                                              stream_ptr(dev))
+                                              ptr(ws), ctypes.c_size_t(ws_bytes), stream_ptr(dev))
     check("ema_b200_state_passing_bwd", rc)
     dt = dout.dtype if dstates_dtype is None else dstates_dtype
     return (dS if dt == torch.float32 else dS.to(dt)), ddA

@@ -3,8 +3,9 @@
 Same providers (minus the upstream Mamba package, which is not a dependency here), same shapes (fp32, B = 16,
 HEAD_DIM = 1024, two heads for the heads-style provider, chunk 128), same byte model (x read + y written + p read,
 ema_bench.py:141-145), same outputs: a CSV with one row per SEQLEN and one column per provider, and a raw log per
-provider and length.  Timing is the median of CUDA-event measurements of single calls after warm-up (the reference uses
-triton.testing.do_bench_cudagraph; this package does not depend on Triton).
+provider and length.  Timing is a CUDA-graph replay of the call (many replays between two CUDA events), which is what the
+reference's triton.testing.do_bench_cudagraph measures: the GPU time of the call without the host's launch cost; this
+package does not depend on Triton.  --eager times single eager calls instead (median of CUDA-event measurements).
 
     python -m kernels.benchmarks.ema_bench [--seqlens 8192 16384 32768 65536] [--dtype fp32|bf16] [--out DIR]
 """
@@ -45,7 +46,37 @@ def time_ms(fn, warmup=5, reps=20):
     return statistics.median(times)
 
 
-def bench_ema(BATCH, SEQLEN, HEAD_DIM, provider, dtype, raw_dir):
+def time_ms_graph(fn, warmup=3, reps=20):
+    """GPU time of one call of `fn`: the call is captured into a CUDA graph (its allocations come from the graph's own
+    pool) and the graph is replayed `reps` times between two CUDA events.  Falls back to eager timing if the call cannot
+    be captured."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(warmup):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+    except RuntimeError:
+        torch.cuda.synchronize()
+        return time_ms(fn, warmup=warmup, reps=reps)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def bench_ema(BATCH, SEQLEN, HEAD_DIM, provider, dtype, raw_dir, eager=False):
     device = "cuda"
     x = torch.randn((BATCH, SEQLEN, HEAD_DIM), dtype=torch.float32, device=device).to(dtype)
     p = torch.sigmoid(torch.randn((BATCH, SEQLEN, 1), dtype=torch.float32, device=device))
@@ -66,7 +97,7 @@ def bench_ema(BATCH, SEQLEN, HEAD_DIM, provider, dtype, raw_dir):
     else:
         raise ValueError(provider)
     with torch.no_grad():
-        ms = time_ms(fn)
+        ms = time_ms(fn) if eager else time_ms_graph(fn)
     bytes_moved = 2 * x.numel() * x.element_size() + p.numel() * p.element_size()
     gbps = bytes_moved / (ms * 1e-3) / 1e9
     raw = os.path.join(raw_dir, f"raw_{provider}_b{BATCH}_seq{SEQLEN}_chunk{MAMBA_CHUNK_SIZE}_h{HEAD_DIM}_nh{MAMBA_NUM_HEADS}.bench")
@@ -84,6 +115,7 @@ def main():
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--head-dim", type=int, default=1024)
     ap.add_argument("--out", default=os.path.join(".", "kernels", "benchmarks", "outputs_ema_scan"))
+    ap.add_argument("--eager", action="store_true", help="time single eager calls instead of CUDA-graph replays")
     args = ap.parse_args()
     dtype = torch.float32 if args.dtype == "fp32" else torch.bfloat16
     out_dir = os.path.join(args.out, gpu_name())
@@ -92,7 +124,7 @@ def main():
     name = f"ema_b{args.batch}_head_dim{args.head_dim}_nh{MAMBA_NUM_HEADS}_chunk{MAMBA_CHUNK_SIZE}.bench"
     rows = []
     for L in args.seqlens:
-        rows.append([float(L)] + [bench_ema(args.batch, L, args.head_dim, prov, dtype, raw_dir)[0] for prov, _ in PROVIDERS])
+        rows.append([float(L)] + [bench_ema(args.batch, L, args.head_dim, prov, dtype, raw_dir, args.eager)[0] for prov, _ in PROVIDERS])
     header = ",".join(["SEQLEN"] + [n for _, n in PROVIDERS])
     lines = [header] + [",".join(f"{v:.6f}" for v in r) for r in rows]
     with open(os.path.join(out_dir, name + ".csv"), "w") as f:

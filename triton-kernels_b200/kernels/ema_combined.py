@@ -8,10 +8,11 @@ weight, C = 1, kernels/benchmarks/ema_bench.py:104-117):
     dt'  = clamp(softplus?(dt + dt_bias), dt_limit)                      (ema_chunk_state.py:69-78)
     s_t  = exp(dt'_t A_h) s_{t-1} + dt'_t B_t x_t ,     y_t = C_t s_t  (+ D x_t)  (* silu(z_t))
 
-The recurrence runs in the fused scan kernels (pre-scaled log-decay convention: decay = dt' A, input =
-dt' B x).  Without gradients, D and z, the weights dt' B and C are folded into the scan kernel (one read of x, one
-write of the result); otherwise what surrounds the scan is elementwise torch, so gradients reach every tensor
-argument through autograd.
+The recurrence runs in the fused scan kernels (pre-scaled log-decay convention: decay = dt' A) with the weights dt' B
+(input) and C (output) folded into the kernels: one read of x and one write of the result forward, one read of x and
+dy and one write of dx backward.  The backward pass also returns the gradients of the decay and of both weights as
+[b, l, h] tensors, from which autograd reaches dt, A, B, C and dt_bias on [b, l, h]-sized data.  Only D and z, when
+given, add elementwise torch work on the full-size tensors.
 The reference's own backward for this entry point is a stub that returns None for every input (:89-92).
 `seq_idx` (a sequence id per position: the state restarts from zero where the id changes, as in the reference's
 chunked kernels) is a decay of exactly 0 at the first step of every new sequence.  State sizes above 1 and
@@ -23,22 +24,26 @@ import torch.nn.functional as F
 from ema_b200 import ops
 
 
-class _PrescaledScan(torch.autograd.Function):
-    """s_t = exp(A_t) s_{t-1} + u_t over u[b,L,h,p], A[b,L,h] (log decay), optional initial state [b,h,p]."""
+class _WeightedScan(torch.autograd.Function):
+    """y_t = c_t s_t, s_t = exp(A_t) s_{t-1} + w_t x_t over x[b,L,h,p] with per-step A, w, c [b,L,h] (fp32) and an
+    optional initial state: forward and backward are one kernel pass each, the weights folded into the scan, and the
+    gradients of A, w, c come out of the backward pass as [b,L,h] tensors."""
 
     @staticmethod
-    def forward(ctx, u, a_log, init_state):
-        r = ops.ema_fwd(u, a_log, prescaled_log=True, init_state=init_state, want_tile_states=True, want_final=True)
-        ctx.save_for_backward(u, a_log, r["tile_states"])
+    def forward(ctx, x, a_log, w, c, init_state):
+        r = ops.ema_fwd(x, a_log, prescaled_log=True, init_state=init_state, want_tile_states=True, want_final=True,
+                        in_weight=w, out_weight=c)
+        ctx.save_for_backward(x, a_log, w, c, r["tile_states"])
         ctx.has_init = init_state is not None
         return r["y"], r["final_state"]
 
     @staticmethod
     def backward(ctx, dy, dfinal):
-        u, a_log, tile_states = ctx.saved_tensors
-        r = ops.ema_bwd(u, a_log, dy.contiguous(), tile_states, prescaled_log=True,
-                        dfinal_state=None if dfinal is None else dfinal.float().contiguous(), want_dinit=ctx.has_init)
-        return r["dx"], r["ddecay"], r.get("dinit_state")
+        x, a_log, w, c, tile_states = ctx.saved_tensors
+        r = ops.ema_bwd_weighted(x, a_log, dy.contiguous(), tile_states, in_weight=w, out_weight=c, prescaled_log=True,
+                                 dfinal_state=None if dfinal is None else dfinal.float().contiguous(),
+                                 want_dinit=ctx.has_init)
+        return r["dx"], r["ddecay"], r["din_weight"], r["dout_weight"], r.get("dinit_state")
 
 
 def _processed_dt(dt, dt_bias, dt_softplus, dt_limit):
@@ -91,9 +96,13 @@ def _ema_chunk_scan_combined_fwd(x, dt, A, B, C, chunk_size, D=None, z=None, dt_
         r = ops.ema_fwd(x, a_log.contiguous(), prescaled_log=True, init_state=init, want_final=True,
                         in_weight=(dtp * Bh).contiguous(), out_weight=Ch.contiguous())
         return r["y"], r["final_state"].unsqueeze(-1)
-    u = (x.float() * (dtp * Bh).unsqueeze(-1)).to(x.dtype)
-    s, final = _PrescaledScan.apply(u.contiguous(), a_log.contiguous(), init)
-    out = s.float() * Ch.unsqueeze(-1)
+    # training: the same folding, with the gradients of the decay and of both weights returned by the backward pass as
+    # [b, l, h] tensors; autograd carries them on to dt, A, B, C, dt_bias (small elementwise work)
+    s, final = _WeightedScan.apply(x.contiguous() if x.stride(-1) != 1 else x, a_log.contiguous(),
+                                   (dtp * Bh).contiguous(), Ch.contiguous(), init)
+    if D is None and z is None:
+        return s, final.unsqueeze(-1)
+    out = s.float()
     if D is not None:
         out = out + x.float() * (D.float().unsqueeze(-1) if D.dim() == 1 else D.float())
     if z is not None:
