@@ -556,11 +556,8 @@ def run_gpu(args):
             dist.destroy_process_group()
             raise SystemExit(1)
 
-    if world > 1:
-        # Every step ends with a small collective that overlaps the next step's kernels.  Keep whole work items per
-        # thread block (128 of the 148 SMs busy on this workload): the collective's kernel then finds a free SM
-        # instead of holding back one thread block of a grid that fills the GPU.
-        ema_b200.lib().ema_b200_set_split(0)
+    # (The headline workload's 256 work items run as whole items, two per thread block on 128 of the 148 SMs, at every
+    # N: with N > 1 the small collective that ends a step overlaps the next step's kernels and finds a free SM.)
     b, L, h, d = W["b"], W["L"], W["h"], W["d"]
     per_head, fwd_only = W["per_head"], W["fwd_only"]
     run = RowShardedRun(W, b, dev, rank, world)
@@ -690,7 +687,6 @@ def run_gpu(args):
     if world > 1 and args.workload == "c3" and not args.no_sp:
         del run
         torch.cuda.empty_cache()
-        ema_b200.lib().ema_b200_set_split(1)
         sp = run_seq_parallel(WORKLOADS["c5"], dev, rank, world, min(K, 10), peak)
         run = None
 
@@ -768,7 +764,7 @@ def run_gpu(args):
                    "tile_steps": ts,
                    "sharding": "batch rows per rank, no data-path collective",
                    "decay": "per head [h]" if per_head else "per step [b, L, h]",
-                   "schedule": "whole items per thread block" if world > 1 else "tiles cut evenly over the SMs",
+                   "schedule": "whole work items (scan row x 128 channels), two per thread block on 128 of 148 SMs",
                    "l2": f"inputs ({b * L * h * d * 2 * (1 if fwd_only else 2) / 2**30:.1f} GiB per step) exceed the 126 MB L2; "
                          "no flush needed"},
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,

@@ -28,17 +28,22 @@ def needs_build():
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force=False, verbose=False):
-    if not force and not needs_build():
+def build(force=False, verbose=False, defines=(), out=None):
+    """Compiles every .cu under csrc/ and links the library.  `defines` (e.g. ["EMA_TRYWAIT_HINT_NS=1000"]) and `out`
+    (another library path; objects go next to it) build a variant beside the default library for A/B measurements."""
+    lib = out or LIB
+    if not force and not out and not needs_build():
         return LIB
-    os.makedirs(LIB_DIR, exist_ok=True)
+    obj_dir = os.path.dirname(lib) if out else LIB_DIR
+    os.makedirs(obj_dir, exist_ok=True)
     nvcc = os.environ.get("NVCC", "nvcc")
     objs = []
     procs = []
     for src in sources():
-        obj = os.path.join(LIB_DIR, os.path.basename(src)[:-3] + ".o")
+        obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
         cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
                "-Xcompiler", "-fPIC", "-I", os.path.join(ROOT, "include"), "-I", CSRC, "-c", src, "-o", obj]
+        cmd += [f"-D{d}" for d in defines]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")
@@ -52,13 +57,15 @@ def build(force=False, verbose=False):
         failed = failed or pr.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.check_call([nvcc, "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"])
-    return LIB
+    subprocess.check_call([nvcc, "-shared", "-o", lib] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"])
+    return lib
 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("-D", dest="defines", action="append", default=[], help="preprocessor definition for a variant build")
+    ap.add_argument("--out", help="path of the variant library (default: the package's lib/libema_b200.so)")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.defines, a.out))

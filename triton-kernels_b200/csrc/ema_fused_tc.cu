@@ -375,15 +375,36 @@ struct Sched {
 };
 // State entering tile k0 of a row's channel c: h <- P_j h + S_j over the tiles j < k0 (vec, fac: this row's aggregates).
 // Kept out of line: it runs once per piece, and the epilogue's hot loop must stay small.
+// (kFoldBatch aggregates are fetched at a time - independent loads, so one memory round trip per batch - and then folded
+// in order, one FMA each: the thread block that starts deepest inside an item would otherwise pay a round trip per tile.)
+constexpr int kFoldBatch = 32;
 __device__ __noinline__ float fold_state_before(const float *vec, const float *fac, int64_t d, int k0, float h) {
-#pragma unroll 4
-    for (int j = 0; j < k0; ++j) h = fmaf(fac[j], h, vec[static_cast<int64_t>(j) * d]);
+    for (int j = 0; j < k0; j += kFoldBatch) {
+        float s[kFoldBatch], f[kFoldBatch];
+#pragma unroll
+        for (int i = 0; i < kFoldBatch; ++i) {
+            const bool ok = j + i < k0;   // past the end: the identity step
+            s[i] = ok ? __ldg(vec + static_cast<int64_t>(j + i) * d) : 0.f;
+            f[i] = ok ? __ldg(fac + j + i) : 1.f;
+        }
+#pragma unroll
+        for (int i = 0; i < kFoldBatch; ++i) h = fmaf(f[i], h, s[i]);
+    }
     return h;
 }
 // Adjoint entering tile k1 - 1 from the right: g <- G_j + F_j g over the tiles j = n_tiles - 1 .. k1.
 __device__ __noinline__ float fold_adjoint_after(const float *vec, const float *fac, int64_t d, int k1, int n_tiles, float g) {
-#pragma unroll 4
-    for (int j = n_tiles - 1; j >= k1; --j) g = fmaf(fac[j], g, vec[static_cast<int64_t>(j) * d]);
+    for (int j = n_tiles - 1; j >= k1; j -= kFoldBatch) {
+        float s[kFoldBatch], f[kFoldBatch];
+#pragma unroll
+        for (int i = 0; i < kFoldBatch; ++i) {
+            const bool ok = j - i >= k1;
+            s[i] = ok ? __ldg(vec + static_cast<int64_t>(j - i) * d) : 0.f;
+            f[i] = ok ? __ldg(fac + j - i) : 1.f;
+        }
+#pragma unroll
+        for (int i = 0; i < kFoldBatch; ++i) g = fmaf(f[i], g, s[i]);
+    }
     return g;
 }
 constexpr int kCarryFloats = 2 * DT;   // per cut: the carries of up to two channel tiles
@@ -612,7 +633,10 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         const bool loader = half == 0;   // 128 threads that move per-channel vectors: thread m <-> channel m
         uint32_t it = 0, mt = 0;
         int cur_head = -1;
-        float h_reg[2] = {0.f, 0.f};   // AGG: the state entering the current tile, channel m of each sub-tile (loaders)
+        // AGG (loaders): the state entering the current tile for channel m of each of the (at most two) sub-tiles, and the
+        // current tile's aggregates, fetched one tile ahead.  Plain scalars selected by the sub-tile index: an array
+        // indexed at run time would live in local memory, and storing a value just loaded there waits for the load.
+        float h_reg0 = 0.f, h_reg1 = 0.f, agg_s0 = 0.f, agg_s1 = 0.f, agg_p = 0.f;
         for (int pi = 0; pi < sched.n; ++pi) {
             const Piece pc = sched.get<true>(pi);
             const int dt0 = item_dt0(pc.item), nsub = item_nsub(pc.item);
@@ -641,12 +665,18 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         v = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x) * kCarryFloats + u * DT + m);
                     }
                     h_sm[((it + u) & (kFwdHRing - 1)) * DT + m] = v;
-                    h_reg[u] = v;
+                    if (u == 0) h_reg0 = v; else h_reg1 = v;
                 }
             }
             bar_sync(1, kEpiThreads);  // once per piece: the previous one is finished everywhere, the state is in place
             if (AGG ? (loader && lane == 0) : (m == QT - 1))
                 for (int u = 0; u < nsub; ++u) mbar_arrive(bar(B_H + ((it + u) & (kFwdHRing - 1))));
+            if (AGG && loader && pc.k0 + 1 < pc.k1) {   // aggregates of the piece's first tile
+                agg_p = __ldg(p.agg_fac + row * p.n_tiles + pc.k0);
+                const float *av = p.agg_vec + (row * p.n_tiles + pc.k0) * p.d + dt0 * DT + m;
+                agg_s0 = (dt0 * DT + m < p.d) ? __ldg(av) : 0.f;
+                agg_s1 = (nsub > 1 && (dt0 + 1) * DT + m < p.d) ? __ldg(av + DT) : 0.f;
+            }
             for (int k = pc.k0; k < pc.k1; ++k)
             for (int u = 0; u < nsub; ++u, ++it) {
                 const int c0 = (dt0 + u) * DT;
@@ -660,22 +690,23 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     const int tw = k * QT + m;
                     out_w = tw < L ? p.out_weight[(row / p.h) * p.a_sb + static_cast<int64_t>(tw) * p.a_sl + hi * p.a_sh] : 0.f;
                 }
-                // AGG: this tile's aggregate, fetched ahead of the wait that hides its latency
-                float agg_s = 0.f, agg_p = 0.f;
-                if (AGG && loader && k + 1 < pc.k1) {
-                    agg_p = p.agg_fac[row * p.n_tiles + k];
-                    if (ch_ok) agg_s = p.agg_vec[(row * p.n_tiles + k) * p.d + c0 + m];
+                if (AGG && loader && k + 1 < pc.k1) {   // the state entering this channel tile's next tile
+                    const float hn = fmaf(agg_p, u == 0 ? h_reg0 : h_reg1, u == 0 ? agg_s0 : agg_s1);
+                    if (u == 0) h_reg0 = hn; else h_reg1 = hn;
+                    h_sm[((it + nsub) & (kFwdHRing - 1)) * DT + m] = hn;
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar(B_H + ((it + nsub) & (kFwdHRing - 1))));
+                    // the next tile's aggregates: a whole tile's time to arrive
+                    if (k + 2 < pc.k1) {
+                        const float *an = p.agg_vec + (row * p.n_tiles + k + 1) * p.d + c0 + m;
+                        if (ch_ok && u == 0) agg_s0 = __ldg(an);
+                        if (ch_ok && u != 0) agg_s1 = __ldg(an);
+                        if (u == nsub - 1) agg_p = __ldg(p.agg_fac + row * p.n_tiles + k + 1);
+                    }
                 }
                 if (lane == 0) mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 5);  // one poller per warp
                 __syncwarp();
                 tc_fence_after_sync();
-                if (AGG && loader && k + 1 < pc.k1) {   // the state entering this channel tile's next tile
-                    const float hn = fmaf(agg_p, h_reg[u], agg_s);
-                    h_reg[u] = hn;
-                    h_sm[((it + nsub) & (kFwdHRing - 1)) * DT + m] = hn;
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(B_H + ((it + nsub) & (kFwdHRing - 1))));
-                }
                 const float E = e_sm[((mt - 1) & (kRing - 1)) * QT + m];
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * DT + half * 64;
                 if (lane == 0) mbar_wait(bar(B_H + slot), hph, abort_flag, 6);
@@ -1117,7 +1148,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             // cut blockIdx.x is this CTA's left edge (it publishes there), cut blockIdx.x + 1 its right edge (it reads there)
             float *carry_out = p.carry + static_cast<int64_t>(blockIdx.x) * kCarryFloats;
             float hs_next = 0.f;
-            float g_reg[2] = {0.f, 0.f};   // AGG: the adjoint entering the current tile, channel m of each sub-tile (loaders)
+            float g_reg0 = 0.f, g_reg1 = 0.f;   // AGG: the adjoint entering the current tile, channel m of each sub-tile (loaders)
             if (loader) {
                 if (!AGG && pc.k1 < p.n_tiles) {   // left part of a cut item: the adjoint comes from the CTA that made the right part
                     if (lane == 0) wait_carry(p.flags + blockIdx.x + 1, 2u * nsub, abort_flag, 23);
@@ -1139,7 +1170,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                                                     p.agg_fac + row * p.n_tiles, p.d, pc.k1, p.n_tiles, gv);
                     }
                     g_sm[slot0 * DT + m] = gv;
-                    g_reg[u] = gv;
+                    if (u == 0) g_reg0 = gv; else g_reg1 = gv;
                 }
             }
             bar_sync(1, kEpiThreads);
@@ -1263,8 +1294,8 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 }
                 if (loader && k > pc.k0) {  // the saved state the tile on the left will need
                     if (AGG) {   // and the adjoint entering it
-                        const float gn = fmaf(agg_f, g_reg[u], agg_g);
-                        g_reg[u] = gn;
+                        const float gn = fmaf(agg_f, u == 0 ? g_reg0 : g_reg1, agg_g);
+                        if (u == 0) g_reg0 = gn; else g_reg1 = gn;
                         g_sm[nslot * DT + m] = gn;
                     }
                     hs_sm[nslot * DT + m] = hs_next;
@@ -1764,8 +1795,11 @@ static int make_plan(const FusedParams &fp, bool allow_carry_split, bool allow_a
     const int n_items = pl->n_items;
     const int rounds = (n_items + sms - 1) / sms;
     pl->grid = (n_items + rounds - 1) / rounds;
-    // cutting pays when whole items would leave a noticeable share of the SM-rounds idle (256 items on 148 SMs: 13.5 %)
-    const bool uneven = static_cast<int64_t>(rounds) * sms * 92 > static_cast<int64_t>(n_items) * 100;
+    // Cutting pays only when whole items would leave a large share of the SM-rounds idle.  At 256 items on 148 SMs
+    // (13.5 % idle) it does not: 128 thread blocks with two items each already move 6.0 TB/s when the clocks are high,
+    // and under the power cap the 18 extra thread blocks of the cut schedule cost in clock what they add in width
+    // (0.530 ms against 0.537 ms per headline step, measured back to back on one GPU).
+    const bool uneven = static_cast<int64_t>(rounds) * sms * 85 > static_cast<int64_t>(n_items) * 100;
     // (with fewer items than SMs a cut that hands carries on cannot help: an item's tiles are a sequential chain, and
     // the thread blocks that would share it only wait for one another - measured 30-40 % slower)
     if (!allow_carry_split || split_setting() == 0 || n_items < sms || sms > kMaxSplitGrid || !uneven || !have_carry_ws)

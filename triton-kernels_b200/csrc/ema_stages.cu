@@ -422,7 +422,7 @@ __global__ void __launch_bounds__(128) chunk_recurrence_vec_kernel(const T *__re
 
 // Forward carry over the chunks, four channels per thread (128-bit loads and stores, coalesced across the warp) with
 // the next kDepth chunk states already in flight: the chain itself is one FMA per chunk.
-constexpr int kPassDepth = 8;
+constexpr int kPassDepth = 16;
 __global__ void __launch_bounds__(32) state_passing_fwd_vec_kernel(const float4 *__restrict__ S, const float *__restrict__ cl,
                                                                    int64_t cl_sb, int64_t cl_sc, float4 *__restrict__ out,
                                                                    float4 *__restrict__ fin, int64_t C, int64_t T4) {
@@ -457,7 +457,7 @@ __global__ void __launch_bounds__(32) state_passing_fwd_vec_kernel(const float4 
 // Reverse carry of the adjoint, one warp per 128 channels of a batch row (so a row is spread over T / 128 thread
 // blocks).  Every warp writes the dot product <h_c, dS_c> over ITS channels to partial[b, c, warp]; a second kernel
 // sums the partials in a fixed order and applies exp(cs_last).
-constexpr int kPassBwdDepth = 4;
+constexpr int kPassBwdDepth = 8;
 __global__ void __launch_bounds__(32) state_passing_bwd_vec_kernel(const float4 *__restrict__ h, const float *__restrict__ cl,
                                                                    int64_t cl_sb, int64_t cl_sc, const float4 *__restrict__ dh,
                                                                    float4 *__restrict__ dS, float *__restrict__ partial,

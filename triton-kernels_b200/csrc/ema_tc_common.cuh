@@ -29,8 +29,24 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
+// One poll of an mbarrier phase.  try_wait may suspend the thread until the phase completes or a time limit passes;
+// EMA_TRYWAIT_HINT_NS > 0 asks for that limit in nanoseconds instead of the (short) system default, so that a role
+// which waits for most of a tile's time executes a handful of polls instead of hundreds - each failed poll is also a
+// read of the abort flag, and all of it competes with the working warps for issue slots and power.
+#ifndef EMA_TRYWAIT_HINT_NS
+#define EMA_TRYWAIT_HINT_NS 0
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
+#if EMA_TRYWAIT_HINT_NS > 0
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(EMA_TRYWAIT_HINT_NS))
+        : "memory");
+#else
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -38,6 +54,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok)
         : "r"(bar), "r"(parity)
         : "memory");
+#endif
     return ok != 0;
 }
 // Bounded wait.  `abort_flag` lives in shared memory; `site` identifies the wait in the status word.

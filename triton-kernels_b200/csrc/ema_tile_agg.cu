@@ -65,6 +65,22 @@ __global__ void __launch_bounds__(kAggThreads) tile_aggregate_kernel(const AggPa
     auto log2_decay = [&](float v) { return fmaxf(conv ? v * 1.4426950408889634f : __log2f(v), -160.f); };
     const float ident = conv ? 0.f : 1.f;
 
+    // ---- this thread's 16 rows of the tile (lane -> 8 channels, warp -> every 8th step), requested before the weights
+    // are worked out so that the memory round trip overlaps the scan below.  Rows past L re-read the last row and are
+    // discarded: an unconditional load is what lets all of them be in flight at once.
+    const int64_t c = static_cast<int64_t>(cg) * kAggChannels + lane * 8;
+    const bool c_ok = c < p.d;   // d is a multiple of 8 on this path
+    const __nv_bfloat16 *base = p.src + bi * p.sb + hi * p.sh + c;
+    uint4 raw[16];
+    if (c_ok) {
+        const int64_t t_last = p.L - 1;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int64_t t = t0 + warp + kAggGroups * i;
+            raw[i] = __ldg(reinterpret_cast<const uint4 *>(base + (t < p.L ? t : t_last) * p.sl));
+        }
+    }
+
     // ---- the tile's weights: inclusive scan of log2 a over 128 steps (threads 0-127)
     float v = ident, cs = 0.f;
     if (tid < kAggSteps) {
@@ -107,35 +123,19 @@ __global__ void __launch_bounds__(kAggThreads) tile_aggregate_kernel(const AggPa
     }
     __syncthreads();
 
-    // ---- weighted column sums: lane -> 8 channels, warp -> every 8th step
-    const int64_t c = static_cast<int64_t>(cg) * kAggChannels + lane * 8;
-    const bool c_ok = c < p.d;   // d is a multiple of 8 on this path
-    const __nv_bfloat16 *base = p.src + bi * p.sb + hi * p.sh + c;
+    // ---- weighted column sums
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     if (c_ok) {
-        const int64_t t_last = p.L - 1;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            // eight independent 16-byte loads in flight per thread (rows past L re-read the last row and are
-            // discarded: an unconditional load is what lets the compiler issue them back to back)
-            uint4 raw[8];
+        for (int i = 0; i < 16; ++i) {
+            const int q = warp + kAggGroups * i;
+            const float w = w_sm[q];   // 0 for steps past L
+            float f[8];
+            unpack<__nv_bfloat16, 8>(raw[i], f);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int64_t t = t0 + warp + kAggGroups * (half * 8 + i);
-                raw[i] = __ldg(reinterpret_cast<const uint4 *>(base + (t < p.L ? t : t_last) * p.sl));
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int q = warp + kAggGroups * (half * 8 + i);
-                const float w = w_sm[q];
-                if (t0 + q >= p.L) raw[i] = make_uint4(0u, 0u, 0u, 0u);
-                float f[8];
-                unpack<__nv_bfloat16, 8>(raw[i], f);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, f[e], acc[e]);
-            }
+            for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, f[e], acc[e]);
         }
     }
 #pragma unroll
