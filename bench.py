@@ -47,6 +47,10 @@ WORKLOADS = {
                 b=16, L=8192, h=2, d=1024, chunk=128, per_head=False, fwd_only=False, lo=2.0, hi=6.0),
     "c4": dict(name="ema_fwd_bwd_b4_L65536_h8_d1024_bf16_perstep_decay_chunk512",
                b=4, L=65536, h=8, d=1024, chunk=512, per_head=False, fwd_only=False, lo=3.0, hi=8.0),
+    # one rank's share of the headline batch when it is split over 8 GPUs (strong scaling): 4 scan rows = 32 work items,
+    # the few-item case in which every row is cut into pieces that start from per-tile aggregates
+    "c3_shard8": dict(name="ema_fwd_bwd_b2_L8192_h2_d1024_bf16_perhead_decay_chunk256_one_eighth_of_headline_batch",
+                      b=2, L=8192, h=2, d=1024, chunk=256, per_head=True, fwd_only=False, lo=2.0, hi=6.0),
     # sequence parallel: every rank holds one contiguous 65536-step segment of b8 h4 d1024 sequences of length
     # 65536 * N (N = 8 gives the suite's 524288-step configuration); carries are exchanged over NCCL
     "c5": dict(name="ema_fwd_bwd_seqparallel_b8_Lseg65536_h4_d1024_bf16_perstep_decay_chunk256",
@@ -592,6 +596,7 @@ def run_gpu(args):
     stats = timed_steps(run, K, dev, world, spin_seconds=0.0 if args.no_spinup else 1.2)
     t_end = time.time()
     clocks = sampler.stop(t_begin, t_end)
+    schedule = ema_b200.lib().ema_b200_last_schedule()   # of the timed steps' last call (the backward, or the forward)
     ms_per_step, fwd_ms, bwd_ms = stats["ms_per_step"], stats["fwd_ms"], stats["bwd_ms"]
     tokens = b * L * world
     value = tokens / (ms_per_step * 1e-3)
@@ -756,6 +761,8 @@ def run_gpu(args):
             cpu_baseline["c_oracle_error"] = str(exc)[:120]
 
     launches_per_step = 1 if fwd_only else (4 if per_head else 3)
+    if schedule == 2:
+        launches_per_step += 1 if fwd_only else 2   # the aggregate passes over x and dy
     line = {
         "metric": "ema_fwd_tokens_per_s" if fwd_only else METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -764,9 +771,12 @@ def run_gpu(args):
                    "tile_steps": ts,
                    "sharding": "batch rows per rank, no data-path collective",
                    "decay": "per head [h]" if per_head else "per step [b, L, h]",
-                   "schedule": "whole work items (scan row x 128 channels), two per thread block on 128 of 148 SMs",
-                   "l2": f"inputs ({b * L * h * d * 2 * (1 if fwd_only else 2) / 2**30:.1f} GiB per step) exceed the 126 MB L2; "
-                         "no flush needed"},
+                   "schedule": {0: "whole work items (scan row x 128 channels) per thread block",
+                                1: "tile ranges over the SMs, carries handed between thread blocks",
+                                2: "per-tile aggregates, then pieces of items dealt evenly over the SMs"}.get(
+                                    schedule, "cuda cores"),
+                   "l2": (f"tensors touched per step ({b * L * h * d * 2 * (2 if fwd_only else 4) / 2**20:.0f} MiB) exceed the "
+                          "126 MB L2; no flush needed")},
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
         "gpu_launches": launches_per_step * K,
         "clocks": clocks,

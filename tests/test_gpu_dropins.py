@@ -70,6 +70,37 @@ def test_prefix_entry_point_matches_pweighted_loop():
         ema_scan_combined(cu(x).transpose(1, 2), cu(p))
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_prefix_entry_point_values_and_gradients(dtype):
+    """The prefix entry point in both element types, with the gradients the reference's backward leaves out
+    (kernels/ema.py:366-367 returns None): against the sequential p-weighted loop and autograd through it."""
+    from kernels.ema import ema_scan_combined
+    from oracle import ema_loop_port as lp
+    B, T, D = 3, 700, 256
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn((B, T, D), generator=g).to(dtype)
+    p = torch.sigmoid(-4.0 + 3.0 * torch.rand((B, T, 1), generator=g))     # long memory: 1 - p up to 0.98
+    dz = torch.randn((B, T, D), generator=g).to(dtype)
+    xr = x.float().clone().requires_grad_(True)
+    pr = p.clone().requires_grad_(True)
+    z_ref = lp.ema_loop_pweighted(xr, pr)
+    (z_ref * dz.float()).sum().backward()
+    xd, pd = x.cuda().requires_grad_(True), p.cuda().requires_grad_(True)
+    z = ema_scan_combined(xd, pd)
+    assert z.dtype == dtype and z.shape == (B, T, D)
+    z.backward(dz.cuda())
+
+    def close(got, want, what):
+        got, want = got.detach().float().cpu(), want.detach().float()
+        scale = max(float(want.abs().max()), 1e-6)
+        tol = 2e-2 * scale if dtype == torch.bfloat16 else 1e-4 + 2e-5 * scale
+        assert float((got - want).abs().max()) <= tol, what
+
+    close(z, z_ref, "z")
+    close(xd.grad, xr.grad, "dx")
+    close(pd.grad, pr.grad, "dp")
+
+
 def test_reference_argument_contracts():
     from kernels.ema_kernels.ema_state_fwd import _ema_chunk_state_fwd
     from kernels.ema_kernels.ema_state_pass import _ema_state_passing_fwd

@@ -1,7 +1,8 @@
 """Parity at the full sizes of the benchmark configurations.
 
-The sequential oracle cannot run a whole 2-billion-element problem in seconds, but the scan rows (b, h) are
-independent: a few full-length rows, all channels, are checked against the oracle, and the rest of the tensor
+The headline configuration (268 million elements) is checked against the oracle as a whole: y, dx and the per-head
+decay gradient.  The sequential oracle cannot run a 2-billion-element problem in seconds, but the scan rows (b, h) are
+independent: there a few full-length rows, all channels, are checked against the oracle, and the rest of the tensor
 through properties that do not depend on the size:
   * the decay gradient of a time-invariant decay equals the sum over (b, t) of the per-step gradient of the
     same decay broadcast to [b, L, h] (two different kernel paths, one reduction each);
@@ -12,7 +13,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import BF16_REL
+from helpers import BF16_REL, assert_close_da_head
 from oracle import ema_oracle as eo
 
 pytestmark = pytest.mark.gpu
@@ -71,6 +72,19 @@ def test_headline_config_time_invariant_decay(ema_lib):
     for t in (y, dx, da):
         assert bool(torch.isfinite(t).all())
     assert ema_lib.ema_b200_device_status(0) == 0
+    # The whole tensors against the oracle (the C restatement of the sequential loop, all host cores, fp64 accumulation;
+    # about a minute): y and dx everywhere, and the per-head decay gradient - a sum of 268 million terms of either sign -
+    # within 2e-2 |ref| + 2^-8 ||terms||_2.
+    xn, dyn, an = x.float().cpu().numpy(), dy.float().cpu().numpy(), a.cpu().numpy()
+    y_ref = eo.fwd(xn, an, acc64=True)
+    dx_ref, da_ref = eo.bwd(xn, an, dyn, acc64=True)
+    for got, ref, what in ((y, y_ref, "y"), (dx, dx_ref, "dx")):
+        scale = float(np.abs(ref).max())
+        worst = 0.0
+        for bi in range(b):   # slice by slice: the fp32 copies are 1 GiB each
+            worst = max(worst, float(np.abs(got[bi].float().cpu().numpy() - ref[bi]).max()))
+        assert worst <= BF16_REL * scale, f"{what}: normalised max err {worst / scale:.3e}"
+    assert_close_da_head(da, da_ref, (xn, an, dyn), y_ref, dx_ref, "da[h] at full size")
 
 
 def test_time_varying_decay_config(ema_lib):
