@@ -123,9 +123,52 @@ class ClockSampler:
             for n, v in zip(names, r[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
+        power = []
+        for r in inside:
+            try:
+                power.append(float(r[3]))
+            except (ValueError, IndexError):
+                pass
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+                "power_w": statistics.median(power) if power else None, "power_w_max": max(power) if power else None,
                 "reasons": sorted(reasons), "samples": len(sm),
                 "window": "about 1.2 s of identical back-to-back steps ending with the timed steps"}
+
+
+def copy_probe(x, y, gpu_index):
+    """A plain device-to-device copy of the forward's bytes (x -> y), measured the way the kernels are: the best of 5
+    launches after idling, then the median of 30 after 1.2 s of back-to-back copies, with the SM clock and the power
+    nvidia-smi reported during the run-in.  It shows what the power cap leaves a kernel that only moves the bytes."""
+    import torch
+    def timed(n):
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+        for e0, e1 in ev:
+            e0.record()
+            y.copy_(x)
+            e1.record()
+        torch.cuda.synchronize()
+        return [e0.elapsed_time(e1) for e0, e1 in ev]
+    for _ in range(3):
+        y.copy_(x)
+    torch.cuda.synchronize()
+    time.sleep(0.5)
+    alone = min(timed(5))
+    sampler = ClockSampler(gpu_index)
+    sampler.start()
+    time.sleep(0.3)
+    t_begin = time.time()
+    while time.time() - t_begin < 1.2:
+        for _ in range(50):
+            y.copy_(x)
+        torch.cuda.synchronize()
+    sustained = statistics.median(timed(30))
+    clocks = sampler.stop(t_begin, time.time())
+    nbytes = 2 * x.numel() * x.element_size()
+    return {"bytes": nbytes, "alone_ms": alone, "alone_gbs": nbytes / (alone * 1e-3) / 1e9,
+            "sustained_ms": sustained, "sustained_gbs": nbytes / (sustained * 1e-3) / 1e9,
+            "sm_mhz": clocks.get("sm_mhz"), "power_w": clocks.get("power_w"), "power_w_max": clocks.get("power_w_max"),
+            "reasons": clocks.get("reasons"),
+            "note": "torch copy_ of x into y (the forward's bytes) on the same GPU right after the timed steps"}
 
 
 def algorithmic_bytes(b, L, h, d, s=2, per_head=True):
@@ -602,6 +645,12 @@ def run_gpu(args):
     value = tokens / (ms_per_step * 1e-3)
     per_rank = per_rank_table(stats, clocks.get("sm_mhz"), dev, world) if world > 1 else None
 
+    probe = None
+    if world == 1 and not args.no_spinup and not args.no_copy_probe:
+        probe = copy_probe(run.x, run.y, local)
+        run.fwd()   # y holds the forward's result again
+        torch.cuda.synchronize()
+
     # ---- strong scaling (N > 1): the headline batch split over the ranks
     strong = None
     if world > 1 and not fwd_only and b % world == 0 and not args.no_strong:
@@ -729,6 +778,8 @@ def run_gpu(args):
             "bwd_frac": bwd_b / (burst[1] * 1e-3) / 1e9 / peak,
             "note": "best of 5 launches right after warm-up, before the clocks settle under the power cap; "
                     "every other figure of this line is from the timed steps under sustained load"}
+    if probe is not None:
+        roofline["copy_probe"] = probe
     traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
     if args.workload == "c3" and os.path.exists(traffic_file):
         # dram__bytes_read.sum + dram__bytes_write.sum from the committed ncu capture of this workload
@@ -806,6 +857,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-spinup", action="store_true", help="skip the untimed run-in used for clock sampling (profiling runs)")
+    ap.add_argument("--no-copy-probe", action="store_true", help="skip the plain-copy comparison (N = 1)")
     ap.add_argument("--no-parity", action="store_true", help="N > 1: skip the multi-GPU parity self-check")
     ap.add_argument("--no-strong", action="store_true", help="N > 1: skip the strong-scaling leg")
     ap.add_argument("--no-sp", action="store_true", help="N > 1: skip the sequence-parallel leg")
