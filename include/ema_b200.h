@@ -95,6 +95,25 @@ int ema_b200_device_status(int clear);
  * working. */
 int ema_b200_selftest_wait(int mode, int polls, const void *zero_word, void *stream);
 
+/* Bounds-checking build (test support; no counterpart in the reference).  A library built with -DEMA_BOUNDS_CHECK
+ * (build.py --checked -> libema_b200_checked.so) routes every plain global-memory access of the fused kernels -
+ * ema_b200_fwd, _fwd_weighted, _bwd, _bwd_weighted, _fold_records and everything they launch - through a check against
+ * the address ranges of the call's own buffers, which the entry point derives from the shapes, strides and byte counts
+ * it was given.  An access outside all of them is recorded (the first one only) and redirected to a sink inside the
+ * library's table: nothing outside the buffers is read or written and nothing traps.  TMA copies are clipped by their
+ * tensor maps and need no check.  The table is per device and rewritten from host memory before every launch: use one
+ * stream at a time with this build, and do not capture its calls in a CUDA graph.
+ *   ema_b200_bounds_checked()      1 in that build, 0 in the normal one (where the two calls below do nothing).
+ *   ema_b200_bounds_status(clear)  0, or 0x400 | site of the first rejected access since the word was last cleared;
+ *                                  synchronises the device.
+ *   ema_b200_bounds_shrink_next(n) test hook: the next checked call of this thread registers its output tensor (y or dx)
+ *                                  as n bytes shorter than it is, so that the kernel's last stores are rejected although
+ *                                  the memory is really there - a self-test of the checker that touches nothing foreign.
+ *                                  Returns EMA_ERR_UNSUPPORTED in the normal build. */
+int ema_b200_bounds_checked(void);
+int ema_b200_bounds_status(int clear);
+int ema_b200_bounds_shrink_next(size_t bytes);
+
 /* Which kernels bf16 problems run on: 0 = tensor-core path wherever the layout allows it (default),
  * 1 = plain CUDA-core kernels only (also for fp32, which otherwise uses the TMA-fed variants of the same
  * kernels).  fp32 problems always compute on the CUDA cores (exactness).  Meant for A/B

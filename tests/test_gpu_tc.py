@@ -237,6 +237,8 @@ def test_many_restarts_inside_a_tile(_lib):
 
 
 def test_calls_can_be_captured_in_cuda_graphs(_lib):
+    if _lib.ema_b200_bounds_checked():
+        pytest.skip("the bounds-checking build rewrites its table from host memory before every launch: not capturable")
     """With caller-provided buffers a forward and a backward call only queue stream work (kernels and two small
     memsets), so they capture into CUDA graphs; a replay must reproduce the eager results bit for bit."""
     E = _E()

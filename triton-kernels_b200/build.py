@@ -1,6 +1,9 @@
 """Build libema_b200.so (sm_100a only) in-tree with nvcc.
 
-    python triton-kernels_b200/build.py [--force] [--verbose]
+    python triton-kernels_b200/build.py [--force] [--verbose] [--checked]
+
+--checked builds lib/libema_b200_checked.so as well: the same sources with -DEMA_BOUNDS_CHECK, every plain global-memory
+access of the fused kernels checked against the call's buffers (csrc/ema_bounds.cuh).
 
 The library lands in triton-kernels_b200/lib/ next to the sources, so that it travels with the
 repository checkout; nothing is installed into site-packages or a JIT cache.
@@ -15,15 +18,16 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libema_b200.so")
+LIB_CHECKED = os.path.join(LIB_DIR, "libema_b200_checked.so")
 
 def sources():
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
-def needs_build():
-    if not os.path.exists(LIB):
+def needs_build(lib=LIB):
+    if not os.path.exists(lib):
         return True
-    t = os.path.getmtime(LIB)
+    t = os.path.getmtime(lib)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(ROOT, "include", "ema_b200.h")]
     return any(os.path.getmtime(d) > t for d in deps)
 
@@ -34,7 +38,7 @@ def build(force=False, verbose=False, defines=(), out=None):
     lib = out or LIB
     if not force and not out and not needs_build():
         return LIB
-    obj_dir = os.path.dirname(lib) if out else LIB_DIR
+    obj_dir = os.path.join(os.path.dirname(lib), "obj_" + os.path.basename(lib)[:-3]) if out else LIB_DIR
     os.makedirs(obj_dir, exist_ok=True)
     nvcc = os.environ.get("NVCC", "nvcc")
     objs = []
@@ -61,11 +65,21 @@ def build(force=False, verbose=False, defines=(), out=None):
     return lib
 
 
+def build_checked(force=False, verbose=False):
+    """The bounds-checking variant, beside the default library."""
+    if not force and not needs_build(LIB_CHECKED):
+        return LIB_CHECKED
+    return build(force=True, verbose=verbose, defines=["EMA_BOUNDS_CHECK"], out=LIB_CHECKED)
+
+
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("-D", dest="defines", action="append", default=[], help="preprocessor definition for a variant build")
     ap.add_argument("--out", help="path of the variant library (default: the package's lib/libema_b200.so)")
+    ap.add_argument("--checked", action="store_true", help="also build the bounds-checking variant")
     a = ap.parse_args()
     print(build(a.force, a.verbose, a.defines, a.out))
+    if a.checked:
+        print(build_checked(a.force, a.verbose))

@@ -2,8 +2,10 @@
 #include "ema_common.cuh"
 
 #include <atomic>
+#include <cstddef>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 namespace ema {
 
@@ -51,6 +53,37 @@ bool tc_enabled() {
     return v == 0;
 }
 
+// ---- bounds-checking build: the address ranges of a call's buffers ---------------------------------------------
+// bytes spanned by a [b, L, h, d] tensor with element strides sb, sl, sh (d contiguous), es bytes per element
+size_t span4(const ema_b200_problem *p, int64_t sb, int64_t sl, int64_t sh, size_t es) {
+    if (p->b <= 0 || p->L <= 0 || p->h <= 0 || p->d <= 0) return 0;
+    return static_cast<size_t>((p->b - 1) * sb + (p->L - 1) * sl + (p->h - 1) * sh + p->d) * es;
+}
+// bytes spanned by the decay (and everything shaped like it: its gradient, the per-step weights and theirs)
+size_t span_decay(const ema_b200_problem *p) {
+    if (p->b <= 0 || p->L <= 0 || p->h <= 0) return 0;
+    if (p->decay_mode == EMA_DECAY_PER_STEP)
+        return static_cast<size_t>((p->b - 1) * p->a_sb + (p->L - 1) * p->a_sl + (p->h - 1) * p->a_sh + 1) * 4;
+    return static_cast<size_t>((p->h - 1) * p->a_sh + 1) * 4;
+}
+#ifdef EMA_BOUNDS_CHECK
+thread_local size_t g_shrink_next = 0;
+BoundsTable *device_table() {   // one table per device, made on first use
+    static std::mutex mu;
+    static BoundsTable *tabs[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!tabs[dev]) {
+        BoundsTable *t = nullptr;
+        if (cudaMalloc(&t, sizeof(BoundsTable)) != cudaSuccess) return nullptr;
+        if (cudaMemset(t, 0, sizeof(BoundsTable)) != cudaSuccess) return nullptr;
+        tabs[dev] = t;
+    }
+    return tabs[dev];
+}
+#endif
+
 void fill_params(FusedParams &fp, const ema_b200_problem *p, int vec) {
     std::memset(&fp, 0, sizeof(fp));
     fp.b = p->b; fp.L = p->L; fp.h = p->h; fp.d = p->d;
@@ -68,11 +101,72 @@ void fill_params(FusedParams &fp, const ema_b200_problem *p, int vec) {
 }
 
 }  // namespace
+
+// ranges[0] is the call's output tensor (the one ema_b200_bounds_shrink_next shortens)
+BoundsTable *bounds_prepare(const BoundsRange *ranges, int n, cudaStream_t stream) {
+#ifdef EMA_BOUNDS_CHECK
+    BoundsTable *tb = device_table();
+    if (!tb) return nullptr;
+    BoundsTable h;
+    std::memset(&h, 0, sizeof(h));
+    for (int i = 0; i < n && h.n < kBoundsMaxRanges; ++i) {
+        if (!ranges[i].ptr || ranges[i].bytes == 0) continue;
+        size_t bytes = ranges[i].bytes;
+        if (i == 0 && g_shrink_next) bytes = bytes > g_shrink_next ? bytes - g_shrink_next : 0;
+        h.lo[h.n] = reinterpret_cast<unsigned long long>(ranges[i].ptr);
+        h.hi[h.n] = h.lo[h.n] + bytes;
+        ++h.n;
+    }
+    g_shrink_next = 0;
+    // everything between the status word and the sink (pageable source: staged before the call returns)
+    const size_t off = offsetof(BoundsTable, n), len = offsetof(BoundsTable, sink) - off;
+    if (cudaMemcpyAsync(reinterpret_cast<char *>(tb) + off, reinterpret_cast<const char *>(&h) + off, len,
+                        cudaMemcpyHostToDevice, stream) != cudaSuccess)
+        return nullptr;
+    return tb;
+#else
+    (void)ranges; (void)n; (void)stream;
+    return nullptr;
+#endif
+}
+
+int bounds_read_status(int clear) {
+#ifdef EMA_BOUNDS_CHECK
+    BoundsTable *tb = device_table();
+    if (!tb) return 0;
+    unsigned v = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return 0;
+    if (cudaMemcpy(&v, &tb->status, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+    if (v && clear) cudaMemset(&tb->status, 0, sizeof(v));
+    return static_cast<int>(v);
+#else
+    (void)clear;
+    return 0;
+#endif
+}
 }  // namespace ema
 
 using namespace ema;
 
 extern "C" int ema_b200_version(void) { return EMA_B200_VERSION; }
+
+extern "C" int ema_b200_bounds_checked(void) {
+#ifdef EMA_BOUNDS_CHECK
+    return 1;
+#else
+    return 0;
+#endif
+}
+extern "C" int ema_b200_bounds_status(int clear) { return bounds_read_status(clear); }
+extern "C" int ema_b200_bounds_shrink_next(size_t bytes) {
+#ifdef EMA_BOUNDS_CHECK
+    g_shrink_next = bytes;
+    return EMA_OK;
+#else
+    (void)bytes;
+    return EMA_ERR_UNSUPPORTED;
+#endif
+}
 
 extern "C" int ema_b200_last_cuda_error(void) { return g_last_cuda_error; }
 
@@ -192,6 +286,18 @@ static int fwd_impl(const ema_b200_problem *p, const void *x, const float *decay
     fp.sync_ws = ws_ok ? workspace : nullptr;
     fp.sync_ws_bytes = ws_ok ? workspace_bytes : 0;
     if (rows * fp.n_dtiles >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;
+    if (ema_b200_bounds_checked()) {
+        const size_t state = static_cast<size_t>(rows * p->d) * 4;
+        const BoundsRange ranges[] = {
+            {y, span4(p, p->y_sb, p->y_sl, p->y_sh, es)},
+            {x, span4(p, p->x_sb, p->x_sl, p->x_sh, es)},
+            {decay, span_decay(p)}, {in_weight, span_decay(p)}, {out_weight, span_decay(p)},
+            {chunk_states, state * static_cast<size_t>(fp.n_chunks)}, {tile_states, ema_b200_tile_states_bytes(p)},
+            {init_state, state}, {final_state, state}, {log_decay_sum, static_cast<size_t>(rows) * 4},
+            {fp.sync_ws, fp.sync_ws_bytes}};
+        fp.bounds = bounds_prepare(ranges, static_cast<int>(sizeof(ranges) / sizeof(ranges[0])), st);
+        if (!fp.bounds) return EMA_ERR_CUDA;
+    }
     if (p->dtype == EMA_BF16 && y && stop_below == 0.f && tc_enabled() &&
         tc_tensor_ok(x, p->d, p->x_sb, p->x_sl, p->x_sh, p->b, p->L, p->h) &&
         tc_tensor_ok(y, p->d, p->y_sb, p->y_sl, p->y_sh, p->b, p->L, p->h) && aligned(tile_states, 16)) {
@@ -275,6 +381,17 @@ extern "C" int ema_b200_bwd(const ema_b200_problem *p, const void *x, const floa
     fp.sync_ws = static_cast<uint8_t *>(workspace) + bwd_partial_bytes(p);
     fp.sync_ws_bytes = sync_bytes(p);
     if (rows * fp.n_dtiles >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;
+    if (ema_b200_bounds_checked()) {
+        const size_t state = static_cast<size_t>(rows * p->d) * 4;
+        const BoundsRange ranges[] = {
+            {dx, span4(p, p->y_sb, p->y_sl, p->y_sh, es)},
+            {x, span4(p, p->x_sb, p->x_sl, p->x_sh, es)}, {dy, span4(p, p->g_sb, p->g_sl, p->g_sh, es)},
+            {decay, span_decay(p)}, {ddecay, span_decay(p)},
+            {tile_states, ema_b200_tile_states_bytes(p)}, {dfinal_state, state}, {dinit_state, state},
+            {workspace, ema_b200_bwd_workspace_bytes(p)}};
+        fp.bounds = bounds_prepare(ranges, static_cast<int>(sizeof(ranges) / sizeof(ranges[0])), st);
+        if (!fp.bounds) return EMA_ERR_CUDA;
+    }
     bool done = false;
     if (p->dtype == EMA_BF16 && stop_below == 0.f && tc_enabled() && vec == 4 &&
         tc_tensor_ok(x, p->d, p->x_sb, p->x_sl, p->x_sh, p->b, p->L, p->h) &&
@@ -336,6 +453,18 @@ extern "C" int ema_b200_bwd_weighted(const ema_b200_problem *p, const void *x, c
     fp.da_partial = static_cast<float *>(workspace);
     fp.weighted_partial_stride = static_cast<int64_t>(bwd_partial_bytes(p) / sizeof(float));
     if (rows * fp.n_dtiles >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;
+    if (ema_b200_bounds_checked()) {
+        const size_t state = static_cast<size_t>(rows * p->d) * 4;
+        const BoundsRange ranges[] = {
+            {dx, span4(p, p->y_sb, p->y_sl, p->y_sh, es)},
+            {x, span4(p, p->x_sb, p->x_sl, p->x_sh, es)}, {dy, span4(p, p->g_sb, p->g_sl, p->g_sh, es)},
+            {decay, span_decay(p)}, {ddecay, span_decay(p)}, {in_weight, span_decay(p)}, {out_weight, span_decay(p)},
+            {din_weight, span_decay(p)}, {dout_weight, span_decay(p)},
+            {tile_states, ema_b200_tile_states_bytes(p)}, {dfinal_state, state}, {dinit_state, state},
+            {workspace, ema_b200_bwd_weighted_workspace_bytes(p)}};
+        fp.bounds = bounds_prepare(ranges, static_cast<int>(sizeof(ranges) / sizeof(ranges[0])), st);
+        if (!fp.bounds) return EMA_ERR_CUDA;
+    }
     if (p->d == 0) {
         fp.n_dtiles = 0;   // no channels: every gradient of a per-step quantity is an empty sum
     } else {

@@ -17,15 +17,20 @@ struct RegisterFeedBwd {
     int64_t x_sl, g_sl;
     int sub;
     bool c_ok;
+    BoundsTable *bounds;
+    // VEC elements at q (bounds-checked in the checking build), or zeros
+    __device__ __forceinline__ R fetch(const T *q, bool ok, unsigned site) {
+        return ok ? ld_stream<T, VEC>(EMA_ATN(*this, q, site, sizeof(T) * VEC)) : raw_zero<T, VEC>();
+    }
     __device__ __forceinline__ void init(const FusedParams &p, const T *xrow_, const T *grow_, bool c_ok_, int sub_, int L,
                                          int n_tiles) {
-        xrow = xrow_; grow = grow_; x_sl = p.x_sl; g_sl = p.g_sl; sub = sub_; c_ok = c_ok_;
+        xrow = xrow_; grow = grow_; x_sl = p.x_sl; g_sl = p.g_sl; sub = sub_; c_ok = c_ok_; bounds = p.bounds;
 #pragma unroll
         for (int s = 0; s < kFmaSB; ++s) {   // the last tile may be ragged
             const int t = (n_tiles - 1) * kFmaTile + sub * kFmaSB + s;
             const bool ok = c_ok && t < L;
-            xc[s] = load_or_zero<T, VEC>(xrow + static_cast<int64_t>(t) * x_sl, ok);
-            gc[s] = load_or_zero<T, VEC>(grow + static_cast<int64_t>(t) * g_sl, ok);
+            xc[s] = fetch(xrow + static_cast<int64_t>(t) * x_sl, ok, 50);
+            gc[s] = fetch(grow + static_cast<int64_t>(t) * g_sl, ok, 51);
         }
     }
     // tile k (never the last one: it is a full tile)
@@ -33,8 +38,8 @@ struct RegisterFeedBwd {
 #pragma unroll
         for (int s = 0; s < kFmaSB; ++s) {
             const int t = k * kFmaTile + sub * kFmaSB + s;
-            xd[s] = load_or_zero<T, VEC>(xrow + static_cast<int64_t>(t) * x_sl, c_ok);
-            gd[s] = load_or_zero<T, VEC>(grow + static_cast<int64_t>(t) * g_sl, c_ok);
+            xd[s] = fetch(xrow + static_cast<int64_t>(t) * x_sl, c_ok, 52);
+            gd[s] = fetch(grow + static_cast<int64_t>(t) * g_sl, c_ok, 53);
         }
     }
     __device__ __forceinline__ void begin(int, int k, bool more) {
@@ -124,12 +129,13 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
     const T *grow = static_cast<const T *>(p.dy) + bi * p.g_sb + hi * p.g_sh + c0;
     T *orow = static_cast<T *>(p.out) + bi * p.o_sb + hi * p.o_sh + c0;
     const float *arow = p.decay + (per_step ? bi * p.a_sb + hi * p.a_sh : hi * p.a_sh);
-    const float a_head = per_step ? 1.f : (conv ? expf(arow[0]) : arow[0]);
+    const float a_head_raw = per_step ? 0.f : *EMA_AT(p, arow, 54);
+    const float a_head = per_step ? 1.f : (conv ? expf(a_head_raw) : a_head_raw);
 
     auto load_a = [&](int t) -> float {
         if (t >= L) return 1.f;
         if (!per_step) return a_head;
-        const float v = arow[static_cast<int64_t>(t) * p.a_sl];
+        const float v = *EMA_AT(p, arow + static_cast<int64_t>(t) * p.a_sl, 55);
         return conv ? expf(v) : v;
     };
     // per-step weights share the decay's strides; a missing output weight is 1, a missing input weight the convention's
@@ -137,23 +143,23 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
     const bool explicit_w = WEIGHTED && p.in_weight != nullptr;
     auto load_in_w = [&](int t) -> float {
         if (t >= L) return 0.f;
-        if (p.in_weight) return p.in_weight[w_off + static_cast<int64_t>(t) * p.a_sl];
-        return conv ? 1.f : 1.f - arow[static_cast<int64_t>(t) * p.a_sl];
+        if (p.in_weight) return *EMA_AT(p, p.in_weight + w_off + static_cast<int64_t>(t) * p.a_sl, 56);
+        return conv ? 1.f : 1.f - *EMA_AT(p, arow + static_cast<int64_t>(t) * p.a_sl, 57);
     };
     auto load_out_w = [&](int t) -> float {
         if (!p.out_weight) return 1.f;
-        return t < L ? p.out_weight[w_off + static_cast<int64_t>(t) * p.a_sl] : 0.f;
+        return t < L ? *EMA_AT(p, p.out_weight + w_off + static_cast<int64_t>(t) * p.a_sl, 58) : 0.f;
     };
     auto load_state = [&](int k, float (&hs)[VEC]) {
         const float *ts = p.tile_states + (row * n_tiles + k) * p.d + c0;
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) hs[v] = c_ok ? ts[v] : 0.f;
+        for (int v = 0; v < VEC; ++v) hs[v] = c_ok ? *EMA_AT(p, ts + v, 59) : 0.f;
     };
 
     float dfin[VEC];
 #pragma unroll
     for (int v = 0; v < VEC; ++v)
-        dfin[v] = (p.dfinal_state && c_ok) ? p.dfinal_state[row * p.d + c0 + v] : 0.f;
+        dfin[v] = (p.dfinal_state && c_ok) ? *EMA_AT(p, p.dfinal_state + row * p.d + c0 + v, 60) : 0.f;
 
     if (sub == 0) {
 #pragma unroll
@@ -311,14 +317,15 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
                 acc_c[s] = (t < L) ? c_acc : 0.f;
             }
             if (c_ok && t < L)
-                st_stream<T, VEC>(orow + static_cast<int64_t>(t) * p.o_sl, pack<T, VEC>(dxf));
+                st_stream<T, VEC>(EMA_ATN(p, orow + static_cast<int64_t>(t) * p.o_sl, 61, sizeof(T) * VEC),
+                                  pack<T, VEC>(dxf));
         }
         if (sub == 0) {
 #pragma unroll
             for (int v = 0; v < VEC; ++v) g_sm[par ^ 1][lc * VEC + v] = g[v];
             if (k == 0 && p.dinit_state && c_ok) {
 #pragma unroll
-                for (int v = 0; v < VEC; ++v) p.dinit_state[row * p.d + c0 + v] = a_r[0] * g[v];
+                for (int v = 0; v < VEC; ++v) *EMA_AT(p, p.dinit_state + row * p.d + c0 + v, 62) = a_r[0] * g[v];
             }
         }
 
@@ -326,13 +333,13 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
         if (per_step) {
             const float tot = reduce8_over16(acc, lc);
             const int64_t slot = blk * (static_cast<int64_t>(n_tiles) * QT) + t0 + (lc >> 1);
-            if ((lc & 1) == 0) p.da_partial[slot] = tot;
+            if ((lc & 1) == 0) *EMA_AT(p, p.da_partial + slot, 63) = tot;
             if constexpr (WEIGHTED) {
                 const float tot_w = reduce8_over16(acc_w, lc);
                 const float tot_c = reduce8_over16(acc_c, lc);
                 if ((lc & 1) == 0) {
-                    p.da_partial[p.weighted_partial_stride + slot] = tot_w;
-                    p.da_partial[2 * p.weighted_partial_stride + slot] = tot_c;
+                    *EMA_AT(p, p.da_partial + p.weighted_partial_stride + slot, 64) = tot_w;
+                    *EMA_AT(p, p.da_partial + 2 * p.weighted_partial_stride + slot, 65) = tot_c;
                 }
             }
         } else {
@@ -342,7 +349,8 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
             if ((tid & 31) == 0)
-                p.da_partial[kHeadPartialOffset(p.b * p.h) + (blk * n_tiles + k) * (kFmaThreads / 32) + (tid >> 5)] = tot;
+                *EMA_AT(p, p.da_partial + kHeadPartialOffset(p.b * p.h) + (blk * n_tiles + k) * (kFmaThreads / 32) + (tid >> 5),
+                        66) = tot;
         }
 
         if (p.stop_below > 0.f) {

@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include "ema_b200.h"
+#include "ema_bounds.cuh"
 
 namespace ema {
 
@@ -40,6 +41,8 @@ struct FusedParams {
     // scratch for carries handed between CTAs of the tensor-core kernels (optional; see tc_sync_bytes)
     void *sync_ws;
     size_t sync_ws_bytes;
+    // bounds-checking build: the table of this call's buffers (null in the normal build)
+    BoundsTable *bounds;
 };
 
 // ---- raw vector types: VEC elements of T moved by one load/store instruction ----------------

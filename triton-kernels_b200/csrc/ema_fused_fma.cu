@@ -44,44 +44,47 @@ __global__ void __launch_bounds__(kFmaThreads) ema_bwd_fma_weighted_kernel(const
 // ------------------------------------------------------------------------------------------------
 // decay-gradient reductions (fixed order, no atomics)
 // ------------------------------------------------------------------------------------------------
+struct BoundsRef {   // what EMA_AT needs from a parameter block
+    BoundsTable *bounds;
+};
 // per-step decay: ddecay[b,t,h] = sum over channel tiles of da_partial[row][dtile][t]
 __global__ void da_reduce_steps_kernel(const float *__restrict__ part, float *__restrict__ ddecay,
                                        int64_t rows, int64_t h, int64_t L, int64_t L_pad,
-                                       int n_dtiles, int64_t a_sb, int64_t a_sl, int64_t a_sh) {
+                                       int n_dtiles, int64_t a_sb, int64_t a_sl, int64_t a_sh, BoundsRef br) {
     const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= rows * L) return;
     const int64_t row = idx / L, t = idx % L;
     const float *src = part + row * n_dtiles * L_pad + t;
     float s = 0.f;
-    for (int j = 0; j < n_dtiles; ++j) s += src[static_cast<int64_t>(j) * L_pad];
-    ddecay[(row / h) * a_sb + t * a_sl + (row % h) * a_sh] = s;
+    for (int j = 0; j < n_dtiles; ++j) s += *EMA_AT(br, src + static_cast<int64_t>(j) * L_pad, 220);
+    *EMA_AT(br, ddecay + (row / h) * a_sb + t * a_sl + (row % h) * a_sh, 221) = s;
 }
 
 // per-head decay, level 1: one CTA per scan row sums that row's partials (channel tiles x time
 // tiles x warps) in a fixed order
 __global__ void da_reduce_rows_kernel(const float *__restrict__ part, double *__restrict__ row_sum,
-                                      int64_t per_row) {
+                                      int64_t per_row, BoundsRef br) {
     __shared__ double red[256];
     const float *src = part + static_cast<int64_t>(blockIdx.x) * per_row;
     double s = 0.0;
-    for (int64_t i = threadIdx.x; i < per_row; i += blockDim.x) s += static_cast<double>(src[i]);
+    for (int64_t i = threadIdx.x; i < per_row; i += blockDim.x) s += static_cast<double>(*EMA_AT(br, src + i, 222));
     red[threadIdx.x] = s;
     __syncthreads();
     for (int o = 128; o > 0; o >>= 1) {
         if (static_cast<int>(threadIdx.x) < o) red[threadIdx.x] += red[threadIdx.x + o];
         __syncthreads();
     }
-    if (threadIdx.x == 0) row_sum[blockIdx.x] = red[0];
+    if (threadIdx.x == 0) *EMA_AT(br, row_sum + blockIdx.x, 223) = red[0];
 }
 
 // level 2: ddecay[h] = sum over the batch of the row sums
 __global__ void da_reduce_head_kernel(const double *__restrict__ row_sum, float *__restrict__ ddecay,
-                                      int64_t b, int64_t h, int64_t a_sh) {
+                                      int64_t b, int64_t h, int64_t a_sh, BoundsRef br) {
     const int64_t hi = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (hi >= h) return;
     double s = 0.0;
-    for (int64_t bi = 0; bi < b; ++bi) s += row_sum[bi * h + hi];
-    ddecay[hi * a_sh] = static_cast<float>(s);
+    for (int64_t bi = 0; bi < b; ++bi) s += *EMA_AT(br, row_sum + bi * h + hi, 224);
+    *EMA_AT(br, ddecay + hi * a_sh, 225) = static_cast<float>(s);
 }
 
 template <typename T, int VEC>
@@ -133,14 +136,14 @@ int launch_da_reduce(const FusedParams &p, float *ddecay, int tile_steps, cudaSt
         const int64_t L_pad = static_cast<int64_t>(p.n_tiles) * tile_steps;
         if ((n + 255) / 256 >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;   // beyond one grid dimension
         da_reduce_steps_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(
-            p.da_partial, ddecay, rows, p.h, p.L, L_pad, p.n_dtiles, p.a_sb, p.a_sl, p.a_sh);
+            p.da_partial, ddecay, rows, p.h, p.L, L_pad, p.n_dtiles, p.a_sb, p.a_sl, p.a_sh, BoundsRef{p.bounds});
     } else {
         const int64_t per_row = static_cast<int64_t>(p.n_dtiles) * p.n_tiles * (kFmaThreads / 32);
         double *row_sum = reinterpret_cast<double *>(p.da_partial);
         da_reduce_rows_kernel<<<static_cast<unsigned>(rows), 256, 0, stream>>>(
-            p.da_partial + kHeadPartialOffset(rows), row_sum, per_row);
-        da_reduce_head_kernel<<<static_cast<unsigned>((p.h + 127) / 128), 128, 0, stream>>>(row_sum, ddecay, p.b,
-                                                                                           p.h, p.a_sh);
+            p.da_partial + kHeadPartialOffset(rows), row_sum, per_row, BoundsRef{p.bounds});
+        da_reduce_head_kernel<<<static_cast<unsigned>((p.h + 127) / 128), 128, 0, stream>>>(
+            row_sum, ddecay, p.b, p.h, p.a_sh, BoundsRef{p.bounds});
     }
     return check_launch();
 }

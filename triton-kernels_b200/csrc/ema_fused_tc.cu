@@ -286,10 +286,13 @@ __device__ __forceinline__ void builder_scan(float v, int t, float *cs_sm, float
 }
 
 // dst[0..min(32, n_valid)) = y; deliberately not inlined (see the forward epilogue)
-__device__ __noinline__ void store_row32(float *dst, const float (&y)[32], int n_valid) {
+struct BoundsRef {   // what EMA_AT needs from a parameter block
+    BoundsTable *bounds;
+};
+__device__ __noinline__ void store_row32(float *dst, const float (&y)[32], int n_valid, BoundsRef br) {
 #pragma unroll
     for (int c = 0; c < 32; ++c)
-        if (c < n_valid) dst[c] = y[c];
+        if (c < n_valid) *EMA_AT(br, dst + c, 100) = y[c];
 }
 
 // MMA descriptors of a [128 steps x 128 channels] tile: two 64-channel blocks kBlockBytes apart (LBO),
@@ -318,6 +321,7 @@ struct TcParams {
     // aggregate schedule (split == 2): per-tile aggregates [rows, n_tiles, d] and decay products [rows, n_tiles] made
     // by tile_aggregate_kernel; a piece that starts inside an item folds the aggregates of the tiles before it
     const float *agg_vec, *agg_fac;
+    BoundsTable *bounds;   // bounds-checking build only
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -378,14 +382,15 @@ struct Sched {
 // (kFoldBatch aggregates are fetched at a time - independent loads, so one memory round trip per batch - and then folded
 // in order, one FMA each: the thread block that starts deepest inside an item would otherwise pay a round trip per tile.)
 constexpr int kFoldBatch = 32;
-__device__ __noinline__ float fold_state_before(const float *vec, const float *fac, int64_t d, int k0, float h) {
+__device__ __noinline__ float fold_state_before(const float *vec, const float *fac, int64_t d, int k0, float h,
+                                                BoundsRef br) {
     for (int j = 0; j < k0; j += kFoldBatch) {
         float s[kFoldBatch], f[kFoldBatch];
 #pragma unroll
         for (int i = 0; i < kFoldBatch; ++i) {
             const bool ok = j + i < k0;   // past the end: the identity step
-            s[i] = ok ? __ldg(vec + static_cast<int64_t>(j + i) * d) : 0.f;
-            f[i] = ok ? __ldg(fac + j + i) : 1.f;
+            s[i] = ok ? __ldg(EMA_AT(br, vec + static_cast<int64_t>(j + i) * d, 101)) : 0.f;
+            f[i] = ok ? __ldg(EMA_AT(br, fac + j + i, 102)) : 1.f;
         }
 #pragma unroll
         for (int i = 0; i < kFoldBatch; ++i) h = fmaf(f[i], h, s[i]);
@@ -393,14 +398,15 @@ __device__ __noinline__ float fold_state_before(const float *vec, const float *f
     return h;
 }
 // Adjoint entering tile k1 - 1 from the right: g <- G_j + F_j g over the tiles j = n_tiles - 1 .. k1.
-__device__ __noinline__ float fold_adjoint_after(const float *vec, const float *fac, int64_t d, int k1, int n_tiles, float g) {
+__device__ __noinline__ float fold_adjoint_after(const float *vec, const float *fac, int64_t d, int k1, int n_tiles, float g,
+                                                 BoundsRef br) {
     for (int j = n_tiles - 1; j >= k1; j -= kFoldBatch) {
         float s[kFoldBatch], f[kFoldBatch];
 #pragma unroll
         for (int i = 0; i < kFoldBatch; ++i) {
             const bool ok = j - i >= k1;
-            s[i] = ok ? __ldg(vec + static_cast<int64_t>(j - i) * d) : 0.f;
-            f[i] = ok ? __ldg(fac + j - i) : 1.f;
+            s[i] = ok ? __ldg(EMA_AT(br, vec + static_cast<int64_t>(j - i) * d, 103)) : 0.f;
+            f[i] = ok ? __ldg(EMA_AT(br, fac + j - i, 104)) : 1.f;
         }
 #pragma unroll
         for (int i = 0; i < kFoldBatch; ++i) g = fmaf(f[i], g, s[i]);
@@ -648,7 +654,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             float *carry_out = p.carry + static_cast<int64_t>(blockIdx.x + 1) * kCarryFloats;
             if (loader) {
                 if (!AGG && pc.k0 > 0) {   // second part of a cut item: the state comes from the CTA that made the first part
-                    if (lane == 0) wait_carry(p.flags + blockIdx.x, 2u * nsub, abort_flag, 22);
+                    if (lane == 0) wait_carry(EMA_AT(p, p.flags + blockIdx.x, 105), 2u * nsub, abort_flag, 22);
                     __syncwarp();
                 }
                 for (int u = 0; u < nsub; ++u) {
@@ -656,13 +662,14 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     const bool ok = c0u + m < p.d;
                     float v;
                     if (AGG || pc.k0 == 0) {
-                        v = (p.init_state && ok) ? p.init_state[row * p.d + c0u + m] : 0.f;
-                        if (pc.k0 == 0 && p.chunk_states && ok) p.chunk_states[(row * p.n_chunks) * p.d + c0u + m] = v;
+                        v = (p.init_state && ok) ? *EMA_AT(p, p.init_state + row * p.d + c0u + m, 106) : 0.f;
+                        if (pc.k0 == 0 && p.chunk_states && ok)
+                            *EMA_AT(p, p.chunk_states + (row * p.n_chunks) * p.d + c0u + m, 107) = v;
                         if (AGG && pc.k0 > 0 && ok)
                             v = fold_state_before(p.agg_vec + row * p.n_tiles * p.d + c0u + m,
-                                                  p.agg_fac + row * p.n_tiles, p.d, pc.k0, v);
+                                                  p.agg_fac + row * p.n_tiles, p.d, pc.k0, v, BoundsRef{p.bounds});
                     } else {
-                        v = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x) * kCarryFloats + u * DT + m);
+                        v = __ldcg(EMA_AT(p, p.carry + static_cast<int64_t>(blockIdx.x) * kCarryFloats + u * DT + m, 108));
                     }
                     h_sm[((it + u) & (kFwdHRing - 1)) * DT + m] = v;
                     if (u == 0) h_reg0 = v; else h_reg1 = v;
@@ -672,10 +679,10 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             if (AGG ? (loader && lane == 0) : (m == QT - 1))
                 for (int u = 0; u < nsub; ++u) mbar_arrive(bar(B_H + ((it + u) & (kFwdHRing - 1))));
             if (AGG && loader && pc.k0 + 1 < pc.k1) {   // aggregates of the piece's first tile
-                agg_p = __ldg(p.agg_fac + row * p.n_tiles + pc.k0);
+                agg_p = __ldg(EMA_AT(p, p.agg_fac + row * p.n_tiles + pc.k0, 109));
                 const float *av = p.agg_vec + (row * p.n_tiles + pc.k0) * p.d + dt0 * DT + m;
-                agg_s0 = (dt0 * DT + m < p.d) ? __ldg(av) : 0.f;
-                agg_s1 = (nsub > 1 && (dt0 + 1) * DT + m < p.d) ? __ldg(av + DT) : 0.f;
+                agg_s0 = (dt0 * DT + m < p.d) ? __ldg(EMA_AT(p, av, 110)) : 0.f;
+                agg_s1 = (nsub > 1 && (dt0 + 1) * DT + m < p.d) ? __ldg(EMA_AT(p, av + DT, 111)) : 0.f;
             }
             for (int k = pc.k0; k < pc.k1; ++k)
             for (int u = 0; u < nsub; ++u, ++it) {
@@ -688,7 +695,8 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 float out_w = 1.f;   // fetched before the wait, used after the side outputs
                 if (WEIGHTED && p.out_weight) {
                     const int tw = k * QT + m;
-                    out_w = tw < L ? p.out_weight[(row / p.h) * p.a_sb + static_cast<int64_t>(tw) * p.a_sl + hi * p.a_sh] : 0.f;
+                    out_w = tw < L ? *EMA_AT(p, p.out_weight + (row / p.h) * p.a_sb + static_cast<int64_t>(tw) * p.a_sl + hi * p.a_sh, 112)
+                                   : 0.f;
                 }
                 if (AGG && loader && k + 1 < pc.k1) {   // the state entering this channel tile's next tile
                     const float hn = fmaf(agg_p, u == 0 ? h_reg0 : h_reg1, u == 0 ? agg_s0 : agg_s1);
@@ -699,9 +707,9 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     // the next tile's aggregates: a whole tile's time to arrive
                     if (k + 2 < pc.k1) {
                         const float *an = p.agg_vec + (row * p.n_tiles + k + 1) * p.d + c0 + m;
-                        if (ch_ok && u == 0) agg_s0 = __ldg(an);
-                        if (ch_ok && u != 0) agg_s1 = __ldg(an);
-                        if (u == nsub - 1) agg_p = __ldg(p.agg_fac + row * p.n_tiles + k + 1);
+                        if (ch_ok && u == 0) agg_s0 = __ldg(EMA_AT(p, an, 113));
+                        if (ch_ok && u != 0) agg_s1 = __ldg(EMA_AT(p, an, 114));
+                        if (u == nsub - 1) agg_p = __ldg(EMA_AT(p, p.agg_fac + row * p.n_tiles + k + 1, 115));
                     }
                 }
                 if (lane == 0) mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 5);  // one poller per warp
@@ -753,13 +761,14 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         for (int c = 0; c < 32; ++c) tmp[c] = y[c];
                         const int n_valid = static_cast<int>(p.d) - (c0 + cb);
                         if (at_chunk_end)
-                            store_row32(p.chunk_states + (row * p.n_chunks + (t + 1) / p.chunk) * p.d + c0 + cb, tmp, n_valid);
-                        if (at_last_step) store_row32(p.final_state + row * p.d + c0 + cb, tmp, n_valid);
+                            store_row32(p.chunk_states + (row * p.n_chunks + (t + 1) / p.chunk) * p.d + c0 + cb, tmp, n_valid,
+                                        BoundsRef{p.bounds});
+                        if (at_last_step) store_row32(p.final_state + row * p.d + c0 + cb, tmp, n_valid, BoundsRef{p.bounds});
                         if (at_cut) {
-                            store_row32(carry_out + u * DT + cb, tmp, 32);
+                            store_row32(carry_out + u * DT + cb, tmp, 32, BoundsRef{p.bounds});
                             if (pass == 1) {   // this half of the carry is complete
                                 __threadfence();
-                                atomicAdd(p.flags + blockIdx.x + 1, 1u);
+                                atomicAdd(EMA_AT(p, p.flags + blockIdx.x + 1, 116), 1u);
                             }
                         }
                     }
@@ -780,7 +789,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     }
                 }
                 // state entering the tile -> saved state k, one coalesced line per 32 threads
-                if (ts_item && ch_ok) ts_item[static_cast<int64_t>(k) * p.d + m] = hin[m];
+                if (ts_item && ch_ok) *EMA_AT(p, ts_item + static_cast<int64_t>(k) * p.d + m, 117) = hin[m];
                 fence_proxy_async();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(B_STAGED + s));
@@ -832,38 +841,41 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const int64_t bi = row / p.h, hi = row % p.h;
             const float *arow = p.decay + (per_step ? bi * p.a_sb + hi * p.a_sh : hi * p.a_sh);
             if (!per_step) {
-                const float v = arow[0];
+                const float v = *EMA_AT(p, arow, 118);
                 if (static_cast<int>(hi) != cur_head) {
                     cur_head = static_cast<int>(hi);
                     build(log2_decay(v), conv ? 1.f : 1.f - v);
                 }
                 if (p.log_decay_sum && bt == 0 && dtile == 0)
-                    p.log_decay_sum[row] = static_cast<float>(L) * (conv ? v : logf(v));
+                    *EMA_AT(p, p.log_decay_sum + row, 119) = static_cast<float>(L) * (conv ? v : logf(v));
                 continue;
             }
             // per-step decay: the raw value of step r of the next tile is fetched one tile ahead
             float logsum = 0.f;
             const float ident = conv ? 0.f : 1.f;   // raw value of an identity step (past L)
-            float v_next = (row_owner && pc.k0 * QT + r < L) ? arow[static_cast<int64_t>(pc.k0 * QT + r) * p.a_sl] : ident;
+            float v_next = (row_owner && pc.k0 * QT + r < L) ? *EMA_AT(p, arow + static_cast<int64_t>(pc.k0 * QT + r) * p.a_sl, 120)
+                                                             : ident;
             // input weights (WEIGHTED only): same strides as the decay; free of branches on the pointer (without an
             // input-weight tensor the decay is simply read twice)
             const bool has_w = WEIGHTED && p.in_weight != nullptr;
             const float *wrow = (has_w ? p.in_weight : p.decay) + bi * p.a_sb + hi * p.a_sh;
             float w_next = 0.f;
             if constexpr (WEIGHTED)
-                w_next = (row_owner && pc.k0 * QT + r < L) ? wrow[static_cast<int64_t>(pc.k0 * QT + r) * p.a_sl] : 0.f;
+                w_next = (row_owner && pc.k0 * QT + r < L) ? *EMA_AT(p, wrow + static_cast<int64_t>(pc.k0 * QT + r) * p.a_sl, 121)
+                                                           : 0.f;
             for (int k = pc.k0; k < pc.k1; ++k) {
                 const float v = v_next, w = w_next;
                 if (k + 1 < pc.k1) {
                     const int t = (k + 1) * QT + r;
-                    v_next = (row_owner && t < L) ? arow[static_cast<int64_t>(t) * p.a_sl] : ident;
-                    if constexpr (WEIGHTED) w_next = (row_owner && t < L) ? wrow[static_cast<int64_t>(t) * p.a_sl] : 0.f;
+                    v_next = (row_owner && t < L) ? *EMA_AT(p, arow + static_cast<int64_t>(t) * p.a_sl, 122) : ident;
+                    if constexpr (WEIGHTED)
+                        w_next = (row_owner && t < L) ? *EMA_AT(p, wrow + static_cast<int64_t>(t) * p.a_sl, 123) : 0.f;
                 }
                 build(log2_decay(v), has_w ? w : (conv ? 1.f : 1.f - v));
                 // cs_sm[127] now holds log2 of the product of this tile's decays
                 if (p.log_decay_sum && bt == 0) logsum += cs_sm[QT - 1] * 0.6931471805599453f;
             }
-            if (p.log_decay_sum && bt == 0 && dtile == 0) p.log_decay_sum[row] = logsum;
+            if (p.log_decay_sum && bt == 0 && dtile == 0) *EMA_AT(p, p.log_decay_sum + row, 124) = logsum;
         }
     }
 
@@ -912,6 +924,7 @@ struct TcBwdParams {
     unsigned *flags;
     // aggregate schedule (split == 2): adjoint aggregates [rows, n_tiles, d] and products [rows, n_tiles]
     const float *agg_vec, *agg_fac;
+    BoundsTable *bounds;   // bounds-checking build only
 };
 
 constexpr int kBwdStages = 2;
@@ -1151,7 +1164,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             float g_reg0 = 0.f, g_reg1 = 0.f;   // AGG: the adjoint entering the current tile, channel m of each sub-tile (loaders)
             if (loader) {
                 if (!AGG && pc.k1 < p.n_tiles) {   // left part of a cut item: the adjoint comes from the CTA that made the right part
-                    if (lane == 0) wait_carry(p.flags + blockIdx.x + 1, 2u * nsub, abort_flag, 23);
+                    if (lane == 0) wait_carry(EMA_AT(p, p.flags + blockIdx.x + 1, 150), 2u * nsub, abort_flag, 23);
                     __syncwarp();
                 }
                 for (int u = 0; u < nsub; ++u) {
@@ -1159,15 +1172,16 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     const bool ok = c0u + m < p.d;
                     const int slot0 = (it + u) % kBwdCRing;
                     hs_sm[slot0 * DT + m] =
-                        ok ? p.tile_states[(row * p.n_tiles + (pc.k1 - 1)) * p.d + c0u + m] : 0.f;
+                        ok ? *EMA_AT(p, p.tile_states + (row * p.n_tiles + (pc.k1 - 1)) * p.d + c0u + m, 151) : 0.f;
                     float gv;
                     if (!AGG && pc.k1 < p.n_tiles) {
-                        gv = __ldcg(p.carry + static_cast<int64_t>(blockIdx.x + 1) * kCarryFloats + u * DT + m);
+                        gv = __ldcg(EMA_AT(p, p.carry + static_cast<int64_t>(blockIdx.x + 1) * kCarryFloats + u * DT + m, 152));
                     } else {
-                        gv = (p.dfinal_state && ok) ? p.dfinal_state[row * p.d + c0u + m] : 0.f;
+                        gv = (p.dfinal_state && ok) ? *EMA_AT(p, p.dfinal_state + row * p.d + c0u + m, 153) : 0.f;
                         if (AGG && pc.k1 < p.n_tiles && ok)
                             gv = fold_adjoint_after(p.agg_vec + row * p.n_tiles * p.d + c0u + m,
-                                                    p.agg_fac + row * p.n_tiles, p.d, pc.k1, p.n_tiles, gv);
+                                                    p.agg_fac + row * p.n_tiles, p.d, pc.k1, p.n_tiles, gv,
+                                                    BoundsRef{p.bounds});
                     }
                     g_sm[slot0 * DT + m] = gv;
                     if (u == 0) g_reg0 = gv; else g_reg1 = gv;
@@ -1195,12 +1209,12 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 const uint32_t aph = (it >> 1) & 1, gph = (it / kBwdCRing) & 1;
                 if (u == 0 && (per_step || hi != cur_head)) { cur_head = hi; ++mt; }
                 // prefetch the saved state of the next tile to the left while this one is being finished
-                if (loader && k > pc.k0) hs_next = ch_ok ? ts_item[static_cast<int64_t>(k - 1) * p.d] : 0.f;
+                if (loader && k > pc.k0) hs_next = ch_ok ? *EMA_AT(p, ts_item + static_cast<int64_t>(k - 1) * p.d, 154) : 0.f;
                 // AGG: this tile's adjoint aggregate, for the adjoint the tile on the left receives
                 float agg_g = 0.f, agg_f = 0.f;
                 if (AGG && loader && k > pc.k0) {
-                    agg_f = p.agg_fac[row * p.n_tiles + k];
-                    if (ch_ok) agg_g = p.agg_vec[(row * p.n_tiles + k) * p.d + c0 + m];
+                    agg_f = *EMA_AT(p, p.agg_fac + row * p.n_tiles + k, 155);
+                    if (ch_ok) agg_g = *EMA_AT(p, p.agg_vec + (row * p.n_tiles + k) * p.d + c0 + m, 156);
                 }
                 if (lane == 0) mbar_wait(bar(B_ACC_FULL + acc), aph, abort_flag, 15);
                 __syncwarp();
@@ -1260,16 +1274,17 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                             float *co = carry_out + u * DT + cb;
 #pragma unroll
                             for (int c = 0; c < 32; c += 4)
-                                *reinterpret_cast<float4 *>(co + c) = make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
+                                *reinterpret_cast<float4 *>(EMA_ATN(p, co + c, 157, 16)) =
+                                    make_float4(lam[c], lam[c + 1], lam[c + 2], lam[c + 3]);
                             if (pass == 1) {   // this half of the carry is complete
                                 __threadfence();
-                                atomicAdd(p.flags + blockIdx.x, 1u);
+                                atomicAdd(EMA_AT(p, p.flags + blockIdx.x, 158), 1u);
                             }
                         } else if (p.dinit_state && pc.k0 == 0) {
                             float *di = p.dinit_state + row * p.d + c0 + cb;
 #pragma unroll
                             for (int c = 0; c < 32; ++c)
-                                if (c0 + cb + c < p.d) di[c] = a_m * lam[c];
+                                if (c0 + cb + c < p.d) *EMA_AT(p, di + c, 159) = a_m * lam[c];
                         }
                     }
                     const float2 Ep2 = make_float2(Eprev, Eprev), p2 = make_float2(p_m, p_m);
@@ -1306,14 +1321,14 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 if (conv) dacc *= a_m;
                 if (t >= L) dacc = 0.f;
                 if (per_step) {
-                    if (t < L && slice_ok) dap_step[t] = dacc;
+                    if (t < L && slice_ok) *EMA_AT(p, dap_step + t, 160) = dacc;
                 } else {
                     float wsum = dacc;
 #pragma unroll
                     for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
                     if (lane == 0 && slice_ok) {   // four warps per slice fill its eight slots
-                        dap_head[k * 8 + q * 2] = wsum;
-                        dap_head[k * 8 + q * 2 + 1] = 0.f;
+                        *EMA_AT(p, dap_head + k * 8 + q * 2, 161) = wsum;
+                        *EMA_AT(p, dap_head + k * 8 + q * 2 + 1, 162) = 0.f;
                     }
                 }
                 fence_proxy_async();
@@ -1388,12 +1403,13 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             if (!per_step) {
                 if (static_cast<int>(hi) != cur_head) {
                     cur_head = static_cast<int>(hi);
-                    build(arow[0], arow[0]);
+                    const float v = *EMA_AT(p, arow, 163);
+                    build(v, v);
                 }
                 continue;
             }
             auto load_v = [&](int t) {
-                return (row_owner && t >= 0 && t < L) ? arow[static_cast<int64_t>(t) * p.a_sl] : ident;
+                return (row_owner && t >= 0 && t < L) ? *EMA_AT(p, arow + static_cast<int64_t>(t) * p.a_sl, 164) : ident;
             };
             float v_next = load_v((pc.k1 - 1) * QT + r);
             float edge_next = load_v(pc.k1 * QT);  // past the end (identity) unless the item continues in another CTA
@@ -1831,6 +1847,7 @@ int launch_fused_fwd_tc(const FusedParams &fp, cudaStream_t stream) {
     p.n_tiles = static_cast<int>((fp.L + tc::QT - 1) / tc::QT);
     p.n_dtiles = static_cast<int>((fp.d + tc::DT - 1) / tc::DT);
     p.n_chunks = fp.n_chunks;
+    p.bounds = fp.bounds;
     // the sum of the log decays is accumulated per item by one CTA: no cutting when it is asked for; the weighted
     // scan has no aggregate pass
     Plan pl;
@@ -1877,6 +1894,7 @@ int launch_fused_bwd_tc(const FusedParams &fp, cudaStream_t stream) {
     p.n_dtiles = static_cast<int>((fp.d + tc::DT - 1) / tc::DT);
     p.n_dt64 = static_cast<int>((fp.d + 63) / 64);
     p.head_partial_offset = kHeadPartialOffset(fp.b * fp.h);
+    p.bounds = fp.bounds;
     Plan pl;
     rc = make_plan(fp, true, true, stream, &pl);
     if (rc) return rc;

@@ -6,11 +6,6 @@
 
 namespace ema {
 
-template <typename T, int VEC>
-__device__ __forceinline__ raw_t<T, VEC> load_or_zero(const T *p, bool ok) {
-    return ok ? ld_stream<T, VEC>(p) : raw_zero<T, VEC>();
-}
-
 // x tiles through registers: tile k + 1 is loaded while tile k computes
 template <typename T, int VEC>
 struct RegisterFeed {
@@ -20,15 +15,18 @@ struct RegisterFeed {
     int64_t x_sl;
     int sub, L;
     bool c_ok;
+    BoundsTable *bounds;
     __device__ __forceinline__ void load(R (&dst)[kFmaSB], int t0) {
 #pragma unroll
         for (int s = 0; s < kFmaSB; ++s) {
             const int t = t0 + s;
-            dst[s] = load_or_zero<T, VEC>(xrow + static_cast<int64_t>(t) * x_sl, c_ok && t < L);
+            const bool ok = c_ok && t < L;
+            dst[s] = ok ? ld_stream<T, VEC>(EMA_ATN(*this, xrow + static_cast<int64_t>(t) * x_sl, 1, sizeof(T) * VEC))
+                        : raw_zero<T, VEC>();
         }
     }
     __device__ __forceinline__ void init(const FusedParams &p, const T *xrow_, bool c_ok_, int sub_, int L_) {
-        xrow = xrow_; x_sl = p.x_sl; sub = sub_; L = L_; c_ok = c_ok_;
+        xrow = xrow_; x_sl = p.x_sl; sub = sub_; L = L_; c_ok = c_ok_; bounds = p.bounds;
         load(cur, sub * kFmaSB);
     }
     __device__ __forceinline__ void begin(int k, bool more) {
@@ -82,12 +80,13 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
     const T *xrow = static_cast<const T *>(p.x) + bi * p.x_sb + hi * p.x_sh + c0;
     T *yrow = static_cast<T *>(p.out) + bi * p.o_sb + hi * p.o_sh + c0;
     const float *arow = p.decay + (per_step ? bi * p.a_sb + hi * p.a_sh : hi * p.a_sh);
-    const float a_head = per_step ? 1.f : (conv ? expf(arow[0]) : arow[0]);
+    const float a_head_raw = per_step ? 0.f : *EMA_AT(p, arow, 2);
+    const float a_head = per_step ? 1.f : (conv ? expf(a_head_raw) : a_head_raw);
 
     auto load_a = [&](int t) -> float {  // multiplicative decay of step t (identity past the end)
         if (t >= L) return 1.f;
         if (!per_step) return a_head;
-        const float v = arow[static_cast<int64_t>(t) * p.a_sl];
+        const float v = *EMA_AT(p, arow + static_cast<int64_t>(t) * p.a_sl, 3);
         return conv ? expf(v) : v;
     };
     // per-step weights share the decay's strides (weighted calls always have a per-step decay); a missing output
@@ -95,18 +94,18 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
     const int64_t w_off = bi * p.a_sb + hi * p.a_sh;
     auto load_w = [&](const float *w, int t) -> float {
         if (!w) return 1.f;
-        return t < L ? w[w_off + static_cast<int64_t>(t) * p.a_sl] : 0.f;
+        return t < L ? *EMA_AT(p, w + w_off + static_cast<int64_t>(t) * p.a_sl, 4) : 0.f;
     };
     auto load_in_w = [&](int t) -> float {
         if (p.in_weight) return load_w(p.in_weight, t);
         if (t >= L) return 0.f;
-        return conv ? 1.f : 1.f - arow[static_cast<int64_t>(t) * p.a_sl];
+        return conv ? 1.f : 1.f - *EMA_AT(p, arow + static_cast<int64_t>(t) * p.a_sl, 5);
     };
 
     float h[VEC];
 #pragma unroll
     for (int v = 0; v < VEC; ++v)
-        h[v] = (p.init_state && c_ok) ? p.init_state[row * p.d + c0 + v] : 0.f;
+        h[v] = (p.init_state && c_ok) ? *EMA_AT(p, p.init_state + row * p.d + c0 + v, 6) : 0.f;
     if (sub == 0) {
 #pragma unroll
         for (int v = 0; v < VEC; ++v) h_sm[0][lc * VEC + v] = h[v];
@@ -178,12 +177,12 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
             if (p.tile_states) {
                 float *ts = p.tile_states + (row * p.n_tiles + k) * p.d + c0;
 #pragma unroll
-                for (int v = 0; v < VEC; ++v) ts[v] = h[v];
+                for (int v = 0; v < VEC; ++v) *EMA_AT(p, ts + v, 7) = h[v];
             }
             if (k == 0 && p.chunk_states) {
                 float *cs = p.chunk_states + (row * p.n_chunks) * p.d + c0;
 #pragma unroll
-                for (int v = 0; v < VEC; ++v) cs[v] = h[v];
+                for (int v = 0; v < VEC; ++v) *EMA_AT(p, cs + v, 8) = h[v];
             }
         }
         for (int i = 0; i < sub; ++i) {
@@ -213,17 +212,20 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
                         float ys[VEC];
 #pragma unroll
                         for (int v = 0; v < VEC; ++v) ys[v] = cw * h[v];
-                        st_stream<T, VEC>(yrow + static_cast<int64_t>(t) * p.o_sl, pack<T, VEC>(ys));
+                        st_stream<T, VEC>(EMA_ATN(p, yrow + static_cast<int64_t>(t) * p.o_sl, 9, sizeof(T) * VEC),
+                                          pack<T, VEC>(ys));
                     }
                 } else {
-                    if (p.out) st_stream<T, VEC>(yrow + static_cast<int64_t>(t) * p.o_sl, pack<T, VEC>(h));
+                    if (p.out)
+                        st_stream<T, VEC>(EMA_ATN(p, yrow + static_cast<int64_t>(t) * p.o_sl, 10, sizeof(T) * VEC),
+                                          pack<T, VEC>(h));
                 }
                 if (p.chunk_states) {
                     // y_t is the state at the start of chunk (t+1)/chunk when t+1 is a boundary
                     if (c_rem == 0 && t + 1 < L) {
                         float *cs = p.chunk_states + (row * p.n_chunks + c_idx) * p.d + c0;
 #pragma unroll
-                        for (int v = 0; v < VEC; ++v) cs[v] = h[v];
+                        for (int v = 0; v < VEC; ++v) *EMA_AT(p, cs + v, 11) = h[v];
                     }
                 }
             }
@@ -254,9 +256,9 @@ __device__ __forceinline__ void ema_fwd_fma_body(const FusedParams &p, FEED &fee
     // h of the last sub-block is the state after the last processed step (steps past L are identity)
     if (sub == NS - 1 && c_ok && p.final_state) {
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) p.final_state[row * p.d + c0 + v] = h[v];
+        for (int v = 0; v < VEC; ++v) *EMA_AT(p, p.final_state + row * p.d + c0 + v, 12) = h[v];
     }
-    if (p.log_decay_sum && tid == 0 && dtile == 0) p.log_decay_sum[row] = logsum;
+    if (p.log_decay_sum && tid == 0 && dtile == 0) *EMA_AT(p, p.log_decay_sum + row, 13) = logsum;
 }
 
 }  // namespace ema

@@ -37,6 +37,7 @@ struct AggParams {
     int64_t a_sb, a_sl, a_sh;
     int decay_mode, convention;
     int n_tiles, n_cgroups;
+    BoundsTable *bounds;   // bounds-checking build only
 };
 
 __device__ __forceinline__ float ex2f(float x) {
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(kAggThreads) tile_aggregate_kernel(const AggPa
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const int64_t t = t0 + warp + kAggGroups * i;
-            raw[i] = __ldg(reinterpret_cast<const uint4 *>(base + (t < p.L ? t : t_last) * p.sl));
+            raw[i] = __ldg(reinterpret_cast<const uint4 *>(EMA_ATN(p, base + (t < p.L ? t : t_last) * p.sl, 200, 16)));
         }
     }
 
@@ -85,7 +86,7 @@ __global__ void __launch_bounds__(kAggThreads) tile_aggregate_kernel(const AggPa
     float v = ident, cs = 0.f;
     if (tid < kAggSteps) {
         const int64_t t = t0 + tid;
-        if (t < p.L) v = per_step ? arow[t * p.a_sl] : arow[0];
+        if (t < p.L) v = *EMA_AT(p, per_step ? arow + t * p.a_sl : arow, 201);
         cs = log2_decay(v);
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -115,10 +116,10 @@ __global__ void __launch_bounds__(kAggThreads) tile_aggregate_kernel(const AggPa
                 // the step after the tile (identity past L) closes the product handed to the tile on the left
                 const int64_t te = t0 + kAggSteps;
                 float ve = ident;
-                if (te < p.L) ve = per_step ? arow[te * p.a_sl] : arow[0];
+                if (te < p.L) ve = *EMA_AT(p, per_step ? arow + te * p.a_sl : arow, 202);
                 f = total - first + log2_decay(ve);
             }
-            p.fac[row * p.n_tiles + k] = ex2f(f);
+            *EMA_AT(p, p.fac + row * p.n_tiles + k, 203) = ex2f(f);
         }
     }
     __syncthreads();
@@ -147,7 +148,7 @@ __global__ void __launch_bounds__(kAggThreads) tile_aggregate_kernel(const AggPa
         float s = 0.f;
 #pragma unroll
         for (int g = 0; g < kAggGroups; ++g) s += red[g][tid];
-        p.vec[(row * p.n_tiles + k) * p.d + cc] = s;
+        *EMA_AT(p, p.vec + (row * p.n_tiles + k) * p.d + cc, 204) = s;
     }
 }
 
@@ -172,6 +173,7 @@ int launch_tile_aggregates(const FusedParams &fp, int adjoint, float *buf, cudaS
     p.b = fp.b; p.L = fp.L; p.h = fp.h; p.d = fp.d;
     p.a_sb = fp.a_sb; p.a_sl = fp.a_sl; p.a_sh = fp.a_sh;
     p.decay_mode = fp.decay_mode; p.convention = fp.convention;
+    p.bounds = fp.bounds;
     const int64_t blocks = rows * p.n_tiles * p.n_cgroups;
     if (blocks <= 0) return EMA_OK;
     if (blocks >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;

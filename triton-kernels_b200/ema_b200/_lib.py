@@ -53,6 +53,9 @@ def lib():
         "ema_b200_error_string": (ctypes.c_char_p, [ci]),
         "ema_b200_device_status": (ci, [ci]),
         "ema_b200_selftest_wait": (ci, [ci, ci, vp, vp]),
+        "ema_b200_bounds_checked": (ci, []),
+        "ema_b200_bounds_status": (ci, [ci]),
+        "ema_b200_bounds_shrink_next": (ci, [sz]),
         "ema_b200_set_path": (ci, [ci]),
         "ema_b200_last_path": (ci, []),
         "ema_b200_last_schedule": (ci, []),
