@@ -811,7 +811,7 @@ def run_gpu(args):
         except Exception as exc:  # the C oracle is optional context, never the measured product
             cpu_baseline["c_oracle_error"] = str(exc)[:120]
 
-    launches_per_step = 1 if fwd_only else (4 if per_head else 3)
+    launches_per_step = 1 if fwd_only else 3   # forward scan, backward scan, decay-gradient reduction
     if schedule == 2:
         launches_per_step += 1 if fwd_only else 2   # the aggregate passes over x and dy
     line = {

@@ -125,6 +125,10 @@ __device__ __forceinline__ void ema_bwd_fma_body(const FusedParams &p, FEED &fee
     const bool per_step = p.decay_mode == EMA_DECAY_PER_STEP;
     const int n_tiles = p.n_tiles;
 
+    // arrival counter of the per-head reduction that follows this kernel (see kHeadCounterIndex)
+    if (!per_step && blk == 0 && tid == 0)
+        *reinterpret_cast<unsigned *>(EMA_AT(p, p.da_partial + kHeadCounterIndex(p.b * p.h), 67)) = 0u;
+
     const T *xrow = static_cast<const T *>(p.x) + bi * p.x_sb + hi * p.x_sh + c0;
     const T *grow = static_cast<const T *>(p.dy) + bi * p.g_sb + hi * p.g_sh + c0;
     T *orow = static_cast<T *>(p.out) + bi * p.o_sb + hi * p.o_sh + c0;

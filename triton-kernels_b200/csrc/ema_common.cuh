@@ -162,9 +162,12 @@ constexpr int kFmaSB = 8;
 constexpr int kFmaNS = kFmaThreads / kFmaCT;
 constexpr int kFmaTile = kFmaNS * kFmaSB;  // 128 time steps per tile, like the tensor-core path
 
-// per-head decay gradient workspace: [rows doubles of row sums][partials], the partials starting
-// at this float offset (kept 16-byte aligned)
-__host__ __device__ inline int64_t kHeadPartialOffset(int64_t rows) { return ((rows * 2 + 3) / 4) * 4; }
+// per-head decay gradient workspace: [rows * kHeadRowSplit doubles of partial row sums][arrival counter, 3 floats of
+// padding][partials]: float index of the counter, and of the first partial (16-byte aligned).  The backward scan
+// kernels clear the counter (one thread, at their start), so that the caller's workspace needs no preparation.
+constexpr int kHeadRowSplit = 8;
+__host__ __device__ inline int64_t kHeadCounterIndex(int64_t rows) { return rows * 2 * kHeadRowSplit; }
+__host__ __device__ inline int64_t kHeadPartialOffset(int64_t rows) { return kHeadCounterIndex(rows) + 4; }
 
 int launch_fused_fwd_fma(const FusedParams &p, int dtype, int vec, cudaStream_t stream);
 int launch_fused_bwd_fma(const FusedParams &p, int dtype, int vec, cudaStream_t stream);

@@ -60,31 +60,42 @@ __global__ void da_reduce_steps_kernel(const float *__restrict__ part, float *__
     *EMA_AT(br, ddecay + (row / h) * a_sb + t * a_sl + (row % h) * a_sh, 221) = s;
 }
 
-// per-head decay, level 1: one CTA per scan row sums that row's partials (channel tiles x time
-// tiles x warps) in a fixed order
-__global__ void da_reduce_rows_kernel(const float *__restrict__ part, double *__restrict__ row_sum,
-                                      int64_t per_row, BoundsRef br) {
+// Per-head decay, one launch.  Thread block (row, s) sums the s-th of `split` equal parts of that scan row's partials
+// (channel tiles x time tiles x warps) in a fixed order and leaves the sum in sub_sum[row * split + s]; the block that
+// arrives last (a counter the backward scan kernel cleared) then adds the sub-sums of every head over the batch, again
+// in a fixed order, so that the result does not depend on which block that was.
+__global__ void da_reduce_head_kernel(const float *__restrict__ part, double *sub_sum, unsigned *counter,
+                                      float *__restrict__ ddecay, int64_t per_row, int split, int64_t b, int64_t h,
+                                      int64_t a_sh, BoundsRef br) {
     __shared__ double red[256];
-    const float *src = part + static_cast<int64_t>(blockIdx.x) * per_row;
-    double s = 0.0;
-    for (int64_t i = threadIdx.x; i < per_row; i += blockDim.x) s += static_cast<double>(*EMA_AT(br, src + i, 222));
-    red[threadIdx.x] = s;
+    __shared__ bool last;
+    const int64_t row = blockIdx.x / split;
+    const int s = static_cast<int>(blockIdx.x % split);
+    const int64_t part_len = (per_row + split - 1) / split;
+    const int64_t i0 = s * part_len, i1 = i0 + part_len < per_row ? i0 + part_len : per_row;
+    const float *src = part + row * per_row;
+    double acc = 0.0;
+    for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) acc += static_cast<double>(*EMA_AT(br, src + i, 222));
+    red[threadIdx.x] = acc;
     __syncthreads();
     for (int o = 128; o > 0; o >>= 1) {
         if (static_cast<int>(threadIdx.x) < o) red[threadIdx.x] += red[threadIdx.x + o];
         __syncthreads();
     }
-    if (threadIdx.x == 0) *EMA_AT(br, row_sum + blockIdx.x, 223) = red[0];
-}
-
-// level 2: ddecay[h] = sum over the batch of the row sums
-__global__ void da_reduce_head_kernel(const double *__restrict__ row_sum, float *__restrict__ ddecay,
-                                      int64_t b, int64_t h, int64_t a_sh, BoundsRef br) {
-    const int64_t hi = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (hi >= h) return;
-    double s = 0.0;
-    for (int64_t bi = 0; bi < b; ++bi) s += *EMA_AT(br, row_sum + bi * h + hi, 224);
-    *EMA_AT(br, ddecay + hi * a_sh, 225) = static_cast<float>(s);
+    if (threadIdx.x == 0) {
+        *EMA_AT(br, sub_sum + blockIdx.x, 223) = red[0];
+        __threadfence();   // the sub-sum is visible before the arrival is
+        last = atomicAdd(EMA_AT(br, counter, 226), 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    for (int64_t hi = threadIdx.x; hi < h; hi += blockDim.x) {
+        double sum = 0.0;
+        for (int64_t bi = 0; bi < b; ++bi)
+            for (int j = 0; j < split; ++j) sum += __ldcg(EMA_AT(br, sub_sum + (bi * h + hi) * split + j, 224));
+        *EMA_AT(br, ddecay + hi * a_sh, 225) = static_cast<float>(sum);
+    }
 }
 
 template <typename T, int VEC>
@@ -139,11 +150,14 @@ int launch_da_reduce(const FusedParams &p, float *ddecay, int tile_steps, cudaSt
             p.da_partial, ddecay, rows, p.h, p.L, L_pad, p.n_dtiles, p.a_sb, p.a_sl, p.a_sh, BoundsRef{p.bounds});
     } else {
         const int64_t per_row = static_cast<int64_t>(p.n_dtiles) * p.n_tiles * (kFmaThreads / 32);
-        double *row_sum = reinterpret_cast<double *>(p.da_partial);
-        da_reduce_rows_kernel<<<static_cast<unsigned>(rows), 256, 0, stream>>>(
-            p.da_partial + kHeadPartialOffset(rows), row_sum, per_row, BoundsRef{p.bounds});
-        da_reduce_head_kernel<<<static_cast<unsigned>((p.h + 127) / 128), 128, 0, stream>>>(
-            row_sum, ddecay, p.b, p.h, p.a_sh, BoundsRef{p.bounds});
+        // enough thread blocks to have the partials' loads in flight at once, at least 2048 floats each
+        int64_t split = per_row / 2048;
+        split = split < 1 ? 1 : (split > kHeadRowSplit ? kHeadRowSplit : split);
+        double *sub_sum = reinterpret_cast<double *>(p.da_partial);
+        unsigned *counter = reinterpret_cast<unsigned *>(p.da_partial + kHeadCounterIndex(rows));
+        da_reduce_head_kernel<<<static_cast<unsigned>(rows * split), 256, 0, stream>>>(
+            p.da_partial + kHeadPartialOffset(rows), sub_sum, counter, ddecay, per_row, static_cast<int>(split), p.b, p.h,
+            p.a_sh, BoundsRef{p.bounds});
     }
     return check_launch();
 }

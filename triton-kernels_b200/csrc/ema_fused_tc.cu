@@ -1028,6 +1028,9 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    // arrival counter of the per-head reduction that follows this kernel (it sits right before the partial sums)
+    if (!per_step && blockIdx.x == 0 && tid == 0)
+        *reinterpret_cast<unsigned *>(EMA_AT(p, p.da_partial + p.head_partial_offset - 4, 165)) = 0u;
     const Sched sched(p.n_items, p.n_tiles, p.split != 0);
     // item -> scan row, first channel tile, number of channel tiles (1 or 2)
     auto item_row = [&](int64_t item) { return item / p.n_groups; };

@@ -138,7 +138,7 @@ class HostPipeline:
                             workspace=self.fwd_workspace[slot])
                 ops.ema_bwd(xs, a_i, dys, ts, dx=dxs, ddecay=da_i, workspace=self.workspace[slot],
                             prescaled_log=self.prescaled_log)
-                launches += 4 if self.per_head else 3
+                launches += 3   # forward scan, backward scan, decay-gradient reduction
                 self.ev_comp[slot].record(self.s_comp)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(self.ev_comp[slot])
