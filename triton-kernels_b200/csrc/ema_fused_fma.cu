@@ -90,11 +90,31 @@ __global__ void da_reduce_head_kernel(const float *__restrict__ part, double *su
     __syncthreads();
     if (!last) return;
     __threadfence();
-    for (int64_t hi = threadIdx.x; hi < h; hi += blockDim.x) {
+    const int64_t per_head = b * split;   // sub-sums per head
+    if (h >= 64) {
+        // many heads: a thread per head, its sub-sums in order (the threads' loads overlap one another)
+        for (int64_t hi = threadIdx.x; hi < h; hi += blockDim.x) {
+            double sum = 0.0;
+            for (int64_t i = 0; i < per_head; ++i)
+                sum += __ldcg(EMA_AT(br, sub_sum + ((i / split) * h + hi) * split + i % split, 224));
+            *EMA_AT(br, ddecay + hi * a_sh, 225) = static_cast<float>(sum);
+        }
+        return;
+    }
+    // few heads: the whole block on one head at a time - thread t takes the sub-sums t, t + 256, ... in order, then the
+    // same tree as above; a single thread walking the list would pay an L2 round trip per element
+    for (int64_t hi = 0; hi < h; ++hi) {
         double sum = 0.0;
-        for (int64_t bi = 0; bi < b; ++bi)
-            for (int j = 0; j < split; ++j) sum += __ldcg(EMA_AT(br, sub_sum + (bi * h + hi) * split + j, 224));
-        *EMA_AT(br, ddecay + hi * a_sh, 225) = static_cast<float>(sum);
+        for (int64_t i = threadIdx.x; i < per_head; i += blockDim.x)
+            sum += __ldcg(EMA_AT(br, sub_sum + ((i / split) * h + hi) * split + i % split, 227));
+        __syncthreads();   // the previous head's tree has been read
+        red[threadIdx.x] = sum;
+        __syncthreads();
+        for (int o = 128; o > 0; o >>= 1) {
+            if (static_cast<int>(threadIdx.x) < o) red[threadIdx.x] += red[threadIdx.x + o];
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) *EMA_AT(br, ddecay + hi * a_sh, 228) = static_cast<float>(red[0]);
     }
 }
 
