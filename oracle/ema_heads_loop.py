@@ -27,8 +27,13 @@ def processed_dt(dt, dt_bias=None, dt_softplus=False, dt_limit=(0.0, float("inf"
 
 
 def heads_loop(x, dt, A, B, C, D=None, z=None, dt_bias=None, initial_states=None, dt_softplus=False,
-               dt_limit=(0.0, float("inf")), seq_idx=None):
-    """x[b,L,h,p], dt[b,L,h], A[h], B/C[b,L,g,1] -> (out[b,L,h,p], final_states[b,h,p,1]) in float64."""
+               dt_limit=(0.0, float("inf")), seq_idx=None, cu_seqlens=None, chunk_size=None):
+    """x[b,L,h,p], dt[b,L,h], A[h], B/C[b,L,g,1] -> (out[b,L,h,p], final_states[b,h,p,1]) in float64.
+    With cu_seqlens (batch 1, packed sequences; seq_idx must mark the same boundaries) a third value: the state after
+    the last step of every sequence, [num_sequences, h, p, 1] (return_varlen_states of the reference,
+    kernels/ema_combined.py:56-62).  The reference adds the state entering the chunk that holds a sequence's end only
+    when the sequence starts before that chunk (kernels/ema_chunk_state.py:560-566): a first sequence that ends inside
+    the first chunk therefore comes out WITHOUT initial_states, and so it does here (chunk_size must then be given)."""
     b, L, h, p = x.shape
     rep = h // B.shape[2]
     d = processed_dt(dt, dt_bias, dt_softplus, dt_limit)
@@ -37,17 +42,30 @@ def heads_loop(x, dt, A, B, C, D=None, z=None, dt_bias=None, initial_states=None
     xs = x.astype(np.float64)
     s = np.zeros((b, h, p)) if initial_states is None else initial_states[..., 0].astype(np.float64).copy()
     out = np.empty((b, L, h, p))
+    ends = {} if cu_seqlens is None else {int(e) - 1: i for i, e in enumerate(np.asarray(cu_seqlens)[1:])}
+    varlen = np.zeros((len(ends), h, p))
+    s_init = s.copy()   # what is left of initial_states alone
     for t in range(L):
         if seq_idx is not None and t > 0:
-            s = s * (seq_idx[:, t] == seq_idx[:, t - 1]).astype(np.float64).reshape(b, 1, 1)
-        s = np.exp(d[:, t] * A.astype(np.float64))[..., None] * s + (d[:, t] * Bh[:, t])[..., None] * xs[:, t]
+            same = (seq_idx[:, t] == seq_idx[:, t - 1]).astype(np.float64).reshape(b, 1, 1)
+            s, s_init = s * same, s_init * same
+        a_t = np.exp(d[:, t] * A.astype(np.float64))[..., None]
+        s = a_t * s + (d[:, t] * Bh[:, t])[..., None] * xs[:, t]
+        s_init = a_t * s_init
         out[:, t] = Ch[:, t][..., None] * s
+        if t in ends:
+            varlen[ends[t]] = s[0]
+            if ends[t] == 0 and initial_states is not None and t // chunk_size == 0:
+                varlen[0] -= s_init[0]
     if D is not None:
         Dd = D.astype(np.float64)
         out = out + xs * (Dd[:, None] if Dd.ndim == 1 else Dd)
     if z is not None:
         zz = z.astype(np.float64)
         out = out * (zz / (1.0 + np.exp(-zz)))
+    if cu_seqlens is not None:
+        assert b == 1
+        return out, s[..., None], varlen[..., None]
     return out, s[..., None]
 
 

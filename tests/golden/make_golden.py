@@ -40,6 +40,7 @@ def main():
     ap.add_argument("--ref", default=os.environ.get("EMA_REFERENCE_CHECKOUT"), required=os.environ.get("EMA_REFERENCE_CHECKOUT") is None,
                     help="path of a checkout of the reference project (kartiksrinivas007/triton-kernels)")
     ap.add_argument("--out", default=os.path.dirname(os.path.abspath(__file__)))
+    ap.add_argument("--only", default=None, choices=[None, "heads_varlen"], help="record only this group of fixtures")
     args = ap.parse_args()
 
     os.environ["TRITON_INTERPRET"] = "1"
@@ -131,8 +132,10 @@ def main():
               "dx:", np.abs(cdx.numpy() - rec["loop_dX"]).max(),
               "out:", np.abs(o.numpy() - rec["loop_out"]).max())
 
-    def heads_case(name, seed, b, L, h, p, g, chunk, full, with_seq_idx=False):
-        """out and final_states of the reference's heads-style entry point for state size 1 and A = -1."""
+    def heads_case(name, seed, b, L, h, p, g, chunk, full, with_seq_idx=False, cu_seqlens=None):
+        """out and final_states of the reference's heads-style entry point for state size 1 and A = -1; with
+        cu_seqlens (batch 1: packed sequences, seq_idx derived from it) also the state at the end of every sequence
+        (return_varlen_states, kernels/ema_combined.py:56-62, kernels/ema_chunk_state.py:578)."""
         import kernels.ema_combined as ref_combined
         import kernels.ema_chunk_state as m1, kernels.ema_state_passing as m2, kernels.ema_bmm as m3, kernels.ema_chunk_scan as m4
         for mod in (m1, m2, m3, m4):
@@ -158,19 +161,37 @@ def main():
             sid[0, chunk:] += 1          # a restart exactly on a chunk boundary
             sid[1, L - 7:] = 5
             rec["seq_idx"] = sid
+        if cu_seqlens is not None:
+            assert b == 1 and cu_seqlens[0] == 0 and cu_seqlens[-1] == L
+            sid = np.zeros((1, L), np.int32)
+            for i in range(len(cu_seqlens) - 1):
+                sid[0, cu_seqlens[i]:cu_seqlens[i + 1]] = i
+            rec["seq_idx"] = sid
+            rec["cu_seqlens"] = np.asarray(cu_seqlens, np.int32)
         t = {k: torch.tensor(v) for k, v in rec.items()}
         with torch.no_grad():
-            out, fin = ref_combined.ema_chunk_scan_combined(
+            res = ref_combined.ema_chunk_scan_combined(
                 t["x"], t["dt"], t["A"], t["B"], t["C"], chunk, D=t.get("D"), z=t.get("z"), dt_bias=t.get("dt_bias"),
-                initial_states=t.get("initial_states"), seq_idx=t.get("seq_idx"), return_final_states=True, **kw)
+                initial_states=t.get("initial_states"), seq_idx=t.get("seq_idx"), cu_seqlens=t.get("cu_seqlens"),
+                return_final_states=True, return_varlen_states=cu_seqlens is not None, **kw)
+        out, fin = res[0], res[1]
+        if cu_seqlens is not None:
+            rec["varlen_states"] = res[2].numpy()
         rec.update(out=out.numpy(), final_states=fin.numpy(), meta=np.array([seed, b, L, h, p, g, chunk, int(full)]),
                    meta_A_is_minus_one=np.array([1]))
         np.savez(os.path.join(args.out, name + ".npz"), **rec)
         print(name, "done", float(np.abs(rec["out"]).max()))
 
+    if args.only == "heads_varlen":
+        # (added after the other fixtures were recorded: --only leaves those files untouched)
+        heads_case("heads_varlen", 24, 1, 120, 2, 16, 1, 32, full=False, cu_seqlens=[0, 37, 64, 101, 120])
+        heads_case("heads_varlen_full", 25, 1, 100, 4, 16, 2, 32, full=True, cu_seqlens=[0, 5, 70, 100])
+        return
     heads_case("heads_plain", 21, 2, 96, 2, 16, 1, 32, full=False)
     heads_case("heads_full", 22, 2, 100, 4, 16, 2, 32, full=True)
     heads_case("heads_seqidx", 23, 2, 90, 2, 16, 1, 32, full=False, with_seq_idx=True)
+    heads_case("heads_varlen", 24, 1, 120, 2, 16, 1, 32, full=False, cu_seqlens=[0, 37, 64, 101, 120])
+    heads_case("heads_varlen_full", 25, 1, 100, 4, 16, 2, 32, full=True, cu_seqlens=[0, 5, 70, 100])
     north_star_case("northstar_c1", 1235, 2, 256, 2, 64, 2.0, 6.0, per_head=False)
     north_star_case("northstar_perhead", 1237, 2, 192, 3, 32, 2.0, 6.0, per_head=True)
     north_star_case("northstar_ragged", 1241, 1, 77, 2, 24, 3.0, 8.0, per_head=False)

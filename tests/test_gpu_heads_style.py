@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from helpers import BF16_REL, FP32_ATOL
-from oracle.ema_heads_loop import heads_loop_torch
+from oracle.ema_heads_loop import heads_loop, heads_loop_torch
 
 
 @pytest.mark.gpu
@@ -148,7 +148,79 @@ def test_rejects_what_is_not_the_ema_case():
     with pytest.raises(NotImplementedError):
         ema_chunk_scan_combined(x, dt, A, B2, B2, 4)                       # state size 2
     B1 = torch.zeros(1, 8, 1, 1)
-    with pytest.raises(NotImplementedError):
-        ema_chunk_scan_combined(x, dt, A, B1, B1, 4, cu_seqlens=torch.tensor([0, 8]), return_varlen_states=True)
+    with pytest.raises(NotImplementedError):   # packed sequences without a seq_idx that restarts the state between them
+        ema_chunk_scan_combined(x, dt, A, B1, B1, 4, cu_seqlens=torch.tensor([0, 4, 8]), return_varlen_states=True)
+    with pytest.raises(AssertionError):         # varlen states need batch 1, as in the reference
+        ema_chunk_scan_combined(x.repeat(2, 1, 1, 1), dt.repeat(2, 1, 1), A, B1.repeat(2, 1, 1, 1), B1.repeat(2, 1, 1, 1), 4,
+                                cu_seqlens=torch.tensor([0, 8]), return_varlen_states=True)
     with pytest.raises(AssertionError):
         ema_chunk_scan_combined(x, dt[:, :4], A, B1, B1, 4)               # dt of the wrong length
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["heads_varlen", "heads_varlen_full"])
+@pytest.mark.parametrize("grad", [False, True])
+def test_varlen_states_match_the_reference_fixture(name, grad, ema_lib, golden_dir):
+    """out, final_states and the state at the end of every packed sequence equal what the reference's entry point
+    returned with return_varlen_states=True (batch 1; kernels/ema_combined.py:56-62)."""
+    from kernels.ema_combined import ema_chunk_scan_combined
+    g = np.load(os.path.join(golden_dir, name + ".npz"))
+    chunk, full = int(g["meta"][6]), bool(g["meta"][7])
+    skip = ("out", "final_states", "varlen_states", "meta", "meta_A_is_minus_one")
+    t = {k: torch.tensor(g[k]).cuda() for k in g.files if k not in skip}
+    if grad:
+        t["x"].requires_grad_(True)
+    kw = dict(dt_softplus=True, dt_limit=(0.001, 2.0)) if full else {}
+    with torch.enable_grad() if grad else torch.no_grad():
+        out, fin, var = ema_chunk_scan_combined(
+            t["x"], t["dt"], t["A"], t["B"], t["C"], chunk, D=t.get("D"), z=t.get("z"), dt_bias=t.get("dt_bias"),
+            initial_states=t.get("initial_states"), seq_idx=t["seq_idx"], cu_seqlens=t["cu_seqlens"],
+            return_final_states=True, return_varlen_states=True, **kw)
+        out2, var2 = ema_chunk_scan_combined(
+            t["x"], t["dt"], t["A"], t["B"], t["C"], chunk, D=t.get("D"), z=t.get("z"), dt_bias=t.get("dt_bias"),
+            initial_states=t.get("initial_states"), seq_idx=t["seq_idx"], cu_seqlens=t["cu_seqlens"],
+            return_varlen_states=True, **kw)
+    assert torch.equal(out, out2) and torch.equal(var, var2)
+    assert var.shape == g["varlen_states"].shape and var.dtype == torch.float32
+    for got, ref, what in ((out, g["out"], "out"), (fin, g["final_states"], "final_states"),
+                           (var, g["varlen_states"], "varlen_states")):
+        err = float(np.abs(got.detach().float().cpu().numpy() - ref).max())
+        tol = FP32_ATOL + 2e-5 * float(np.abs(ref).max())
+        assert err <= tol, f"{name} {what}: {err:.3e} > {tol:.3e}"
+    if grad:   # forward only, as in the reference
+        with pytest.raises(AssertionError):
+            out.sum().backward()
+    assert ema_lib.ema_b200_device_status(1) == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("chunk", [64, 256])
+def test_varlen_states_on_long_packed_sequences(dtype, chunk, ema_lib):
+    """Sequences that end on a chunk boundary, one step long, longer than several chunks, and an initial state;
+    against the sequential loop."""
+    from kernels.ema_combined import ema_chunk_scan_combined
+    L, h, p, g = 1500, 4, 128, 2
+    cu = [0, 1, 64, 65, 256, 300, 1024, 1499, 1500]
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(1, L, h, p, generator=gen).to(dtype)
+    dt = torch.rand(1, L, h, generator=gen) * 0.2 + 0.01
+    A = -torch.rand(h, generator=gen) - 0.5
+    B = torch.rand(1, L, g, 1, generator=gen)
+    C = 0.5 + torch.rand(1, L, g, 1, generator=gen)
+    init = torch.randn(1, h, p, 1, generator=gen)
+    sid = torch.zeros(1, L, dtype=torch.int32)
+    for i in range(len(cu) - 1):
+        sid[0, cu[i]:cu[i + 1]] = i
+    cu_t = torch.tensor(cu, dtype=torch.int32)
+    with torch.no_grad():
+        out, fin, var = ema_chunk_scan_combined(x.cuda(), dt.cuda(), A.cuda(), B.cuda(), C.cuda(), chunk,
+                                                initial_states=init.cuda(), seq_idx=sid.cuda(), cu_seqlens=cu_t.cuda(),
+                                                return_final_states=True, return_varlen_states=True)
+    ref_out, ref_fin, ref_var = heads_loop(x.float().numpy(), dt.numpy(), A.numpy(), B.numpy(), C.numpy(),
+                                           initial_states=init.numpy(), seq_idx=sid.numpy(), cu_seqlens=cu, chunk_size=chunk)
+    rel = BF16_REL if dtype == torch.bfloat16 else 2e-5
+    for got, ref, what in ((out, ref_out, "out"), (fin, ref_fin, "final"), (var, ref_var, "varlen")):
+        err = float(np.abs(got.float().cpu().numpy() - ref).max())
+        assert err <= FP32_ATOL + rel * float(np.abs(ref).max()), f"{what}: {err:.3e}"
+    assert ema_lib.ema_b200_device_status(1) == 0

@@ -132,3 +132,21 @@ def test_heads_loop_matches_the_reference_entry_point(name, golden_dir):
                                     dt_bias=tt("dt_bias"), initial_states=tt("initial_states"), seq_idx=tt("seq_idx"), **kw)
     assert np.abs(out_t.numpy() - out).max() <= 1e-9 * max(scale, 1.0)
     assert np.abs(fin_t.numpy() - fin).max() <= 1e-9 * max(scale, 1.0)
+
+
+@pytest.mark.parametrize("name", ["heads_varlen", "heads_varlen_full"])
+def test_heads_loop_varlen_states_match_the_reference(name, golden_dir):
+    """The state at the end of every packed sequence (return_varlen_states, kernels/ema_combined.py:56-62 and
+    kernels/ema_chunk_state.py:578 of the reference), recorded from the reference's entry point with batch 1 and a
+    seq_idx that marks the same boundaries as cu_seqlens."""
+    from oracle.ema_heads_loop import heads_loop
+    g = np.load(os.path.join(golden_dir, name + ".npz"))
+    full = bool(g["meta"][7])
+    opt = lambda k: g[k] if k in g.files else None
+    kw = dict(dt_softplus=True, dt_limit=(0.001, 2.0)) if full else {}
+    out, fin, varlen = heads_loop(g["x"], g["dt"], g["A"], g["B"], g["C"], D=opt("D"), z=opt("z"), dt_bias=opt("dt_bias"),
+                                  initial_states=opt("initial_states"), seq_idx=g["seq_idx"], cu_seqlens=g["cu_seqlens"],
+                                  chunk_size=int(g["meta"][6]), **kw)
+    for got, ref in ((out, g["out"]), (fin, g["final_states"]), (varlen, g["varlen_states"])):
+        assert got.shape == ref.shape
+        assert np.abs(got - ref).max() <= 1e-5 * max(float(np.abs(ref).max()), 1.0)
