@@ -204,6 +204,23 @@ def cpu_reference_sample(b, L, h, d, steps, warmup):
     return b * L / sec, sec, torch.get_num_threads()
 
 
+SCHEDULES = {0: "whole work items (scan row x 128 channels) per thread block",
+             1: "tile ranges over the SMs, carries handed between thread blocks",
+             2: "per-tile aggregates, then pieces of items dealt evenly over the SMs"}
+
+
+def workload_config(W, schedule, tile_steps=128):
+    """The `config` object of a result line: the same for this library's arm and for the reference arm."""
+    b, L, h, d = W["b"], W["L"], W["h"], W["d"]
+    return {"workload": W["name"], "b_per_gpu": b, "L": L, "h": h, "d": d, "chunk": W["chunk"],
+            "tile_steps": tile_steps,
+            "sharding": "batch rows per rank, no data-path collective",
+            "decay": "per head [h]" if W["per_head"] else "per step [b, L, h]",
+            "schedule": SCHEDULES.get(schedule, "cuda cores"),
+            "l2": (f"tensors touched per step ({b * L * h * d * 2 * (2 if W['fwd_only'] else 4) / 2**20:.0f} MiB) exceed the "
+                   "126 MB L2; no flush needed")}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -216,10 +233,13 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD["name"], "sample": sample,
-                   "note": "the reference checkout does not travel to the GPU box: this is the port of its sequential "
-                           "loop (oracle/ema_loop_port.py, pinned against the reference's own loop by the test "
-                           "fixtures), on the host cores, the same whatever --gpus says"},
+        # this library's arm's config for the same workload (its kernels run the headline on whole work items); what the
+        # reference arm actually timed is in `sample`
+        "config": workload_config(WORKLOAD, 0),
+        "sample": sample,
+        "note": "the reference checkout does not travel to the GPU box: this is the port of its sequential loop "
+                "(oracle/ema_loop_port.py, pinned against the reference's own loop by the test fixtures), on the host "
+                "cores, the same whatever --gpus says",
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample,
                          "host_cpus": os.cpu_count()},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -818,16 +838,7 @@ def run_gpu(args):
         "metric": "ema_fwd_tokens_per_s" if fwd_only else METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16 in/out, f32 accumulate", "data": "synthetic",
-        "config": {"workload": W["name"], "b_per_gpu": b, "L": L, "h": h, "d": d, "chunk": W["chunk"],
-                   "tile_steps": ts,
-                   "sharding": "batch rows per rank, no data-path collective",
-                   "decay": "per head [h]" if per_head else "per step [b, L, h]",
-                   "schedule": {0: "whole work items (scan row x 128 channels) per thread block",
-                                1: "tile ranges over the SMs, carries handed between thread blocks",
-                                2: "per-tile aggregates, then pieces of items dealt evenly over the SMs"}.get(
-                                    schedule, "cuda cores"),
-                   "l2": (f"tensors touched per step ({b * L * h * d * 2 * (2 if fwd_only else 4) / 2**20:.0f} MiB) exceed the "
-                          "126 MB L2; no flush needed")},
+        "config": workload_config(W, schedule, ts),
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
         "gpu_launches": launches_per_step * K,
         "clocks": clocks,
