@@ -96,8 +96,8 @@ int ema_b200_device_status(int clear);
 int ema_b200_selftest_wait(int mode, int polls, const void *zero_word, void *stream);
 
 /* Bounds-checking build (test support; no counterpart in the reference).  A library built with -DEMA_BOUNDS_CHECK
- * (build.py --checked -> libema_b200_checked.so) routes every plain global-memory access of the fused kernels -
- * ema_b200_fwd, _fwd_weighted, _bwd, _bwd_weighted, _fold_records and everything they launch - through a check against
+ * (build.py --checked -> libema_b200_checked.so) routes every plain global-memory access of its kernels - the fused
+ * calls ema_b200_fwd, _fwd_weighted, _bwd, _bwd_weighted, _fold_records and the ten stage calls - through a check against
  * the address ranges of the call's own buffers, which the entry point derives from the shapes, strides and byte counts
  * it was given.  An access outside all of them is recorded (the first one only) and redirected to a sink inside the
  * library's table: nothing outside the buffers is read or written and nothing traps.  TMA copies are clipped by their

@@ -23,7 +23,7 @@ INNER = os.environ.get("EMA_B200_EXPECT_CHECKED") == "1"
 # (not the host pipeline: it keeps calls in flight on several streams, and the checker's table describes one call at a time)
 PARITY_FILES = ["tests/test_gpu_fused.py", "tests/test_gpu_tc.py", "tests/test_gpu_aggregates.py",
                 "tests/test_gpu_weighted.py", "tests/test_gpu_seqpar_single.py", "tests/test_gpu_fp32_tma.py",
-                "tests/test_gpu_guard_zones.py", "tests/test_gpu_fuzz.py", "tests/test_gpu_dropins.py",
+                "tests/test_gpu_guard_zones.py", "tests/test_gpu_fuzz.py", "tests/test_gpu_dropins.py", "tests/test_gpu_stages.py",
                 "tests/test_gpu_heads_style.py", "tests/test_gpu_bounds_build.py"]
 
 
@@ -93,3 +93,20 @@ def test_normal_build_reports_no_checker(ema_lib):
     assert ema_lib.ema_b200_bounds_checked() == 0
     assert ema_lib.ema_b200_bounds_status(1) == 0
     assert ema_lib.ema_b200_bounds_shrink_next(16) == -3   # EMA_ERR_UNSUPPORTED
+
+
+@pytest.mark.skipif(not INNER, reason="runs inside the run the outer test starts with the checking library")
+def test_stage_kernels_are_checked_too(ema_lib):
+    """A stage call whose output is registered 64 bytes short: the last stores of the cumulative sums are rejected
+    (site 321, the chunk-cumsum kernel's output pointer) and everything before them still arrives."""
+    from ema_b200 import stages
+    A = -torch.rand(2, 200, device="cuda")
+    ref = stages.chunk_cumsum(A, 64)
+    assert ema_lib.ema_b200_bounds_status(1) == 0
+    assert ema_lib.ema_b200_bounds_shrink_next(64) == 0
+    cut = stages.chunk_cumsum(A, 64)
+    status = ema_lib.ema_b200_bounds_status(1)
+    assert status == (0x400 | 321), hex(status)
+    assert torch.equal(cut.reshape(-1)[:-16], ref.reshape(-1)[:-16])
+    again = stages.chunk_cumsum(A, 64)
+    assert ema_lib.ema_b200_bounds_status(1) == 0 and torch.equal(again, ref)

@@ -44,6 +44,38 @@ __device__ __forceinline__ T *bounds_at(BoundsTable *tb, T *ptr, unsigned site, 
 #define EMA_ATN(p, ptr, site, bytes) (ptr)
 #endif
 
+// Pointer parameters of the stage kernels.  Normal build: a plain restrict-qualified pointer.  Checking build: a pointer
+// that carries the table and checks every dereference (p[i], *p) - derived pointers (p + n) keep the table; chk(p) gives
+// the raw pointer after checking sizeof(*p) bytes, chk_bytes(p, n) after checking n bytes (vector accesses).
+#ifdef EMA_BOUNDS_CHECK
+template <typename T>
+struct CheckedPtr {
+    T *p;
+    BoundsTable *tb;
+    unsigned site;
+    template <typename I>
+    __device__ __forceinline__ CheckedPtr operator+(I off) const { return CheckedPtr{p + off, tb, site}; }
+    template <typename I>
+    __device__ __forceinline__ T &operator[](I i) const { return *bounds_at(tb, p + i, site, static_cast<unsigned>(sizeof(T))); }
+    __device__ __forceinline__ T &operator*() const { return *bounds_at(tb, p, site, static_cast<unsigned>(sizeof(T))); }
+};
+template <typename T> using Ptr = CheckedPtr<T>;
+template <typename T>
+__device__ __forceinline__ T *chk(CheckedPtr<T> q) { return bounds_at(q.tb, q.p, q.site, static_cast<unsigned>(sizeof(T))); }
+template <typename T>
+__device__ __forceinline__ T *chk_bytes(CheckedPtr<T> q, unsigned bytes) { return bounds_at(q.tb, q.p, q.site, bytes); }
+template <typename T>
+inline Ptr<T> make_ptr(T *p, BoundsTable *tb, unsigned site) { return CheckedPtr<T>{p, tb, site}; }
+#else
+template <typename T> using Ptr = T *__restrict__;
+template <typename T>
+__device__ __forceinline__ T *chk(T *q) { return q; }
+template <typename T>
+__device__ __forceinline__ T *chk_bytes(T *q, unsigned) { return q; }
+template <typename T>
+inline T *make_ptr(T *p, BoundsTable *, unsigned) { return p; }
+#endif
+
 // host side (ema_api.cu): one (pointer, bytes) pair per buffer of the call
 struct BoundsRange {
     const void *ptr;
