@@ -11,6 +11,13 @@ namespace ema {
 
 static thread_local int g_last_cuda_error = 0;
 void set_last_cuda_error(cudaError_t e) { g_last_cuda_error = static_cast<int>(e); }
+bool overlapped_launches() {
+    static const bool on = [] {
+        const char *e = std::getenv("EMA_B200_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
 
 namespace {
 

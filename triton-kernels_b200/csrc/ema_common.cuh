@@ -144,8 +144,34 @@ __device__ __forceinline__ float decay_to_a(float v, int convention) {
     return convention == EMA_CONV_PRESCALED_LOG ? __expf(v) : v;
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------------
+// The scan, aggregate and reduction kernels are launched so that a kernel may be scheduled while the kernel before it
+// on the stream is still running (launch_overlapped below).  Such a kernel does its own set-up - barriers, tensor
+// memory, zero-filled shared memory - and then calls grid_dependency_wait() before it touches global memory: the wait
+// returns once the preceding kernel has finished and its writes are visible.  grid_dependents_launch() tells the
+// scheduler that the kernel after this one may be brought in as soon as SMs are free.  Launched the ordinary way both
+// calls do nothing.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- host side ------------------------------------------------------------------------------
 void set_last_cuda_error(cudaError_t e);
+bool overlapped_launches();   // EMA_B200_PDL=0 turns the overlap off (ema_api.cu)
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                     Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = overlapped_launches() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 inline int check_launch() {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {

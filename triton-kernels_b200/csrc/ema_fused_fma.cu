@@ -51,6 +51,8 @@ struct BoundsRef {   // what EMA_AT needs from a parameter block
 __global__ void da_reduce_steps_kernel(const float *__restrict__ part, float *__restrict__ ddecay,
                                        int64_t rows, int64_t h, int64_t L, int64_t L_pad,
                                        int n_dtiles, int64_t a_sb, int64_t a_sl, int64_t a_sh, BoundsRef br) {
+    grid_dependents_launch();   // (see ema_common.cuh)
+    grid_dependency_wait();
     const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (idx >= rows * L) return;
     const int64_t row = idx / L, t = idx % L;
@@ -69,6 +71,8 @@ __global__ void da_reduce_head_kernel(const float *__restrict__ part, double *su
                                       int64_t a_sh, BoundsRef br) {
     __shared__ double red[256];
     __shared__ bool last;
+    grid_dependents_launch();   // (see ema_common.cuh)
+    grid_dependency_wait();
     const int64_t row = blockIdx.x / split;
     const int s = static_cast<int>(blockIdx.x % split);
     const int64_t part_len = (per_row + split - 1) / split;
@@ -166,8 +170,10 @@ int launch_da_reduce(const FusedParams &p, float *ddecay, int tile_steps, cudaSt
         const int64_t n = rows * p.L;
         const int64_t L_pad = static_cast<int64_t>(p.n_tiles) * tile_steps;
         if ((n + 255) / 256 >= (1ll << 31)) return EMA_ERR_UNSUPPORTED;   // beyond one grid dimension
-        da_reduce_steps_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, stream>>>(
-            p.da_partial, ddecay, rows, p.h, p.L, L_pad, p.n_dtiles, p.a_sb, p.a_sl, p.a_sh, BoundsRef{p.bounds});
+        const cudaError_t e = launch_overlapped(da_reduce_steps_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0,
+                                                stream, p.da_partial, ddecay, rows, p.h, p.L, L_pad, p.n_dtiles, p.a_sb, p.a_sl,
+                                                p.a_sh, BoundsRef{p.bounds});
+        if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     } else {
         const int64_t per_row = static_cast<int64_t>(p.n_dtiles) * p.n_tiles * (kFmaThreads / 32);
         // enough thread blocks to have the partials' loads in flight at once, at least 2048 floats each
@@ -175,9 +181,10 @@ int launch_da_reduce(const FusedParams &p, float *ddecay, int tile_steps, cudaSt
         split = split < 1 ? 1 : (split > kHeadRowSplit ? kHeadRowSplit : split);
         double *sub_sum = reinterpret_cast<double *>(p.da_partial);
         unsigned *counter = reinterpret_cast<unsigned *>(p.da_partial + kHeadCounterIndex(rows));
-        da_reduce_head_kernel<<<static_cast<unsigned>(rows * split), 256, 0, stream>>>(
-            p.da_partial + kHeadPartialOffset(rows), sub_sum, counter, ddecay, per_row, static_cast<int>(split), p.b, p.h,
-            p.a_sh, BoundsRef{p.bounds});
+        const cudaError_t e = launch_overlapped(da_reduce_head_kernel, dim3(static_cast<unsigned>(rows * split)), dim3(256), 0,
+                                                stream, p.da_partial + kHeadPartialOffset(rows), sub_sum, counter, ddecay, per_row,
+                                                static_cast<int>(split), p.b, p.h, p.a_sh, BoundsRef{p.bounds});
+        if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     }
     return check_launch();
 }

@@ -517,6 +517,10 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up done: the next kernel on the stream may be scheduled; nothing before this line has touched global memory,
+    // everything after it may depend on the kernel before this one
+    grid_dependents_launch();
+    grid_dependency_wait();
 
     const Sched sched(p.n_items, p.n_tiles, p.split != 0);
     // item -> scan row, first channel tile, number of channel tiles (1 or 2)
@@ -1027,6 +1031,10 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up done: the next kernel on the stream may be scheduled; nothing before this line has touched global memory,
+    // everything after it may depend on the kernel before this one
+    grid_dependents_launch();
+    grid_dependency_wait();
 
     // arrival counter of the per-head reduction that follows this kernel (it sits right before the partial sums)
     if (!per_step && blockIdx.x == 0 && tid == 0)
@@ -1872,7 +1880,8 @@ int launch_fused_fwd_tc(const FusedParams &fp, cudaStream_t stream) {
                            : (pl.split == 2 ? tc::ema_fwd_tc_kernel<false, true> : tc::ema_fwd_tc_kernel<false, false>);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kFwdSmemBytes);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
-    kernel<<<grid, tc::kThreads, tc::kFwdSmemBytes, stream>>>(tm_x, tm_y, p);
+    e = launch_overlapped(kernel, dim3(grid), dim3(tc::kThreads), tc::kFwdSmemBytes, stream, tm_x, tm_y, p);
+    if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     return check_launch();
 }
 
@@ -1915,7 +1924,8 @@ int launch_fused_bwd_tc(const FusedParams &fp, cudaStream_t stream) {
     auto kernel = pl.split == 2 ? tc::ema_bwd_tc_kernel<true> : tc::ema_bwd_tc_kernel<false>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kBwdSmemBytes);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
-    kernel<<<grid, tc::kThreads, tc::kBwdSmemBytes, stream>>>(tm_x, tm_g, tm_o, p);
+    e = launch_overlapped(kernel, dim3(grid), dim3(tc::kThreads), tc::kBwdSmemBytes, stream, tm_x, tm_g, tm_o, p);
+    if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     return check_launch();
 }
 

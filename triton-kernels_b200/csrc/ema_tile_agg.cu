@@ -52,6 +52,8 @@ __global__ void __launch_bounds__(kAggThreads) tile_aggregate_kernel(const AggPa
     __shared__ float cs_sm[kAggSteps];
     __shared__ float warp_tot[4];
     __shared__ float red[kAggGroups][kAggChannels];
+    grid_dependents_launch();   // (see ema_common.cuh: this kernel may have been scheduled before its predecessor ended)
+    grid_dependency_wait();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t blk = blockIdx.x;
     const int cg = static_cast<int>(blk % p.n_cgroups);
@@ -180,11 +182,15 @@ int launch_tile_aggregates(const FusedParams &fp, int adjoint, float *buf, cudaS
     if (!adjoint) {
         p.src = static_cast<const __nv_bfloat16 *>(fp.x);
         p.sb = fp.x_sb; p.sl = fp.x_sl; p.sh = fp.x_sh;
-        tile_aggregate_kernel<0><<<static_cast<unsigned>(blocks), kAggThreads, 0, stream>>>(p);
+        const cudaError_t e = launch_overlapped(tile_aggregate_kernel<0>, dim3(static_cast<unsigned>(blocks)),
+                                                dim3(kAggThreads), 0, stream, p);
+        if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     } else {
         p.src = static_cast<const __nv_bfloat16 *>(fp.dy);
         p.sb = fp.g_sb; p.sl = fp.g_sl; p.sh = fp.g_sh;
-        tile_aggregate_kernel<1><<<static_cast<unsigned>(blocks), kAggThreads, 0, stream>>>(p);
+        const cudaError_t e = launch_overlapped(tile_aggregate_kernel<1>, dim3(static_cast<unsigned>(blocks)),
+                                                dim3(kAggThreads), 0, stream, p);
+        if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     }
     return check_launch();
 }
