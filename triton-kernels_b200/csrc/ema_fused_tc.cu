@@ -517,9 +517,8 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    // set-up done: the next kernel on the stream may be scheduled; nothing before this line has touched global memory,
-    // everything after it may depend on the kernel before this one
-    grid_dependents_launch();
+    // set-up done; nothing before this line has touched global memory, everything after it may depend on the kernel
+    // before this one on the stream
     grid_dependency_wait();
 
     const Sched sched(p.n_items, p.n_tiles, p.split != 0);
@@ -543,6 +542,9 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             if (lane == 0) {
                 uint32_t it = 0;
                 for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
+                    // whole items, several per thread block: the SMs that other thread blocks leave early are better used
+                    // by the next kernel's set-up from the last item on (see the end of this loop)
+                    if (!sched.split && sched.n > 1 && pi == sched.n - 1) grid_dependents_launch();
                     const Piece pc = sched.get<true>(pi);
                     const int dt0 = item_dt0(pc.item), nsub = item_nsub(pc.item);
                     const int64_t row = item_row(pc.item);
@@ -560,6 +562,11 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         }
                     }
                 }
+                // The last loads are on their way: from here on the next kernel on the stream may be brought in (it
+                // does its set-up on the SMs that free up and waits for this grid to finish before touching memory).
+                // Not from the start: thread blocks of the next kernel that sit waiting on the idle SMs for a whole
+                // kernel would keep small kernels of other streams - a collective - from finding room.
+                grid_dependents_launch();
             }
         } else if (warp == 1) {
             // ---------------- MMA issuer ----------------
@@ -1031,9 +1038,8 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    // set-up done: the next kernel on the stream may be scheduled; nothing before this line has touched global memory,
-    // everything after it may depend on the kernel before this one
-    grid_dependents_launch();
+    // set-up done; nothing before this line has touched global memory, everything after it may depend on the kernel
+    // before this one on the stream
     grid_dependency_wait();
 
     // arrival counter of the per-head reduction that follows this kernel (it sits right before the partial sums)
@@ -1059,6 +1065,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             if (lane == 0) {
                 uint32_t it = 0;
                 for (int pi = 0; pi < sched.n && !*abort_flag; ++pi) {
+                    if (!sched.split && sched.n > 1 && pi == sched.n - 1) grid_dependents_launch();   // (see the forward kernel)
                     const Piece pc = sched.get<false>(pi);
                     const int dt0 = item_dt0(pc.item), nsub = item_nsub(pc.item);
                     const int64_t row = item_row(pc.item);
@@ -1077,6 +1084,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                         tma_load_4d(dst + kTileBytes + kBlockBytes, &tm_g, bar(B_FULL + s), c0 + kBlockCols, hi, k * QT, bi);
                     }
                 }
+                grid_dependents_launch();   // the last loads are on their way (see the forward kernel)
             }
         } else if (warp == 1) {
             // ---------------- MMA issuer ----------------
