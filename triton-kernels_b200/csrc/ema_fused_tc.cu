@@ -451,7 +451,8 @@ struct FwdSmem {
     static constexpr int cs = e + kRing * QT * 4;              // float[128] cumulative log2 decay
     static constexpr int pw = cs + QT * 4;                     // float[128] input weights
     static constexpr int wlo = pw + QT * 4;                    // float[128] column table of the off-diagonal chunks
-    static constexpr int wt = wlo + QT * 4;                    // float[4] scan scratch
+    static constexpr int ow = wlo + QT * 4;                    // float[kRing][128] output weight per row and build (weighted scan)
+    static constexpr int wt = ow + kRing * QT * 4;             // float[4] scan scratch
     static constexpr int bars = wt + 16;
     // stage full/empty/staged, acc full/empty, matrix full/empty, carry ready
     static constexpr int n_bars = 3 * kFwdStages + 4 + 2 * kFwdMatBufs + kFwdHRing;
@@ -486,6 +487,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     float *cs_sm = reinterpret_cast<float *>(smem + FwdSmem::cs);
     float *p_sm = reinterpret_cast<float *>(smem + FwdSmem::pw);
     float *wlo_sm = reinterpret_cast<float *>(smem + FwdSmem::wlo);
+    float *ow_sm = reinterpret_cast<float *>(smem + FwdSmem::ow);
     float *wt_sm = reinterpret_cast<float *>(smem + FwdSmem::wt);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + FwdSmem::abort_flag);
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + FwdSmem::tmem_slot);
@@ -707,12 +709,6 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 const int acc = it & 1, slot = it & (kFwdHRing - 1), s = it % kFwdStages;
                 const uint32_t aph = (it >> 1) & 1, hph = (it / kFwdHRing) & 1;
                 if (u == 0 && (per_step || hi != cur_head)) { cur_head = hi; ++mt; }
-                float out_w = 1.f;   // fetched before the wait, used after the side outputs
-                if (WEIGHTED && p.out_weight) {
-                    const int tw = k * QT + m;
-                    out_w = tw < L ? *EMA_AT(p, p.out_weight + (row / p.h) * p.a_sb + static_cast<int64_t>(tw) * p.a_sl + hi * p.a_sh, 112)
-                                   : 0.f;
-                }
                 if (AGG && loader && k + 1 < pc.k1) {   // the state entering this channel tile's next tile
                     const float hn = fmaf(agg_p, u == 0 ? h_reg0 : h_reg1, u == 0 ? agg_s0 : agg_s1);
                     if (u == 0) h_reg0 = hn; else h_reg1 = hn;
@@ -731,6 +727,10 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 __syncwarp();
                 tc_fence_after_sync();
                 const float E = e_sm[((mt - 1) & (kRing - 1)) * QT + m];
+                // the row's output weight comes with the matrix, fetched by the builders a tile ahead: a global load
+                // here would put the latency of loaded DRAM into every tile
+                float out_w = 1.f;
+                if constexpr (WEIGHTED) out_w = ow_sm[((mt - 1) & (kRing - 1)) * QT + m];
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * DT + half * 64;
                 if (lane == 0) mbar_wait(bar(B_H + slot), hph, abort_flag, 6);
                 __syncwarp();
@@ -826,8 +826,8 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         });
         const uint8_t *cs_b = smem + FwdSmem::cs, *p_b = smem + FwdSmem::pw, *wlo_b = smem + FwdSmem::wlo;
         // one build: scan log2 a, produce the matrix into registers, then store it when the buffer is free
-        // (l2 and pw are read from the row owners only)
-        auto build = [&](float l2, float pw) {
+        // (l2, pw and the row's output weight ow are read from the row owners only)
+        auto build = [&](float l2, float pw, float ow) {
             const int mb = mt % kFwdMatBufs;
             float to_end = 0.f, from_start = 0.f;
             builder_scan(l2, bt, cs_sm, wt_sm, to_end, from_start);
@@ -843,7 +843,10 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             if (lane == 0) mbar_wait(bar(B_MAT_EMPTY + mb), ((mt / kFwdMatBufs) & 1) ^ 1, abort_flag, 8);
             __syncwarp();
             store_matrix(og, dgm, smem + FwdSmem::mat + mb * kMatBytes, g);
-            if (row_owner) e_sm[(mt & (kRing - 1)) * QT + r] = E;
+            if (row_owner) {
+                e_sm[(mt & (kRing - 1)) * QT + r] = E;
+                if constexpr (WEIGHTED) ow_sm[(mt & (kRing - 1)) * QT + r] = ow;
+            }
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(B_MAT_FULL + mb));
@@ -859,7 +862,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 const float v = *EMA_AT(p, arow, 118);
                 if (static_cast<int>(hi) != cur_head) {
                     cur_head = static_cast<int>(hi);
-                    build(log2_decay(v), conv ? 1.f : 1.f - v);
+                    build(log2_decay(v), conv ? 1.f : 1.f - v, 1.f);
                 }
                 if (p.log_decay_sum && bt == 0 && dtile == 0)
                     *EMA_AT(p, p.log_decay_sum + row, 119) = static_cast<float>(L) * (conv ? v : logf(v));
@@ -878,15 +881,26 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             if constexpr (WEIGHTED)
                 w_next = (row_owner && pc.k0 * QT + r < L) ? *EMA_AT(p, wrow + static_cast<int64_t>(pc.k0 * QT + r) * p.a_sl, 121)
                                                            : 0.f;
+            // output weights (WEIGHTED only): fetched like the input weights and handed to the epilogue with the matrix
+            // (1 without an output-weight tensor, 0 past the end of the sequence)
+            const float *orow = p.out_weight ? p.out_weight + bi * p.a_sb + hi * p.a_sh : nullptr;
+            auto out_weight_at = [&](int t) {
+                if (!orow) return 1.f;
+                return (row_owner && t < L) ? *EMA_AT(p, orow + static_cast<int64_t>(t) * p.a_sl, 112) : 0.f;
+            };
+            float o_next = 1.f;
+            if constexpr (WEIGHTED) o_next = out_weight_at(pc.k0 * QT + r);
             for (int k = pc.k0; k < pc.k1; ++k) {
-                const float v = v_next, w = w_next;
+                const float v = v_next, w = w_next, ow = o_next;
                 if (k + 1 < pc.k1) {
                     const int t = (k + 1) * QT + r;
                     v_next = (row_owner && t < L) ? *EMA_AT(p, arow + static_cast<int64_t>(t) * p.a_sl, 122) : ident;
-                    if constexpr (WEIGHTED)
+                    if constexpr (WEIGHTED) {
                         w_next = (row_owner && t < L) ? *EMA_AT(p, wrow + static_cast<int64_t>(t) * p.a_sl, 123) : 0.f;
+                        o_next = out_weight_at(t);
+                    }
                 }
-                build(log2_decay(v), has_w ? w : (conv ? 1.f : 1.f - v));
+                build(log2_decay(v), has_w ? w : (conv ? 1.f : 1.f - v), ow);
                 // cs_sm[127] now holds log2 of the product of this tile's decays
                 if (p.log_decay_sum && bt == 0) logsum += cs_sm[QT - 1] * 0.6931471805599453f;
             }
