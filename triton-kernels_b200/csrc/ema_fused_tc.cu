@@ -996,7 +996,10 @@ static_assert(kBwdSmemBytes <= 227 * 1024, "backward shared memory exceeds the p
 
 // AGG: the aggregate schedule (split = 2) as its own instantiation: the adjoint entering every tile is the fold of
 // the per-tile adjoint aggregates, g_{k-1} = G_k + F_k g_k, carried in a register by the thread that owns the channel.
-template <bool AGG>
+// PER_STEP: the kind of decay, also as instantiations: 1 % (time-invariant decay) to 2-4 % (per-step decay, long sequences)
+// faster under sustained load than one kernel that branches on it.  (The same split of the forward kernel measured
+// 3-4 % slower with a per-step decay and 20 % slower for the weighted scan, and was not kept.)
+template <bool AGG, bool PER_STEP>
 __global__ void __launch_bounds__(kThreads, 1)
 ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_g,
                   const __grid_constant__ CUtensorMap tm_o, const TcBwdParams p) {
@@ -1011,7 +1014,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         return;
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const bool per_step = p.decay_mode == EMA_DECAY_PER_STEP;
+    constexpr bool per_step = PER_STEP;
     const int conv = p.convention;
     const int L = static_cast<int>(p.L);
 
@@ -1947,7 +1950,9 @@ int launch_fused_bwd_tc(const FusedParams &fp, cudaStream_t stream) {
     }
     const int grid = pl.grid;
     g_last_schedule = pl.split;
-    auto kernel = pl.split == 2 ? tc::ema_bwd_tc_kernel<true> : tc::ema_bwd_tc_kernel<false>;
+    const bool ps = p.decay_mode == EMA_DECAY_PER_STEP;
+    auto kernel = pl.split == 2 ? (ps ? tc::ema_bwd_tc_kernel<true, true> : tc::ema_bwd_tc_kernel<true, false>)
+                                : (ps ? tc::ema_bwd_tc_kernel<false, true> : tc::ema_bwd_tc_kernel<false, false>);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kBwdSmemBytes);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     e = launch_overlapped(kernel, dim3(grid), dim3(tc::kThreads), tc::kBwdSmemBytes, stream, tm_x, tm_g, tm_o, p);
