@@ -53,8 +53,17 @@ constexpr int kEpiWarps = kEpiThreads / 32;
 constexpr int kBuildThread0 = 384;         // warps 12-19
 constexpr int kBuildThreads = 256;
 constexpr int kBuildWarps = kBuildThreads / 32;
-// registers per thread after the role split; 128*48 + 256*136 + 256*80 = 640*96, the allocation at launch
-constexpr int kRegsLight = 48, kRegsEpilogue = 136, kRegsBuilder = 80;
+// Registers per thread after setmaxnreg.  The thread block starts with 96 x 640 = 61440 and the roles must add up to
+// that: 128 light threads, 256 epilogue threads, 256 builder threads.  Where a matrix is built for every tile (the
+// backward with a per-step decay: two matrices and their tables live in the builders' registers; the weighted forward)
+// the builders get 8 more and the epilogue 8 fewer: 4-8 % faster there, 1-4 % slower in the plain forward, which keeps
+// 136 / 80.
+constexpr int kRegsLight = 48;
+template <bool BUILD_HEAVY>
+struct RoleRegs {
+    static constexpr int epilogue = BUILD_HEAVY ? 128 : 136, builder = BUILD_HEAVY ? 88 : 80;
+    static_assert(128 * kRegsLight + 256 * epilogue + 256 * builder == 96 * kThreads, "register pool of the thread block");
+};
 constexpr int kRing = 4;                   // depth of the forward kernel's ring of per-build carry factors
 constexpr uint32_t kIdesc = make_idesc_bf16(QT, DT, 0, 1);
 
@@ -644,7 +653,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             }
         }
     } else if (tid < kBuildThread0) {
-        reg_inc<kRegsEpilogue>();
+        reg_inc<RoleRegs<WEIGHTED>::epilogue>();
         // ---------------- epilogue ----------------
         // Thread (q, lane, half) owns row m = 32 q + lane and channels [64 half, 64 half + 64) of the tile,
         // handled 32 at a time.  The two threads of row 127 are the serial carry chain: they publish the
@@ -811,7 +820,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             }
         }
     } else {
-        reg_dec<kRegsBuilder>();
+        reg_dec<RoleRegs<WEIGHTED>::builder>();
         // ---------------- matrix builders ----------------
         const int bt = tid - kBuildThread0;   // 0-255; threads 0-127 also own row r = bt of the per-row tables
         const int r = bt & 127;
@@ -1182,7 +1191,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             }
         }
     } else if (tid < kBuildThread0) {
-        reg_inc<kRegsEpilogue>();
+        reg_inc<RoleRegs<PER_STEP>::epilogue>();
         // ---------------- epilogue ----------------
         // thread (q, lane, half): row m = 32 q + lane, channels [64 half, 64 half + 64) of the tile, 32 at a time.
         // The two threads of row 0 are the serial carry chain (the adjoint handed to the tile on the left).
@@ -1377,7 +1386,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             }
         }
     } else {
-        reg_dec<kRegsBuilder>();
+        reg_dec<RoleRegs<PER_STEP>::builder>();
         // ---------------- matrix builders ----------------
         const int bt = tid - kBuildThread0;   // 0-255; threads 0-127 also own row r = bt of the per-row tables
         const int r = bt & 127;
