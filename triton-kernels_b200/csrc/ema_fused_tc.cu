@@ -54,10 +54,10 @@ constexpr int kBuildThread0 = 384;         // warps 12-19
 constexpr int kBuildThreads = 256;
 constexpr int kBuildWarps = kBuildThreads / 32;
 // Registers per thread after setmaxnreg.  The thread block starts with 96 x 640 = 61440 and the roles must add up to
-// that: 128 light threads, 256 epilogue threads, 256 builder threads.  Where a matrix is built for every tile (the
-// backward with a per-step decay: two matrices and their tables live in the builders' registers; the weighted forward)
-// the builders get 8 more and the epilogue 8 fewer: 4-8 % faster there, 1-4 % slower in the plain forward, which keeps
-// 136 / 80.
+// that: 128 light threads, 256 epilogue threads, 256 builder threads.  BUILD_HEAVY gives the builders 8 more and the
+// epilogue 8 fewer: 2-12 % faster in the backward with a per-step decay (two matrices and their tables live in the
+// builders' registers), faster or slower in the weighted forward depending on the launch (its launcher chooses), 1-4 %
+// slower in the plain forward, which keeps 136 / 80.
 constexpr int kRegsLight = 48;
 template <bool BUILD_HEAVY>
 struct RoleRegs {
@@ -479,7 +479,8 @@ static_assert(kFwdSmemBytes <= 227 * 1024, "forward shared memory exceeds the pe
 // fold of the per-tile aggregates, h_{k+1} = P_k h_k + S_k, carried in a register by the thread that owns the
 // channel - the same fp32 chain wherever the pieces are cut, so the results do not depend on the grid - and the last
 // row of the product is no longer on a serial chain.
-template <bool WEIGHTED, bool AGG>
+// BUILD_HEAVY: the register split of RoleRegs (weighted scans only; chosen by the launcher).
+template <bool WEIGHTED, bool AGG, bool BUILD_HEAVY = false>
 __global__ void __launch_bounds__(kThreads, 1)
 ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_y,
                   const TcParams p) {
@@ -653,7 +654,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             }
         }
     } else if (tid < kBuildThread0) {
-        reg_inc<RoleRegs<WEIGHTED>::epilogue>();
+        reg_inc<RoleRegs<BUILD_HEAVY>::epilogue>();
         // ---------------- epilogue ----------------
         // Thread (q, lane, half) owns row m = 32 q + lane and channels [64 half, 64 half + 64) of the tile,
         // handled 32 at a time.  The two threads of row 127 are the serial carry chain: they publish the
@@ -820,7 +821,7 @@ ema_fwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             }
         }
     } else {
-        reg_dec<RoleRegs<WEIGHTED>::builder>();
+        reg_dec<RoleRegs<BUILD_HEAVY>::builder>();
         // ---------------- matrix builders ----------------
         const int bt = tid - kBuildThread0;   // 0-255; threads 0-127 also own row r = bt of the per-row tables
         const int r = bt & 127;
@@ -1914,7 +1915,11 @@ int launch_fused_fwd_tc(const FusedParams &fp, cudaStream_t stream) {
     }
     const int grid = pl.grid;
     g_last_schedule = pl.split;
-    auto kernel = weighted ? tc::ema_fwd_tc_kernel<true, false>
+    // weighted scan: the builders' larger register share pays when most SMs are busy and a matrix serves two channel
+    // tiles (measured: 5-6 % faster at d = 256 and 1024 with 128 thread blocks, 5-10 % slower with 64 thread blocks or
+    // one channel tile per item)
+    const bool heavy = weighted && p.sub == 2 && grid >= 100;
+    auto kernel = weighted ? (heavy ? tc::ema_fwd_tc_kernel<true, false, true> : tc::ema_fwd_tc_kernel<true, false, false>)
                            : (pl.split == 2 ? tc::ema_fwd_tc_kernel<false, true> : tc::ema_fwd_tc_kernel<false, false>);
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kFwdSmemBytes);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
