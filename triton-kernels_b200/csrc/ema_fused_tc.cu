@@ -1009,7 +1009,11 @@ static_assert(kBwdSmemBytes <= 227 * 1024, "backward shared memory exceeds the p
 // PER_STEP: the kind of decay, also as instantiations: 1 % (time-invariant decay) to 2-4 % (per-step decay, long sequences)
 // faster under sustained load than one kernel that branches on it.  (The same split of the forward kernel measured
 // 3-4 % slower with a per-step decay and 20 % slower for the weighted scan, and was not kept.)
-template <bool AGG, bool PER_STEP>
+// CONV: the decay convention (1: the decay is given as its logarithm and x comes pre-scaled), instantiated as well:
+// another 5-6 % off the launch with a per-step decay, nothing lost with a time-invariant one.
+// CUT: the tile-range schedule (split = 1: items cut between thread blocks, adjoints handed on through global memory);
+// without it the hand-over code is not in the kernel: 2-3 % faster under sustained load on whole items.
+template <bool AGG, bool PER_STEP, bool CONV, bool CUT>
 __global__ void __launch_bounds__(kThreads, 1)
 ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_g,
                   const __grid_constant__ CUtensorMap tm_o, const TcBwdParams p) {
@@ -1025,7 +1029,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr bool per_step = PER_STEP;
-    const int conv = p.convention;
+    constexpr int conv = CONV ? 1 : 0;
     const int L = static_cast<int>(p.L);
 
     float *hs_sm = reinterpret_cast<float *>(smem + BwdSmem::hs);
@@ -1076,7 +1080,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     // arrival counter of the per-head reduction that follows this kernel (it sits right before the partial sums)
     if (!per_step && blockIdx.x == 0 && tid == 0)
         *reinterpret_cast<unsigned *>(EMA_AT(p, p.da_partial + p.head_partial_offset - 4, 165)) = 0u;
-    const Sched sched(p.n_items, p.n_tiles, p.split != 0);
+    const Sched sched(p.n_items, p.n_tiles, AGG || CUT);
     // item -> scan row, first channel tile, number of channel tiles (1 or 2)
     auto item_row = [&](int64_t item) { return item / p.n_groups; };
     auto item_dt0 = [&](int64_t item) { return static_cast<int>(item % p.n_groups) * p.sub; };
@@ -1207,13 +1211,13 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
             const int dt0 = item_dt0(pc.item), nsub = item_nsub(pc.item);
             const int64_t row = item_row(pc.item);
             const int hi = static_cast<int>(row % p.h);
-            const bool publish = !AGG && pc.k0 > 0;   // the item continues to the left in another CTA: hand it the adjoint
+            const bool publish = CUT && pc.k0 > 0;   // the item continues to the left in another CTA: hand it the adjoint
             // cut blockIdx.x is this CTA's left edge (it publishes there), cut blockIdx.x + 1 its right edge (it reads there)
             float *carry_out = p.carry + static_cast<int64_t>(blockIdx.x) * kCarryFloats;
             float hs_next = 0.f;
             float g_reg0 = 0.f, g_reg1 = 0.f;   // AGG: the adjoint entering the current tile, channel m of each sub-tile (loaders)
             if (loader) {
-                if (!AGG && pc.k1 < p.n_tiles) {   // left part of a cut item: the adjoint comes from the CTA that made the right part
+                if (CUT && pc.k1 < p.n_tiles) {   // left part of a cut item: the adjoint comes from the CTA that made the right part
                     if (lane == 0) wait_carry(EMA_AT(p, p.flags + blockIdx.x + 1, 150), 2u * nsub, abort_flag, 23);
                     __syncwarp();
                 }
@@ -1224,7 +1228,7 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     hs_sm[slot0 * DT + m] =
                         ok ? *EMA_AT(p, p.tile_states + (row * p.n_tiles + (pc.k1 - 1)) * p.d + c0u + m, 151) : 0.f;
                     float gv;
-                    if (!AGG && pc.k1 < p.n_tiles) {
+                    if (CUT && pc.k1 < p.n_tiles) {
                         gv = __ldcg(EMA_AT(p, p.carry + static_cast<int64_t>(blockIdx.x + 1) * kCarryFloats + u * DT + m, 152));
                     } else {
                         gv = (p.dfinal_state && ok) ? *EMA_AT(p, p.dfinal_state + row * p.d + c0u + m, 153) : 0.f;
@@ -1965,8 +1969,18 @@ int launch_fused_bwd_tc(const FusedParams &fp, cudaStream_t stream) {
     const int grid = pl.grid;
     g_last_schedule = pl.split;
     const bool ps = p.decay_mode == EMA_DECAY_PER_STEP;
-    auto kernel = pl.split == 2 ? (ps ? tc::ema_bwd_tc_kernel<true, true> : tc::ema_bwd_tc_kernel<true, false>)
-                                : (ps ? tc::ema_bwd_tc_kernel<false, true> : tc::ema_bwd_tc_kernel<false, false>);
+    const bool cv = p.convention != 0;
+    // one instantiation per schedule (aggregates, tile ranges, whole items) x kind of decay x convention
+    const int variant = (pl.split == 2 ? 0 : pl.split == 1 ? 1 : 2) * 4 + (ps ? 2 : 0) + (cv ? 1 : 0);
+    using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const tc::TcBwdParams);
+    static const KernelFn kernels[12] = {
+        tc::ema_bwd_tc_kernel<true, false, false, false>,  tc::ema_bwd_tc_kernel<true, false, true, false>,
+        tc::ema_bwd_tc_kernel<true, true, false, false>,   tc::ema_bwd_tc_kernel<true, true, true, false>,
+        tc::ema_bwd_tc_kernel<false, false, false, true>,  tc::ema_bwd_tc_kernel<false, false, true, true>,
+        tc::ema_bwd_tc_kernel<false, true, false, true>,   tc::ema_bwd_tc_kernel<false, true, true, true>,
+        tc::ema_bwd_tc_kernel<false, false, false, false>, tc::ema_bwd_tc_kernel<false, false, true, false>,
+        tc::ema_bwd_tc_kernel<false, true, false, false>,  tc::ema_bwd_tc_kernel<false, true, true, false>};
+    const KernelFn kernel = kernels[variant];
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::kBwdSmemBytes);
     if (e != cudaSuccess) { set_last_cuda_error(e); return EMA_ERR_CUDA; }
     e = launch_overlapped(kernel, dim3(grid), dim3(tc::kThreads), tc::kBwdSmemBytes, stream, tm_x, tm_g, tm_o, p);
