@@ -1084,7 +1084,10 @@ ema_bwd_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     // item -> scan row, first channel tile, number of channel tiles (1 or 2)
     auto item_row = [&](int64_t item) { return item / p.n_groups; };
     auto item_dt0 = [&](int64_t item) { return static_cast<int>(item % p.n_groups) * p.sub; };
+    // (with a time-invariant decay a work item is always one channel tile: the launcher pairs tiles only to share
+    // per-step matrices)
     auto item_nsub = [&](int64_t item) {
+        if constexpr (!PER_STEP) return 1;
         const int left = p.n_dtiles - static_cast<int>(item % p.n_groups) * p.sub;
         return left < p.sub ? left : p.sub;
     };
